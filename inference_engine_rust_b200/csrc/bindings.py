@@ -1,0 +1,196 @@
+"""ctypes bindings of the CUDA launchers.  Every function here launches hand-written
+kernels on the current CUDA stream; there is no other implementation behind them, so a
+machine without the built library (or without a GPU) gets an error, not a fallback.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import POINTER, Structure, byref, c_char_p, c_float, c_int, c_longlong, c_ulonglong, c_void_p
+from typing import Optional
+
+import torch
+
+from . import build
+
+F32, BF16 = 0, 1
+PAIR_HALF, PAIR_INTERLEAVED = 0, 1
+GEMM_STORE, GEMM_ADD_RESIDUAL = 0, 1
+
+ERR_TOKEN_RANGE, ERR_NONFINITE_LOGIT, ERR_PAGE_RANGE, ERR_WAIT_EXPIRED = 1, 2, 4, 8
+_ERR_TEXT = {
+    ERR_TOKEN_RANGE: "a token id outside [0, vocab) reached the embedding kernel",
+    ERR_NONFINITE_LOGIT: "sampling saw a NaN or infinite logit",
+    ERR_PAGE_RANGE: "a page-table entry outside the page pool was read",
+    ERR_WAIT_EXPIRED: "a bounded wait inside a kernel expired",
+}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+class KvView(Structure):
+    """Mirror of `IertKvView` (common.cuh)."""
+    _fields_ = [("k", c_void_p), ("v", c_void_p), ("page_table", c_void_p),
+                ("table_width", c_int), ("ring_pages", c_int), ("page_tokens", c_int),
+                ("n_pages", c_int), ("kv_heads", c_int), ("head_dim", c_int),
+                ("dtype", c_int), ("window", c_int)]
+
+
+class BatchView(Structure):
+    """Mirror of `IertBatchView` (common.cuh)."""
+    _fields_ = [("cu_q", c_void_p), ("slot_ids", c_void_p), ("tok_seq", c_void_p),
+                ("pos0", c_void_p), ("n_seqs", c_int), ("n_tokens", c_int)]
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.float32:
+        return F32
+    if dt == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 or bfloat16, got {dt}")
+
+
+_core = None
+
+
+def core() -> ctypes.CDLL:
+    """The core library, built on first use."""
+    global _core
+    if _core is None:
+        lib = build.load_library("iert_core", build.CORE_SOURCES)
+        _declare(lib)
+        _core = lib
+    return _core
+
+
+def _declare(lib) -> None:
+    S = c_void_p  # cudaStream_t
+    P = c_void_p
+    lib.iert_last_cuda_error.restype = c_char_p
+    lib.iert_device_arch.restype = c_int
+    lib.iert_sm_count.restype = c_int
+    sigs = {
+        "iert_embed_gather": [P, c_int, P, P, c_int, c_int, c_int, c_float, P, S],
+        "iert_rmsnorm": [P, P, c_int, P, c_int, P, c_int, c_int, c_float, S],
+        "iert_rope_kv_store": [P, c_int, POINTER(BatchView), POINTER(KvView), P, c_int, c_int, c_int, c_int, P, S],
+        "iert_silu_mul": [P, P, c_int, c_int, c_int, S],
+        "iert_add_into": [P, P, c_int, c_longlong, S],
+        "iert_advance_positions": [P, P, P, c_int, S],
+        "iert_gemm_plain": [P, c_int, P, c_int, P, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int, S],
+        "iert_attention_plain": [P, P, c_int, POINTER(BatchView), POINTER(KvView), c_int, c_float, c_int, P, S],
+        "iert_sample_greedy": [P, c_int, c_int, c_longlong, P, P, S],
+        "iert_sample_temperature": [P, c_int, c_int, c_longlong, c_float, c_ulonglong, P, P, P, P, S],
+        "iert_uniform_draws": [c_ulonglong, P, P, P, c_int, S],
+    }
+    for name, args in sigs.items():
+        fn = getattr(lib, name)
+        fn.argtypes = args
+        fn.restype = c_int
+
+
+def check(status: int, what: str) -> None:
+    if status == 0:
+        return
+    if status == 1:
+        raise KernelError(f"{what}: the kernel does not take these sizes or options")
+    msg = core().iert_last_cuda_error().decode("utf-8", "replace")
+    raise KernelError(f"{what}: CUDA error: {msg}")
+
+
+def require_device() -> None:
+    """Refuse to run anywhere but on an sm_100 GPU with the built library."""
+    if not torch.cuda.is_available():
+        raise KernelError("no CUDA device: this package runs its hand-written sm_100a kernels only")
+    arch = core().iert_device_arch()
+    if arch < 0:
+        raise KernelError("device query failed: " + core().iert_last_cuda_error().decode())
+    if arch // 10 != 10:
+        raise KernelError(f"the kernels are built for sm_100a; this device is sm_{arch}")
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def describe_error_bits(bits: int) -> str:
+    return "; ".join(t for b, t in _ERR_TEXT.items() if bits & b) or f"unknown error bits {bits}"
+
+
+# ---------------------------------------------------------------------------------------
+# thin wrappers: tensors in, launch, nothing returned
+
+
+def embed_gather(table, ids, x, scale: float, err, stream) -> None:
+    vocab, hidden = table.shape
+    check(core().iert_embed_gather(table.data_ptr(), dtype_code(table.dtype), ids.data_ptr(),
+                                   x.data_ptr(), ids.numel(), hidden, vocab, scale,
+                                   err.data_ptr(), stream), "embed_gather")
+
+
+def rmsnorm(x, w, out, eps: float, stream, rows_idx=None, rows: Optional[int] = None) -> None:
+    hidden = x.shape[-1]
+    n = rows if rows is not None else (rows_idx.numel() if rows_idx is not None else x.shape[0])
+    check(core().iert_rmsnorm(x.data_ptr(), w.data_ptr(), dtype_code(w.dtype), out.data_ptr(),
+                              dtype_code(out.dtype),
+                              rows_idx.data_ptr() if rows_idx is not None else None,
+                              n, hidden, eps, stream), "rmsnorm")
+
+
+def rope_kv_store(qkv, batch: BatchView, kv: KvView, inv_freq, heads: int, rotary_dim: int,
+                  pairing: int, write_cache: bool, err, stream) -> None:
+    check(core().iert_rope_kv_store(qkv.data_ptr(), dtype_code(qkv.dtype), byref(batch), byref(kv),
+                                    inv_freq.data_ptr(), heads, rotary_dim, pairing,
+                                    1 if write_cache else 0, err.data_ptr(), stream), "rope_kv_store")
+
+
+def silu_mul(gu, out, n_tokens: int, inter: int, stream) -> None:
+    check(core().iert_silu_mul(gu.data_ptr(), out.data_ptr(), dtype_code(gu.dtype), n_tokens, inter,
+                               stream), "silu_mul")
+
+
+def add_into(residual, y, n: int, stream) -> None:
+    check(core().iert_add_into(residual.data_ptr(), y.data_ptr(), dtype_code(y.dtype), n, stream),
+          "add_into")
+
+
+def advance_positions(batch: "BatchView", stream) -> None:
+    check(core().iert_advance_positions(batch.pos0, batch.cu_q, batch.slot_ids, batch.n_seqs, stream),
+          "advance_positions")
+
+
+def gemm_plain(x, w, out, M: int, mode: int, stream) -> None:
+    """out[:M] (=|+=) x[:M] @ w.T with x [*, K], w [N, K], out [*, N]; row strides taken
+    from the tensors."""
+    N, K = w.shape
+    check(core().iert_gemm_plain(x.data_ptr(), dtype_code(x.dtype), w.data_ptr(), dtype_code(w.dtype),
+                                 out.data_ptr(), dtype_code(out.dtype), M, N, K,
+                                 x.stride(0), w.stride(0), out.stride(0), mode, stream), "gemm_plain")
+
+
+def attention_plain(qkv, out, batch: BatchView, kv: KvView, heads: int, scale: float, paged: bool,
+                    err, stream) -> None:
+    check(core().iert_attention_plain(qkv.data_ptr(), out.data_ptr(), dtype_code(qkv.dtype),
+                                      byref(batch), byref(kv), heads, scale, 1 if paged else 0,
+                                      err.data_ptr(), stream), "attention_plain")
+
+
+def sample_greedy(logits, out, err, stream) -> None:
+    rows, vocab = logits.shape
+    check(core().iert_sample_greedy(logits.data_ptr(), rows, vocab, logits.stride(0), out.data_ptr(),
+                                    err.data_ptr(), stream), "sample_greedy")
+
+
+def sample_temperature(logits, temperature: float, seed: int, request_ids, step_ids, out, err,
+                       stream) -> None:
+    rows, vocab = logits.shape
+    check(core().iert_sample_temperature(logits.data_ptr(), rows, vocab, logits.stride(0),
+                                         temperature, seed & 0xFFFFFFFFFFFFFFFF,
+                                         request_ids.data_ptr(), step_ids.data_ptr(), out.data_ptr(),
+                                         err.data_ptr(), stream), "sample_temperature")
+
+
+def uniform_draws(seed: int, request_ids, step_ids, out, stream) -> None:
+    check(core().iert_uniform_draws(seed & 0xFFFFFFFFFFFFFFFF, request_ids.data_ptr(),
+                                    step_ids.data_ptr(), out.data_ptr(), out.numel(), stream),
+          "uniform_draws")

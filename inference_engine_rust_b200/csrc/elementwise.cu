@@ -1,0 +1,240 @@
+// Memory-bound kernels of the step: embedding gather, RMSNorm (with optional row gather),
+// rotary encoding fused with the cache write, SiLU(gate)*up, residual add, and the
+// sequence-length update.  Statistics, angles and the residual stream are fp32 whatever
+// the storage type.
+#include "common.cuh"
+
+using namespace iert;
+
+// ---------------------------------------------------------------------------------------
+// Embedding gather: x[t, :] = table[ids[t], :] * scale, x in fp32 (the residual stream).
+// Reference: src/layers/embeddings.rs:15-17,119-139; scale src/engine/embed.rs:140-149.
+template <typename TW>
+__global__ void embed_gather_kernel(const TW* __restrict__ table, const int* __restrict__ ids,
+                                    float* __restrict__ x, int hidden, int vocab, float scale,
+                                    int* __restrict__ err) {
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  float* row = x + (size_t)t * hidden;
+  if (id < 0 || id >= vocab) {
+    if (threadIdx.x == 0) atomicOr(err, IERT_ERR_TOKEN_RANGE);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) row[i] = 0.f;
+    return;
+  }
+  const TW* src = table + (size_t)id * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) row[i] = to_f32(src[i]) * scale;
+}
+
+IERT_API int iert_embed_gather(const void* table, int table_dtype, const int* ids, float* x,
+                               int n_tokens, int hidden, int vocab, float scale, int* err,
+                               cudaStream_t stream) {
+  if (n_tokens <= 0) return IERT_OK;
+  if (hidden <= 0 || vocab <= 0) return IERT_BAD_ARGUMENT;
+  const int threads = hidden >= 1024 ? 256 : 128;
+  if (table_dtype == IERT_F32)
+    embed_gather_kernel<float><<<n_tokens, threads, 0, stream>>>((const float*)table, ids, x, hidden, vocab, scale, err);
+  else if (table_dtype == IERT_BF16)
+    embed_gather_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>((const __nv_bfloat16*)table, ids, x, hidden, vocab, scale, err);
+  else
+    return IERT_BAD_ARGUMENT;
+  return iert_check_launch("embed_gather");
+}
+
+// ---------------------------------------------------------------------------------------
+// RMSNorm: out[r, i] = x[row(r), i] * w[i] / sqrt(mean(x^2) + eps), statistics in fp32.
+// `rows_idx` (optional) gathers rows of x: the final norm runs only on the rows whose
+// logits are wanted.  Reference: src/ops/rmsnorm.rs:38-48.
+template <typename TW, typename TO>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const TW* __restrict__ w,
+                               TO* __restrict__ out, const int* __restrict__ rows_idx,
+                               int hidden, float eps) {
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  const int src_row = rows_idx ? rows_idx[r] : r;
+  const float* xr = x + (size_t)src_row * hidden;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float v = xr[i];
+    ss += v * v;
+  }
+  ss = block_sum(ss, scratch);
+  const float rinv = 1.0f / sqrtf(ss / (float)hidden + eps);
+  TO* o = out + (size_t)r * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+    o[i] = from_f32<TO>(xr[i] * to_f32(w[i]) * rinv);
+}
+
+IERT_API int iert_rmsnorm(const float* x, const void* w, int w_dtype, void* out, int out_dtype,
+                          const int* rows_idx, int rows, int hidden, float eps,
+                          cudaStream_t stream) {
+  if (rows <= 0) return IERT_OK;
+  if (hidden <= 0) return IERT_BAD_ARGUMENT;
+  const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+#define LAUNCH(TW, TO) rmsnorm_kernel<TW, TO><<<rows, threads, 0, stream>>>( \
+    x, (const TW*)w, (TO*)out, rows_idx, hidden, eps)
+  if (w_dtype == IERT_F32 && out_dtype == IERT_F32) LAUNCH(float, float);
+  else if (w_dtype == IERT_F32 && out_dtype == IERT_BF16) LAUNCH(float, __nv_bfloat16);
+  else if (w_dtype == IERT_BF16 && out_dtype == IERT_F32) LAUNCH(__nv_bfloat16, float);
+  else if (w_dtype == IERT_BF16 && out_dtype == IERT_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+  else return IERT_BAD_ARGUMENT;
+#undef LAUNCH
+  return iert_check_launch("rmsnorm");
+}
+
+// ---------------------------------------------------------------------------------------
+// Rotary encoding of the query and key heads of a packed [T, (heads + 2*kv_heads)*head_dim]
+// projection, in place, fused with the write of the rotated keys and the values into the
+// paged cache.  One block per (token, head); heads [0, heads) are queries, the next
+// kv_heads are keys, the last kv_heads are values.
+//   angle(pos, k) = pos * inv_freq[k] in fp32; (a, b) -> (a cos - b sin, a sin + b cos)
+// Reference: src/ops/rope.rs:40-57 (rotation), src/layers/attention.rs:314-352 (order:
+// rotate, then append), :518-520 (decode position = cache length before the append).
+// A key or value is stored only if it can still be seen after this step: its position is
+// within the last ring_pages*page_tokens positions of its sequence.
+template <typename T>
+__global__ void rope_kv_store_kernel(T* __restrict__ qkv, IertBatchView b, IertKvView c,
+                                     const float* __restrict__ inv_freq, int heads,
+                                     int rotary_dim, int pairing, int write_cache,
+                                     int* __restrict__ err) {
+  const int t = blockIdx.x;
+  const int head = blockIdx.y;
+  const int s = b.tok_seq[t];
+  if (s < 0) return;
+  const int slot = b.slot_ids[s];
+  if (slot < 0) return;
+  const int hd = c.head_dim, nkv = c.kv_heads;
+  const int q_begin = b.cu_q[s], q_len = b.cu_q[s + 1] - q_begin;
+  const int pos = b.pos0[s] + (t - q_begin);
+  const int final_len = b.pos0[s] + q_len;
+  T* vec = qkv + ((size_t)t * (heads + 2 * nkv) + head) * hd;
+
+  const bool is_q = head < heads;
+  const bool is_k = !is_q && head < heads + nkv;
+  const int kvh = is_q ? 0 : (is_k ? head - heads : head - heads - nkv);
+  T* dst = nullptr;
+  if (!is_q && write_cache && pos >= final_len - c.ring_pages * c.page_tokens) {
+    const long long off = kv_row_offset(c, slot, pos, kvh, err);
+    if (off >= 0) dst = (T*)(is_k ? c.k : c.v) + off;
+  }
+
+  if (is_q || is_k) {
+    const int half = rotary_dim / 2;
+    for (int k = threadIdx.x; k < half; k += blockDim.x) {
+      const int i0 = pairing == IERT_PAIR_HALF ? k : 2 * k;
+      const int i1 = pairing == IERT_PAIR_HALF ? k + half : 2 * k + 1;
+      const float angle = (float)pos * inv_freq[k];
+      float sn, cs;
+      sincosf(angle, &sn, &cs);
+      const float a = to_f32(vec[i0]), bb = to_f32(vec[i1]);
+      const T r0 = from_f32<T>(a * cs - bb * sn);
+      const T r1 = from_f32<T>(a * sn + bb * cs);
+      vec[i0] = r0;
+      vec[i1] = r1;
+      if (dst) { dst[i0] = r0; dst[i1] = r1; }
+    }
+    if (dst)
+      for (int i = rotary_dim + threadIdx.x; i < hd; i += blockDim.x) dst[i] = vec[i];
+  } else if (dst) {
+    for (int i = threadIdx.x; i < hd; i += blockDim.x) dst[i] = vec[i];
+  }
+}
+
+IERT_API int iert_rope_kv_store(void* qkv, int dtype, const IertBatchView* batch,
+                                const IertKvView* cache, const float* inv_freq, int heads,
+                                int rotary_dim, int pairing, int write_cache, int* err,
+                                cudaStream_t stream) {
+  if (batch->n_tokens <= 0) return IERT_OK;
+  if (rotary_dim < 0 || rotary_dim > cache->head_dim || (rotary_dim & 1) || cache->dtype != dtype)
+    return IERT_BAD_ARGUMENT;
+  if (pairing != IERT_PAIR_HALF && pairing != IERT_PAIR_INTERLEAVED) return IERT_BAD_ARGUMENT;
+  const int total_heads = heads + 2 * cache->kv_heads;
+  if (total_heads > 65535) return IERT_BAD_ARGUMENT;
+  dim3 grid(batch->n_tokens, total_heads);
+  const int threads = cache->head_dim >= 128 ? 64 : 32;
+  if (dtype == IERT_F32)
+    rope_kv_store_kernel<float><<<grid, threads, 0, stream>>>((float*)qkv, *batch, *cache, inv_freq, heads, rotary_dim, pairing, write_cache, err);
+  else if (dtype == IERT_BF16)
+    rope_kv_store_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>((__nv_bfloat16*)qkv, *batch, *cache, inv_freq, heads, rotary_dim, pairing, write_cache, err);
+  else
+    return IERT_BAD_ARGUMENT;
+  return iert_check_launch("rope_kv_store");
+}
+
+// ---------------------------------------------------------------------------------------
+// SwiGLU activation on a fused [T, 2*I] projection: out[t, i] = silu(gu[t, i]) * gu[t, I+i],
+// sigmoid evaluated on the stable branch.  Reference: src/ops/swiglu.rs:3-36.
+__device__ __forceinline__ float stable_sigmoid(float x) {
+  if (x >= 0.f) return 1.0f / (1.0f + expf(-x));
+  const float z = expf(x);
+  return z / (1.0f + z);
+}
+
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter,
+                                size_t total) {
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / inter;
+    const int i = (int)(idx - t * inter);
+    const float g = to_f32(gu[t * 2 * inter + i]);
+    const float u = to_f32(gu[t * 2 * inter + inter + i]);
+    out[idx] = from_f32<T>(g * stable_sigmoid(g) * u);
+  }
+}
+
+IERT_API int iert_silu_mul(const void* gu, void* out, int dtype, int n_tokens, int inter,
+                           cudaStream_t stream) {
+  if (n_tokens <= 0) return IERT_OK;
+  if (inter <= 0) return IERT_BAD_ARGUMENT;
+  const size_t total = (size_t)n_tokens * inter;
+  const int threads = 256;
+  const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+  if (dtype == IERT_F32)
+    silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, inter, total);
+  else if (dtype == IERT_BF16)
+    silu_mul_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter, total);
+  else
+    return IERT_BAD_ARGUMENT;
+  return iert_check_launch("silu_mul");
+}
+
+// ---------------------------------------------------------------------------------------
+// residual[i] += y[i] in fp32 (src/ops/residual_add.rs:3-12).  Used by parts whose last
+// kernel cannot add into the residual stream itself.
+template <typename T>
+__global__ void add_into_kernel(float* __restrict__ residual, const T* __restrict__ y, size_t n) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    residual[i] += to_f32(y[i]);
+}
+
+IERT_API int iert_add_into(float* residual, const void* y, int y_dtype, long long n,
+                           cudaStream_t stream) {
+  if (n <= 0) return IERT_OK;
+  const int threads = 256;
+  const long long want = (n + threads - 1) / threads;
+  const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+  if (y_dtype == IERT_F32)
+    add_into_kernel<float><<<blocks, threads, 0, stream>>>(residual, (const float*)y, (size_t)n);
+  else if (y_dtype == IERT_BF16)
+    add_into_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(residual, (const __nv_bfloat16*)y, (size_t)n);
+  else
+    return IERT_BAD_ARGUMENT;
+  return iert_check_launch("add_into");
+}
+
+// ---------------------------------------------------------------------------------------
+// After a step: pos0[s] += tokens the sequence brought, so that the same device-resident
+// batch description can drive the next one-token step without the host.
+__global__ void advance_positions_kernel(int* __restrict__ pos0, const int* __restrict__ cu_q,
+                                         const int* __restrict__ slot_ids, int n_seqs) {
+  const int s = blockIdx.x * blockDim.x + threadIdx.x;
+  if (s >= n_seqs) return;
+  if (slot_ids[s] >= 0) pos0[s] += cu_q[s + 1] - cu_q[s];
+}
+
+IERT_API int iert_advance_positions(int* pos0, const int* cu_q, const int* slot_ids, int n_seqs,
+                                    cudaStream_t stream) {
+  if (n_seqs <= 0) return IERT_OK;
+  advance_positions_kernel<<<(n_seqs + 127) / 128, 128, 0, stream>>>(pos0, cu_q, slot_ids, n_seqs);
+  return iert_check_launch("advance_positions");
+}

@@ -1,0 +1,199 @@
+"""The step function: one batch of sequences, either all at their first token (prompts of
+unequal lengths, packed back to back) or all bringing one more token, run through the
+model against the cache.  It runs exactly the tokens it is given and returns the logits at
+the wanted places.
+
+Reference: `InferenceSession::prefill` / `decode_token` / `logits_last_token`
+(src/engine/session.rs:44-74) for one sequence; the host-side checks are the reference's
+error classes (empty prompt and too-long prompt src/engine/embed.rs:109-118, token out of
+vocabulary src/layers/embeddings.rs:119-126, cache full src/layers/attention.rs:55-59),
+raised here before anything is launched.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence, Tuple, Union
+
+import numpy as np
+import torch
+
+from ..cache import Cache, CacheError, CacheFull
+from ..csrc import bindings as B
+from ..parts.base import StepContext
+from .model import Model
+
+
+class StepError(ValueError):
+    """A step that cannot run as asked (checked on the host; nothing was launched)."""
+
+
+class DeviceFault(RuntimeError):
+    """A kernel reported a problem through the device error word."""
+
+
+Want = Union[str, Sequence[Sequence[int]], None]
+
+
+class _Staging:
+    """Pinned host buffers for a step's integer metadata, used in rotation so that a buffer
+    is rewritten only after its copy to the device has finished."""
+
+    def __init__(self, device, depth: int = 4):
+        self.device = device
+        self.depth = depth
+        self.host: List[Optional[torch.Tensor]] = [None] * depth
+        self.events: List[Optional[torch.cuda.Event]] = [None] * depth
+        self.turn = 0
+
+    def next(self, n_ints: int) -> Tuple[torch.Tensor, int]:
+        i = self.turn
+        self.turn = (self.turn + 1) % self.depth
+        if self.events[i] is not None:
+            self.events[i].synchronize()
+        buf = self.host[i]
+        if buf is None or buf.numel() < n_ints:
+            buf = torch.empty(max(n_ints, 4096), dtype=torch.int32, pin_memory=True)
+            self.host[i] = buf
+        return buf, i
+
+    def sent(self, i: int) -> None:
+        ev = self.events[i] or torch.cuda.Event()
+        ev.record()
+        self.events[i] = ev
+
+
+class Engine:
+    """A model, its cache, and the step function over them."""
+
+    def __init__(self, model: Model, *, max_tokens: int, max_sequences: Optional[int] = None,
+                 max_seq_len: Optional[int] = None, poison_cache: bool = False):
+        if not model.loaded:
+            raise ValueError("the model has no weights yet (load() or load_random() first)")
+        B.require_device()
+        self.model = model
+        self.rt = model.rt
+        spec = model.spec
+        n_pages = -(-max_tokens // 64)
+        if max_sequences is None:
+            max_sequences = max(1, min(n_pages, 1024))
+        if max_seq_len is None:
+            max_seq_len = spec.max_position
+        self.cache = Cache(model.cache_requests(), max_tokens=max_tokens,
+                           max_seq_len=min(max_seq_len, spec.max_position),
+                           max_sequences=max_sequences, dtype=self.rt.dtype, device=self.rt.device,
+                           poison=poison_cache)
+        self._staging = _Staging(self.rt.device)
+        self._meta_dev: Optional[torch.Tensor] = None
+        self.steps_run = 0
+
+    # ---- sequences ------------------------------------------------------------------------
+    def open_sequence(self) -> int:
+        return self.cache.open_sequence()
+
+    def close_sequence(self, slot: int) -> None:
+        self.cache.close_sequence(slot)
+
+    def length(self, slot: int) -> int:
+        return self.cache.length(slot)
+
+    # ---- the step ---------------------------------------------------------------------------
+    def plan(self, entries: Sequence[Tuple[int, Sequence[int]]], want: Want):
+        """Host-side checks and the packed description of a step.  Launches nothing."""
+        spec = self.model.spec
+        if not entries:
+            raise StepError("a step needs at least one sequence")
+        slots = [int(s) for s, _ in entries]
+        if len(set(slots)) != len(slots):
+            raise StepError("a slot appears twice in one step")
+        q_lens, pos0 = [], []
+        for slot, toks in entries:
+            if len(toks) == 0:
+                raise StepError(f"slot {slot}: no tokens (an empty prompt cannot be run)")
+            try:
+                pos0.append(self.cache.length(slot))
+            except CacheError as e:
+                raise StepError(str(e)) from None
+            q_lens.append(len(toks))
+        if all(q == 1 for q in q_lens):
+            kind = "decode"
+        elif all(p == 0 for p in pos0):
+            kind = "prompt"
+        else:
+            raise StepError("the sequences of a step must all start at their first token or all "
+                            "bring exactly one token")
+        tokens = np.fromiter((t for _, toks in entries for t in toks), dtype=np.int64,
+                             count=sum(q_lens))
+        if tokens.size and (tokens.min() < 0 or tokens.max() >= spec.vocab_size):
+            bad = int(tokens[(tokens < 0) | (tokens >= spec.vocab_size)][0])
+            raise StepError(f"token id {bad} is outside the vocabulary [0, {spec.vocab_size})")
+        for slot, p, q in zip(slots, pos0, q_lens):
+            if p + q > self.cache.max_seq_len:
+                raise CacheFull(f"slot {slot}: {p + q} tokens exceed the longest sequence the cache "
+                                f"holds ({self.cache.max_seq_len})")
+        cu = np.zeros(len(entries) + 1, dtype=np.int64)
+        np.cumsum(q_lens, out=cu[1:])
+        rows: List[int] = []
+        if want is None or want == "none":
+            pass
+        elif want == "last":
+            rows = [int(c) - 1 for c in cu[1:]]
+        elif want == "all":
+            rows = list(range(int(cu[-1])))
+        else:
+            if len(want) != len(entries):
+                raise StepError("`want` needs one list of places per sequence")
+            for i, places in enumerate(want):
+                for p in places:
+                    if not 0 <= p < q_lens[i]:
+                        raise StepError(f"wanted place {p} is outside sequence {i}'s {q_lens[i]} tokens")
+                    rows.append(int(cu[i]) + int(p))
+        return kind, slots, q_lens, pos0, tokens, cu, rows
+
+    def step(self, entries: Sequence[Tuple[int, Sequence[int]]], want: Want = "last"
+             ) -> Optional[torch.Tensor]:
+        """Run one step.  `entries` = [(slot, tokens)]; `want` = "last", "all", "none"/None, or
+        for each sequence the places among its tokens whose logits are wanted.  Returns
+        float32 [wanted, vocab] on the device, in the order of the entries and of `want`."""
+        kind, slots, q_lens, pos0, tokens, cu, rows = self.plan(entries, want)
+        n, T, R = len(slots), int(cu[-1]), len(rows)
+        for slot, p, q in zip(slots, pos0, q_lens):
+            self.cache.reserve(slot, p + q)
+        self.cache.upload()
+
+        # packed metadata: cu_q | slot_ids | pos0 | tok_seq | tokens | logit_rows
+        o_cu, o_slot, o_pos = 0, n + 1, 2 * n + 1
+        o_seq, o_tok, o_rows = 3 * n + 1, 3 * n + 1 + T, 3 * n + 1 + 2 * T
+        total = o_rows + max(R, 1)
+        host, turn = self._staging.next(total)
+        h = host.numpy()
+        h[o_cu:o_cu + n + 1] = cu
+        h[o_slot:o_slot + n] = slots
+        h[o_pos:o_pos + n] = pos0
+        h[o_seq:o_seq + T] = np.repeat(np.arange(n, dtype=np.int32), q_lens)
+        h[o_tok:o_tok + T] = tokens
+        h[o_rows:o_rows + R] = rows
+        if self._meta_dev is None or self._meta_dev.numel() < total:
+            self._meta_dev = torch.empty(max(total, 4096), dtype=torch.int32, device=self.rt.device)
+        meta = self._meta_dev
+        meta[:total].copy_(host[:total], non_blocking=True)
+        self._staging.sent(turn)
+
+        base = meta.data_ptr()
+        batch = B.BatchView(cu_q=base + 4 * o_cu, slot_ids=base + 4 * o_slot, tok_seq=base + 4 * o_seq,
+                            pos0=base + 4 * o_pos, n_seqs=n, n_tokens=T)
+        ctx = StepContext(kind=kind, batch=batch, n_tokens=T, n_seqs=n, q_lens=q_lens, pos0=pos0,
+                          slots=slots, stream=B.stream_ptr(), rt=self.rt,
+                          slot_ids_dev=meta[o_slot:o_slot + n], pos0_dev=meta[o_pos:o_pos + n],
+                          cu_q_dev=meta[o_cu:o_cu + n + 1])
+        logits = self.model.forward(ctx, meta[o_tok:o_tok + T], self.cache,
+                                    meta[o_rows:o_rows + R] if R else None, R)
+        for slot, q in zip(slots, q_lens):
+            self.cache.advance(slot, q)
+        self.steps_run += 1
+        return logits
+
+    def check_device(self) -> None:
+        """Read the device error word (synchronises) and raise if a kernel set a bit."""
+        bits = int(self.rt.err.item())
+        if bits:
+            self.rt.err.zero_()
+            raise DeviceFault(B.describe_error_bits(bits))

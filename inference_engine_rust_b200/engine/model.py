@@ -1,0 +1,138 @@
+"""A model assembled from a `ModelSpec`: embedding table, one block per layer, final norm,
+output head; and its forward pass over the tokens of one step.
+
+Reference: the layer loop and the last-row logits of src/engine/runtime.rs:14-33,76-116,
+embedding of src/engine/embed.rs:104-138.  Differences on purpose: the loop follows the
+spec's schedule (a list of layer executions), and logits are produced for any wanted rows.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Mapping, Optional
+
+import torch
+
+from ..cache import CacheRequest
+from ..config.specs import ModelSpec
+from ..csrc import bindings as B
+from ..parts.base import Runtime, StepContext, part_class
+from ..parts.linear import Linear
+from ..weights.loader import (RandomSource, TensorSpec, WeightError, check_source, fetch)
+
+
+class Model:
+    def __init__(self, spec: ModelSpec, rt: Runtime):
+        spec.validate()
+        self.spec = spec
+        self.rt = rt
+        self.blocks = []
+        self._layer_parts = []       # (norm1, mixer, norm2, ffn) per layer
+        h = spec.hidden_size
+        for ls in spec.layers:
+            norm_cls = part_class("norm", ls.norm.kind)
+            norm1 = norm_cls(ls.norm, h, rt)
+            norm2 = norm_cls(ls.norm, h, rt)
+            mixer = part_class("mixer", ls.mixer.kind)(ls.mixer, rt)
+            ffn = part_class("ffn", ls.ffn.kind)(ls.ffn, rt)
+            block = part_class("block", ls.block.kind)(ls, norm1, mixer, norm2, ffn, rt)
+            self._layer_parts.append((norm1, mixer, norm2, ffn))
+            self.blocks.append(block)
+        self.final_norm = part_class("norm", spec.final_norm.kind)(spec.final_norm, h, rt)
+        self.embedding: Optional[torch.Tensor] = None
+        self.lm_head: Optional[Linear] = None
+        self.loaded = False
+
+    # ---- weights ------------------------------------------------------------------------
+    def expected_tensors(self) -> Dict[str, TensorSpec]:
+        """Every tensor name the model reads from a folder, with its shape."""
+        spec = self.spec
+        out: Dict[str, TensorSpec] = {
+            spec.embedding_name: TensorSpec((spec.vocab_size, spec.hidden_size)),
+            spec.final_norm_name: self.final_norm.tensor_specs()["weight"],
+        }
+        if spec.lm_head_name is not None:
+            out[spec.lm_head_name] = TensorSpec((spec.vocab_size, spec.hidden_size))
+        for ls, (norm1, mixer, norm2, ffn) in zip(spec.layers, self._layer_parts):
+            out[ls.mixer_norm_name] = norm1.tensor_specs()["weight"]
+            out[ls.ffn_norm_name] = norm2.tensor_specs()["weight"]
+            for local, ts in mixer.tensor_specs().items():
+                out[ls.mixer_prefix + local] = ts
+            for local, ts in ffn.tensor_specs().items():
+                out[ls.ffn_prefix + local] = ts
+        return out
+
+    def load(self, source, where: str = "weights") -> None:
+        """Check `source` against the expected tensors (one error for everything that is
+        wrong), then hand each part its tensors."""
+        expected = self.expected_tensors()
+        check_source(expected, source, where)
+        rt, spec = self.rt, self.spec
+
+        def get(name):
+            return fetch(source, name, rt.dtype, rt.device)
+
+        self.embedding = get(spec.embedding_name)
+        self.final_norm.load({"weight": get(spec.final_norm_name)})
+        head = self.embedding if spec.lm_head_name is None else get(spec.lm_head_name)
+        self.lm_head = Linear(head, rt)
+        if spec.lm_head_name is None and self.lm_head.weight.dtype == self.embedding.dtype:
+            self.embedding = self.lm_head.weight          # tied: one copy
+        for ls, (norm1, mixer, norm2, ffn) in zip(spec.layers, self._layer_parts):
+            norm1.load({"weight": get(ls.mixer_norm_name)})
+            norm2.load({"weight": get(ls.ffn_norm_name)})
+            mixer.load({local: get(ls.mixer_prefix + local) for local in mixer.tensor_specs()})
+            ffn.load({local: get(ls.ffn_prefix + local) for local in ffn.tensor_specs()})
+        self.loaded = True
+
+    def load_random(self, seed: int, std: float = 0.02, on_device: bool = False) -> None:
+        """Seeded random weights without a folder (`on_device` draws them on the GPU, for
+        models too large to make on the host in reasonable time)."""
+        src = RandomSource(self.expected_tensors(), seed, std, dtype=self.rt.dtype,
+                           device=self.rt.device if on_device else "cpu")
+        self.load(src, where="random weights")
+
+    # ---- cache ----------------------------------------------------------------------------
+    def cache_requests(self) -> Dict[int, CacheRequest]:
+        """What each cache-writing schedule entry asks of the cache, keyed by its position."""
+        out = {}
+        for pos, e in enumerate(self.spec.schedule):
+            if e.writes_cache:
+                out[pos] = self._layer_parts[e.layer][1].cache_request()
+        return out
+
+    def weight_bytes_per_step(self) -> int:
+        """Bytes of weights a one-token step reads: every matrix each scheduled layer uses,
+        the norm scales, the output head (the embedding rows it gathers are negligible)."""
+        total = self.lm_head.nbytes()
+        for e in self.spec.schedule:
+            norm1, mixer, norm2, ffn = self._layer_parts[e.layer]
+            for part in (mixer, ffn):
+                if hasattr(part, "weight_bytes"):
+                    total += part.weight_bytes()
+            for n in (norm1, norm2):
+                if getattr(n, "weight", None) is not None:
+                    total += n.weight.numel() * n.weight.element_size()
+        return total
+
+    # ---- forward --------------------------------------------------------------------------
+    def forward(self, ctx: StepContext, tokens: torch.Tensor, cache, logit_rows: Optional[torch.Tensor],
+                n_logit_rows: int, logits_out: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+        """Run the step's tokens through the scheduled layers.
+
+        tokens      int32 [n_tokens] on the device
+        logit_rows  int32 [n_logit_rows] on the device: packed-token rows whose logits are wanted
+        Returns float32 [n_logit_rows, vocab] (None when no row is wanted)."""
+        rt, spec, ws = self.rt, self.spec, self.rt.workspace
+        T, H = ctx.n_tokens, spec.hidden_size
+        x = ws.take("model.residual", (T, H), torch.float32)
+        B.embed_gather(self.embedding, tokens, x, spec.embedding_scale, rt.err, ctx.stream)
+        for pos, e in enumerate(spec.schedule):
+            view = cache.layer_view(spec.cache_entry(pos))
+            self.blocks[e.layer].forward(x, ctx, view, e.writes_cache)
+        if n_logit_rows == 0:
+            return None
+        hn = ws.take("model.head_in", (n_logit_rows, H), rt.dtype)
+        self.final_norm.forward(x, hn, ctx, rows_idx=logit_rows, rows=n_logit_rows)
+        if logits_out is None:
+            logits_out = torch.empty((n_logit_rows, spec.vocab_size), dtype=torch.float32, device=rt.device)
+        self.lm_head.apply(hn, logits_out, n_logit_rows, ctx.stream)
+        return logits_out

@@ -1,0 +1,170 @@
+"""Interfaces of the parts a layer is assembled from, the registry that maps a part's
+`kind` to its class, and the objects every part shares during a step.
+
+A part is built from its own `PartSpec` (sizes and constants) and a `Runtime`; it never
+learns which model it belongs to.  Adding a part means registering a class under a new
+kind; the configuration then names that kind for the layers that use it.
+
+    norm      Norm(spec, hidden_size, rt)        .forward(x_f32, out, ctx, rows_idx=None, rows=None)
+    position  PositionEncoding(spec, head_dim, rt)
+    mixer     Mixer(spec, rt)                    .forward(xn, residual, ctx, cache_view, writes_cache)
+    ffn       FeedForward(spec, rt)              .forward(xn, residual, ctx)
+    block     Block(layer_spec, norm1, mixer, norm2, ffn, rt)   .forward(x, ctx, cache_view, writes_cache)
+
+Mixers and feed-forwards ADD their result into `residual` (fp32, [tokens, hidden]): the
+residual sum stays in 32-bit and the last projection can fuse the addition.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Callable, Dict, Mapping, Optional, Tuple, Type
+
+import torch
+
+from ..cache import CacheRequest
+from ..config.specs import LayerSpec, PartSpec
+from ..weights.loader import TensorSpec
+
+_REGISTRY: Dict[Tuple[str, str], type] = {}
+CATEGORIES = ("norm", "position", "mixer", "ffn", "block")
+
+
+def register_part(category: str, kind: str, cls: type, *, replace: bool = False) -> None:
+    if category not in CATEGORIES:
+        raise ValueError(f"unknown part category {category!r}; categories: {CATEGORIES}")
+    if (category, kind) in _REGISTRY and not replace:
+        raise ValueError(f"{category} kind {kind!r} is already registered")
+    _REGISTRY[(category, kind)] = cls
+
+
+def unregister_part(category: str, kind: str) -> None:
+    _REGISTRY.pop((category, kind), None)
+
+
+def part_class(category: str, kind: str) -> type:
+    try:
+        return _REGISTRY[(category, kind)]
+    except KeyError:
+        known = sorted(k for c, k in _REGISTRY if c == category)
+        raise KeyError(f"no {category} of kind {kind!r} is registered; registered: {known}") from None
+
+
+class Workspace:
+    """Named scratch tensors that live as long as the workspace: a part that asks twice
+    under one name with sizes that fit gets the same memory, so steps allocate nothing once
+    warm (and captured graphs keep valid addresses)."""
+
+    def __init__(self, device):
+        self.device = device
+        self._bufs: Dict[str, torch.Tensor] = {}
+
+    def take(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= int(s)
+        nbytes = max(n * torch.empty((), dtype=dtype).element_size(), 16)
+        buf = self._bufs.get(name)
+        if buf is None or buf.numel() < nbytes:
+            buf = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+            self._bufs[name] = buf
+        return buf[:n * torch.empty((), dtype=dtype).element_size()].view(dtype).view(*shape)
+
+    def bytes(self) -> int:
+        return sum(b.numel() for b in self._bufs.values())
+
+
+@dataclass
+class Runtime:
+    """What all parts of one model share: the activation dtype, the device, whether only
+    the plain kernels may run, the device error word, and the workspace."""
+
+    dtype: torch.dtype                    # torch.bfloat16 or torch.float32
+    device: torch.device
+    plain_only: bool = False              # float32 always runs the plain (true 32-bit) kernels
+    err: Optional[torch.Tensor] = None    # int32[1] on the device, bits in csrc/common.cuh
+    workspace: Optional[Workspace] = None
+
+    def __post_init__(self):
+        self.device = torch.device(self.device)
+        if self.dtype not in (torch.bfloat16, torch.float32):
+            raise ValueError(f"run dtype must be bfloat16 or float32, got {self.dtype}")
+        if self.dtype == torch.float32:
+            self.plain_only = True
+        if self.err is None:
+            self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
+        if self.workspace is None:
+            self.workspace = Workspace(self.device)
+
+    @property
+    def fast(self) -> bool:
+        return not self.plain_only
+
+
+@dataclass
+class StepContext:
+    """The sequences of the running step as parts see them.
+
+    kind          "prompt": every sequence starts at position 0 with all its tokens;
+                  "decode": every sequence brings exactly one token
+    batch         csrc.bindings.BatchView (device arrays cu_q, slot_ids, tok_seq, pos0)
+    n_tokens      packed tokens, padding included;  n_seqs likewise
+    q_lens, pos0, slots   host copies (lists) for sizing launches and for host-side checks
+    """
+    kind: str
+    batch: object
+    n_tokens: int
+    n_seqs: int
+    q_lens: list
+    pos0: list
+    slots: list
+    stream: int
+    rt: Runtime
+    slot_ids_dev: Optional[torch.Tensor] = None   # int32 [n_seqs] view, for parts written in Python
+    pos0_dev: Optional[torch.Tensor] = None
+    cu_q_dev: Optional[torch.Tensor] = None
+
+    @property
+    def max_q_len(self) -> int:
+        return max(self.q_lens) if self.q_lens else 0
+
+    @property
+    def max_kv_len(self) -> int:
+        return max((p + q for p, q in zip(self.pos0, self.q_lens)), default=0)
+
+
+class Part:
+    """Common to all parts: which tensors it expects (local names) and how it takes them."""
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        return {}
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        if tensors:
+            raise ValueError(f"{type(self).__name__} takes no tensors, got {sorted(tensors)}")
+
+
+class Norm(Part):
+    def forward(self, x, out, ctx, rows_idx=None, rows=None) -> None:
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    pass
+
+
+class Mixer(Part):
+    def cache_request(self) -> CacheRequest:
+        return None
+
+    def forward(self, xn, residual, ctx: StepContext, cache_view, writes_cache: bool) -> None:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, xn, residual, ctx: StepContext) -> None:
+        raise NotImplementedError
+
+
+class Block(Part):
+    def forward(self, x, ctx: StepContext, cache_view, writes_cache: bool) -> None:
+        raise NotImplementedError

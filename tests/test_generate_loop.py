@@ -1,0 +1,121 @@
+"""Decisions of the generation loop, with a scripted engine in place of the device."""
+import pytest
+
+from inference_engine_rust_b200.engine.generate import generate, plan_batches, run_batch
+
+
+class ScriptedEngine:
+    """Stands where the engine stands.  'Logits' are the list of (slot, tokens so far)."""
+
+    def __init__(self, n_slots):
+        self.free = list(range(n_slots - 1, -1, -1))
+        self.held = {}
+        self.steps = []          # (kind, [(slot, n_tokens)])
+        self.opened = []
+
+    def open_sequence(self):
+        s = self.free.pop()
+        self.held[s] = []
+        self.opened.append(s)
+        return s
+
+    def close_sequence(self, slot):
+        assert slot in self.held, "closed twice"
+        del self.held[slot]
+        self.free.append(slot)
+
+    def step(self, entries, want="last"):
+        assert want == "last"
+        lens = [len(t) for _, t in entries]
+        first = all(len(self.held[s]) == 0 for s, _ in entries)
+        assert first or all(n == 1 for n in lens), "mixed step"
+        for s, t in entries:
+            self.held[s].extend(t)
+        self.steps.append(("prompt" if first and any(n > 1 for n in lens) else "decode", [(s, len(t)) for s, t in entries]))
+        return [(s, list(self.held[s])) for s, _ in entries]
+
+
+def scripted_sampler(script):
+    """script[request] = tokens it will be given, in order."""
+    calls = []
+
+    def sampler(logits, request_ids, steps):
+        calls.append((list(request_ids), list(steps)))
+        return [script[r][st] for r, st in zip(request_ids, steps)]
+    sampler.calls = calls
+    return sampler
+
+
+def test_stop_token_is_not_kept_and_shorter_sequences_end_earlier():
+    eng = ScriptedEngine(4)
+    script = {0: [10, 11, 2, 99], 1: [2], 2: [20, 21, 22, 23, 24]}
+    res = run_batch(eng, scripted_sampler(script), [[1, 5], [1, 6, 7], [1]], [0, 1, 2], 4, {2}, 100)
+    assert [r.tokens for r in res] == [[10, 11], [], [20, 21, 22, 23]]
+    assert [r.finish_reason for r in res] == ["stop", "stop", "length"]
+    assert eng.steps[0] == ("prompt", [(0, 2), (1, 3), (2, 1)])
+    assert [len(e) for _, e in eng.steps[1:]] == [2, 2, 1]           # batch shrinks; no step after the last token
+    assert not eng.held and sorted(eng.free) == [0, 1, 2, 3]
+
+
+def test_no_forward_after_the_last_kept_token():
+    eng = ScriptedEngine(1)
+    res = run_batch(eng, scripted_sampler({0: [5, 6, 7]}), [[1, 2, 3]], [0], 3, set(), 100)
+    assert res[0].tokens == [5, 6, 7] and len(eng.steps) == 3        # prompt + 2 decode steps
+
+
+def test_context_limit_ends_a_sequence():
+    eng = ScriptedEngine(1)
+    res = run_batch(eng, scripted_sampler({0: [5, 6, 7, 8, 9]}), [[1, 2, 3]], [0], 10, set(), 5)
+    assert res[0].finish_reason == "context" and res[0].tokens == [5, 6, 7]   # 3 + 2 positions run, third token has no room
+
+
+def test_zero_new_tokens_runs_nothing():
+    eng = ScriptedEngine(1)
+    res = run_batch(eng, scripted_sampler({}), [[1]], [0], 0, set(), 10)
+    assert res[0].tokens == [] and not eng.steps and not eng.opened
+
+
+def test_slots_come_back_when_a_step_fails():
+    class Failing(ScriptedEngine):
+        def step(self, entries, want="last"):
+            if self.steps:
+                raise RuntimeError("boom")
+            return super().step(entries, want)
+    eng = Failing(3)
+    with pytest.raises(RuntimeError):
+        run_batch(eng, scripted_sampler({0: [5, 5], 1: [6, 6]}), [[1], [1]], [0, 1], 5, set(), 100)
+    assert not eng.held and len(eng.free) == 3
+
+
+def test_plan_batches():
+    kw = dict(max_tokens=64 * 6, max_sequences=3, max_seq_len=256, page_tokens=64)
+    assert plan_batches([10, 10, 10, 10], 20, **kw) == [[0, 1, 2], [3]]              # slot bound
+    assert plan_batches([100, 100, 10], 60, **kw) == [[0, 1], [2]]                    # 192 + 192 = 384 tokens
+    assert plan_batches([10, 10, 10], 5, max_batch=2, **kw) == [[0, 1], [2]]
+    assert plan_batches([250], 100, **kw) == [[0]]                                    # capped by max_seq_len
+    for bad in ([0], [257]):
+        with pytest.raises(ValueError):
+            plan_batches(bad, 5, **kw)
+    with pytest.raises(ValueError):
+        plan_batches([200], 100, max_tokens=128, max_sequences=3, max_seq_len=256, page_tokens=64)
+
+
+def test_batches_one_after_another_reuse_slots_and_keep_order():
+    eng = ScriptedEngine(2)
+    script = {i: [30 + i, 40 + i, 2] for i in range(5)}
+    sampler = scripted_sampler(script)
+    res = generate(eng, sampler, [[1, i] for i in range(5)], 8, stop_ids=[2], max_tokens=64 * 2,
+                   max_sequences=2, max_seq_len=64, page_tokens=64)
+    assert [r.tokens for r in res] == [[30 + i, 40 + i] for i in range(5)]
+    assert [r.request for r in res] == list(range(5))
+    assert eng.opened == [0, 1, 1, 0, 0] or len(set(eng.opened)) == 2                 # two slots serve five requests
+    assert sampler.calls[0] == ([0, 1], [0, 0]) and sampler.calls[3] == ([2, 3], [0, 0])
+    assert not eng.held
+
+
+def test_request_ids_reach_the_sampler():
+    eng = ScriptedEngine(2)
+    sampler = scripted_sampler({7: [5], 9: [6]})
+    generate(eng, sampler, [[1], [1]], 1, max_tokens=128, max_sequences=2, max_seq_len=64, page_tokens=64,
+             request_ids=[7, 9])
+    assert sampler.calls == [([7, 9], [0, 0])]
