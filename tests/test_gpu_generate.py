@@ -1,0 +1,136 @@
+"""Generation through the Python entry point and the command line: greedy tokens equal the
+plain implementation's (whole sequence run again for every token), stop tokens, batches one
+after another, temperature sampling that does not depend on the batch."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from helpers import TINY, make_folder, plain_weights, prompts_for
+from plain import mistral_plain as P
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def loaded(tmp_path_factory):
+    from inference_engine_rust_b200 import LoadedModel
+    out = {}
+    root = tmp_path_factory.mktemp("gen")
+    for name in ("A", "B"):
+        folder = make_folder(root, TINY[name], seed=31, dtype="float32")
+        out[name] = (folder, LoadedModel.load(folder, dtype="float32"), plain_weights(folder))
+    return out
+
+
+@pytest.mark.parametrize("name,lengths,new", [("A", [5, 11, 23], 8), ("B", [1, 7, 19, 40], 12)])
+def test_greedy_equals_teacher_forcing(loaded, name, lengths, new):
+    folder, model, w = loaded[name]
+    cfg = TINY[name]
+    prompts = prompts_for(cfg, lengths, seed=3)
+    session = model.session(max_tokens=64 * 8, poison_cache=True)
+    got = session.generate(prompts, max_new_tokens=new, stop_ids=[])
+    want = [P.generate_greedy(cfg, w, p, new) for p in prompts]
+    assert got == want
+    session.engine.cache.check()
+    assert session.engine.cache.slots.free_count == session.engine.cache.n_slots
+
+
+def test_stop_tokens_and_batches_one_after_another(loaded):
+    folder, model, w = loaded["A"]
+    cfg = TINY["A"]
+    prompts = prompts_for(cfg, [9, 4, 30, 17, 2, 12, 6], seed=4)
+    free_run = [P.generate_greedy(cfg, w, p, 10) for p in prompts]
+    stop = {free_run[0][3], free_run[2][0], free_run[5][7]}
+    want = [P.generate_greedy(cfg, w, p, 10, stop_ids=stop) for p in prompts]
+    session = model.session(max_tokens=64 * 3, max_sequences=3, poison_cache=True)   # three slots for seven requests
+    res = session.generate(prompts, max_new_tokens=10, stop_ids=stop, full=True)
+    assert [r.tokens for r in res] == want
+    assert res[2].tokens == [] and res[2].finish_reason == "stop"
+    assert [r.finish_reason for r in res] == ["stop" if len(t) < 10 else "length" for t in want]
+    assert session.engine.steps_run > 3 * 1
+    session.engine.cache.check()
+
+
+def test_default_stop_is_the_configured_eos(loaded):
+    folder, model, w = loaded["B"]
+    cfg = TINY["B"]
+    p = prompts_for(cfg, [6], seed=8)[0]
+    free_run = P.generate_greedy(cfg, w, p, 6)
+    from inference_engine_rust_b200 import LoadedModel
+    cfg2 = dict(cfg, eos_token_id=free_run[2])
+    folder2 = os.path.join(os.path.dirname(folder), "eos_variant")
+    os.makedirs(folder2, exist_ok=True)
+    with open(os.path.join(folder2, "config.json"), "w") as f:
+        json.dump(cfg2, f)
+    if not os.path.exists(os.path.join(folder2, "model.safetensors")):
+        os.link(os.path.join(folder, "model.safetensors"), os.path.join(folder2, "model.safetensors"))
+    m2 = LoadedModel.load(folder2, dtype="float32")
+    assert m2.session(max_tokens=128).generate([p], max_new_tokens=6) == [free_run[:free_run.index(free_run[2])]]
+
+
+def test_temperature_sampling_is_per_request(loaded):
+    folder, model, w = loaded["A"]
+    cfg = TINY["A"]
+    prompts = prompts_for(cfg, [7, 3, 15], seed=5)
+    session = model.session(max_tokens=64 * 6)
+    together = session.generate(prompts, max_new_tokens=6, temperature=0.8, seed=99, stop_ids=[])
+    alone = [session.generate([p], max_new_tokens=6, temperature=0.8, seed=99, stop_ids=[], request_ids=[i])[0]
+             for i, p in enumerate(prompts)]
+    assert together == alone
+    other = session.generate(prompts, max_new_tokens=6, temperature=0.8, seed=100, stop_ids=[])
+    assert other != together
+    # each token follows the plain inverse-CDF rule for that request's draw
+    for i, (p, toks) in enumerate(zip(prompts, together)):
+        ids = list(p)
+        for step, tok in enumerate(toks):
+            logits = P.forward(cfg, w, ids)[-1]
+            cdf = P.temperature_cdf(logits, 0.8)
+            u = P.uniform_draw(99, i, step)
+            lo = float(cdf[tok - 1]) if tok > 0 else 0.0
+            assert lo - 1e-4 <= u <= float(cdf[tok]) + 1e-4
+            ids.append(tok)
+
+
+def test_session_calls_in_the_reference_manner(loaded):
+    folder, model, w = loaded["B"]
+    cfg = TINY["B"]
+    prompts = prompts_for(cfg, [4, 9], seed=6)
+    s = model.session(max_tokens=256)
+    logits = s.prefill(prompts)
+    host = s.logits_last_token(logits)
+    assert len(host) == 2 and len(host[0]) == cfg["vocab_size"]
+    nxt = [P.sample_greedy(r) for r in host]
+    assert nxt == [P.sample_greedy(P.forward(cfg, w, p)[-1].tolist()) for p in prompts]
+    logits = s.decode_tokens([nxt[0], None])          # the second sequence ends
+    ref = P.forward(cfg, w, prompts[0] + [nxt[0]])[-1]
+    assert torch.allclose(logits[0].cpu(), ref, atol=2e-4, rtol=2e-4)
+    with pytest.raises(RuntimeError):
+        s.prefill(prompts)
+    s.reset()
+    assert s.engine.cache.slots.held_count == 0
+    from inference_engine_rust_b200 import StepError
+    for bad in ([[]], [[cfg["vocab_size"]]], [[-1]]):
+        with pytest.raises(StepError):
+            s.prefill(bad)
+        assert s.engine.cache.slots.held_count == 0
+
+
+def test_command_line(loaded):
+    folder, model, w = loaded["A"]
+    cfg = TINY["A"]
+    p = prompts_for(cfg, [6], seed=7)[0]
+    want = P.generate_greedy(cfg, w, p, 5)
+    cmd = [sys.executable, "-m", "inference_engine_rust_b200", "-m", folder, "--dtype", "float32", "-n", "5",
+           "--stop-token", "-1", " ".join(map(str, p))]
+    out = subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr
+    assert out.stdout.strip().split() == [str(t) for t in want]
+    out = subprocess.run(cmd[:-1], cwd=ROOT, input=",".join(map(str, p)) + "\n", capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0 and out.stdout.strip().split() == [str(t) for t in want]
+    bad = subprocess.run(cmd[:-1] + [""], cwd=ROOT, capture_output=True, text=True, timeout=300)
+    assert bad.returncode != 0 and "prompt" in bad.stderr.lower()

@@ -1,0 +1,301 @@
+"""Each part of a layer alone against the plain implementation, and the generality of the
+assembly: a toy mixer with state of its own, defined here, is registered, built and stepped
+without a change to the package; a layer is run twice; a layer reads another layer's
+cache; layers of one model use different mixers."""
+import math
+from dataclasses import dataclass
+
+import pytest
+import torch
+
+from helpers import compare
+from plain import mistral_plain as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def runtime(dtype=torch.float32):
+    from inference_engine_rust_b200.parts.base import Runtime
+    return Runtime(dtype=dtype, device=DEV)
+
+
+def context(rt, q_lens, pos0, slots, kind):
+    """A StepContext over explicit sequences (what Engine.step builds from its entries)."""
+    import numpy as np
+    from inference_engine_rust_b200.csrc import bindings as B
+    from inference_engine_rust_b200.parts.base import StepContext
+    n, T = len(q_lens), sum(q_lens)
+    cu = np.zeros(n + 1, dtype=np.int32)
+    cu[1:] = np.cumsum(q_lens)
+    arrs = [torch.tensor(a, dtype=torch.int32, device=DEV) for a in
+            (cu, slots, np.repeat(np.arange(n, dtype=np.int32), q_lens), pos0)]
+    view = B.BatchView(cu_q=arrs[0].data_ptr(), slot_ids=arrs[1].data_ptr(), tok_seq=arrs[2].data_ptr(),
+                       pos0=arrs[3].data_ptr(), n_seqs=n, n_tokens=T)
+    ctx = StepContext(kind=kind, batch=view, n_tokens=T, n_seqs=n, q_lens=list(q_lens), pos0=list(pos0),
+                      slots=list(slots), stream=B.stream_ptr(), rt=rt, slot_ids_dev=arrs[1], pos0_dev=arrs[3],
+                      cu_q_dev=arrs[0])
+    ctx._keep = arrs
+    return ctx
+
+
+def spec(kind, **params):
+    from inference_engine_rust_b200.config.specs import PartSpec
+    return PartSpec(kind, params)
+
+
+# ---------------------------------------------------------------------------------------
+# parts alone
+
+
+def test_norm_part():
+    from inference_engine_rust_b200.parts import part_class
+    rt = runtime()
+    norm = part_class("norm", "rmsnorm")(spec("rmsnorm", eps=3e-4), 88, rt)
+    assert norm.tensor_specs()["weight"].shape == (88,)
+    w = torch.rand(88) + 0.5
+    norm.load({"weight": w.to(DEV)})
+    x = torch.randn(6, 88) * 2
+    out = torch.empty(6, 88, device=DEV)
+    norm.forward(x.to(DEV), out, context(rt, [6], [0], [0], "prompt"))
+    compare(out, P.rmsnorm(x, w, 3e-4), "float32", "rmsnorm part")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_feed_forward_part(dtype):
+    from inference_engine_rust_b200.parts import part_class
+    tdt = torch.float32 if dtype == "float32" else torch.bfloat16
+    rt = runtime(tdt)
+    ffn = part_class("ffn", "swiglu")(spec("swiglu", hidden_size=88, intermediate_size=200), rt)
+    torch.manual_seed(0)
+    w = {n: (torch.randn(s.shape) * 0.1).to(tdt) for n, s in ffn.tensor_specs().items()}
+    ffn.load({n: t.to(DEV) for n, t in w.items()})
+    x = torch.randn(9, 88).to(tdt)
+    res = torch.randn(9, 88)
+    res_dev = res.to(DEV)
+    ffn.forward(x.to(DEV), res_dev, context(rt, [9], [0], [0], "prompt"))
+    rnd = P.bf16_rounding if dtype == "bfloat16" else P.no_rounding
+    ref = res + P.ffn_layer(x.float(), w["gate_proj.weight"].float(), w["up_proj.weight"].float(),
+                            w["down_proj.weight"].float(), rnd)
+    compare(res_dev, ref, dtype, "swiglu part adds into the residual")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("heads,kvh,hd,window,pairing,rotary", [
+    (4, 2, 16, 16, "half", 16), (6, 1, 32, None, "interleaved", 32), (3, 3, 48, 70, "half", 32)])
+def test_attention_part_prompt_then_decode(dtype, heads, kvh, hd, window, pairing, rotary):
+    """The mixer alone: two prompts of unequal lengths in one step, then three single tokens
+    each, against the plain attention of the whole sequences."""
+    from inference_engine_rust_b200.cache import Cache
+    from inference_engine_rust_b200.parts import part_class
+    tdt = torch.float32 if dtype == "float32" else torch.bfloat16
+    rt = runtime(tdt)
+    H, theta = 72, 5000.0
+    pos = spec("rope", theta=theta, rotary_dim=rotary, pairing=pairing)
+    attn = part_class("mixer", "attention")(
+        spec("attention", hidden_size=H, heads=heads, kv_heads=kvh, head_dim=hd, window=window,
+             scale=1 / math.sqrt(hd), position=pos), rt)
+    torch.manual_seed(1)
+    w = {n: (torch.randn(s.shape) * 0.15).to(tdt) for n, s in attn.tensor_specs().items()}
+    attn.load({n: t.to(DEV) for n, t in w.items()})
+    cache = Cache({0: attn.cache_request()}, max_tokens=64 * 8, max_seq_len=512, max_sequences=2,
+                  dtype=tdt, device=DEV, poison=True)
+    lens, extra = [90, 7], 3
+    xs = [torch.randn(n + extra, H).to(tdt) for n in lens]
+    rnd = P.bf16_rounding if dtype == "bfloat16" else P.no_rounding
+    refs = [P.attention_layer(x.float(), *(w[k + "_proj.weight"].float() for k in "qkvo"), heads=heads,
+                              kv_heads=kvh, head_dim=hd, rope_theta=theta, window=window, pairing=pairing,
+                              rotary_dim=rotary, rnd=rnd) for x in xs]
+    slots = [cache.open_sequence() for _ in lens]
+    for s, n in zip(slots, lens):
+        cache.reserve(s, n + extra)
+    cache.upload()
+    xn = torch.cat([x[:n] for x, n in zip(xs, lens)]).to(DEV)
+    res = torch.zeros(sum(lens), H, device=DEV)
+    attn.forward(xn, res, context(rt, lens, [0, 0], slots, "prompt"), cache.layer_view(0), True)
+    compare(res, torch.cat([r[:n] for r, n in zip(refs, lens)]), dtype, "attention part, prompts")
+    for k in range(extra):
+        xn = torch.stack([x[n + k] for x, n in zip(xs, lens)]).to(DEV)
+        res = torch.zeros(2, H, device=DEV)
+        attn.forward(xn, res, context(rt, [1, 1], [n + k for n in lens], slots, "decode"), cache.layer_view(0), True)
+        compare(res, torch.stack([r[n + k] for r, n in zip(refs, lens)]), dtype, f"attention part, decode {k}")
+    assert rt.err.item() == 0
+
+
+def test_rope_part_constants():
+    from inference_engine_rust_b200.parts import part_class
+    rt = runtime()
+    rope = part_class("position", "rope")(spec("rope", theta=1e6, rotary_dim=32, pairing="half"), 32, rt)
+    want = torch.tensor([1e6 ** (-2 * k / 32) for k in range(16)], dtype=torch.float64).float()
+    assert torch.equal(rope.inv_freq.cpu(), want)
+    scaled = part_class("position", "rope")(spec("rope", theta=1e6, rotary_dim=32, pairing="interleaved",
+                                                 freq_factors=[2.0] * 16), 32, rt)
+    assert torch.allclose(scaled.inv_freq.cpu(), want / 2) and scaled.pairing != rope.pairing
+    for bad in (dict(rotary_dim=34), dict(rotary_dim=15), dict(pairing="odd")):
+        with pytest.raises(ValueError):
+            part_class("position", "rope")(spec("rope", **{"theta": 1e4, "rotary_dim": 32, "pairing": "half", **bad}), 32, rt)
+
+
+# ---------------------------------------------------------------------------------------
+# a toy architecture, defined here: layer 0 = attention, layer 1 = a mixer with state of its
+# own (running mean of its inputs over the sequence, then a projection)
+
+
+class RunningMeanMixer:
+    """y_t = W . mean(x_0 .. x_t).  Its per-sequence state is the running sum [hidden]."""
+
+    def __init__(self, part_spec, rt):
+        from inference_engine_rust_b200.parts.linear import Linear
+        self.rt, self.hidden = rt, int(part_spec["hidden_size"])
+        self.Linear = Linear
+        self.proj = None
+
+    def tensor_specs(self):
+        from inference_engine_rust_b200.weights import TensorSpec
+        return {"proj.weight": TensorSpec((self.hidden, self.hidden))}
+
+    def load(self, tensors):
+        self.proj = self.Linear(tensors["proj.weight"], self.rt)
+
+    def cache_request(self):
+        from inference_engine_rust_b200.cache import StateRequest
+        return StateRequest((self.hidden,), torch.float32)
+
+    def weight_bytes(self):
+        return self.proj.nbytes()
+
+    def forward(self, xn, residual, ctx, cache_view, writes_cache):
+        state = cache_view.state                       # [n_slots, hidden]
+        means = torch.empty(ctx.n_tokens, self.hidden, device=xn.device, dtype=torch.float32)
+        t = 0
+        for slot, p0, q in zip(ctx.slots, ctx.pos0, ctx.q_lens):
+            sums = state[slot] + torch.cumsum(xn[t:t + q].float(), dim=0)
+            counts = torch.arange(p0 + 1, p0 + q + 1, device=xn.device, dtype=torch.float32)
+            means[t:t + q] = sums / counts[:, None]
+            state[slot] = sums[-1]
+            t += q
+        self.proj.apply(means.to(self.rt.dtype), residual, ctx.n_tokens, ctx.stream, add_residual=True)
+
+
+@dataclass(frozen=True)
+class ToyConfig:
+    hidden_size: int
+    vocab_size: int
+    schedule: tuple            # ((layer, reads_cache_of), ...)
+    architecture: str = "ToyForCausalLM"
+
+    @classmethod
+    def from_dict(cls, raw):
+        return cls(raw["hidden_size"], raw["vocab_size"], tuple(tuple(e) for e in raw["schedule"]))
+
+
+def toy_spec(cfg: ToyConfig):
+    from inference_engine_rust_b200.config.specs import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+    H = cfg.hidden_size
+    norm = PartSpec("rmsnorm", {"eps": 1e-5})
+    attn = PartSpec("attention", {"hidden_size": H, "heads": 4, "kv_heads": 2, "head_dim": 16, "window": None,
+                                  "scale": 0.25, "position": PartSpec("rope", {"theta": 1e4, "rotary_dim": 16, "pairing": "half"})})
+    mean = PartSpec("running_mean", {"hidden_size": H})
+    ffn = PartSpec("swiglu", {"hidden_size": H, "intermediate_size": 96})
+    layers = []
+    for i, mixer in enumerate((attn, mean, attn)):
+        p = f"toy.{i}."
+        layers.append(LayerSpec(block=PartSpec("prenorm", {}), norm=norm, mixer=mixer, ffn=ffn, mixer_prefix=p + "mix.",
+                                ffn_prefix=p + "ffn.", mixer_norm_name=p + "n1.weight", ffn_norm_name=p + "n2.weight"))
+    return ModelSpec(architecture=cfg.architecture, hidden_size=H, vocab_size=cfg.vocab_size, layers=tuple(layers),
+                     schedule=tuple(ScheduleEntry(l, r) for l, r in cfg.schedule), final_norm=norm,
+                     embedding_name="toy.embed.weight", final_norm_name="toy.norm.weight", lm_head_name=None,
+                     embedding_scale=2.0, max_position=256, bos_token_id=None, eos_token_id=None)
+
+
+@pytest.fixture(scope="module")
+def toy_registered():
+    from inference_engine_rust_b200.config import registry
+    from inference_engine_rust_b200.parts import register_part, unregister_part
+    register_part("mixer", "running_mean", RunningMeanMixer)
+    registry.register_architecture("ToyForCausalLM", ToyConfig, toy_spec)
+    yield
+    unregister_part("mixer", "running_mean")
+    registry._ARCHITECTURES.pop("ToyForCausalLM", None)
+
+
+def plain_toy(cfg: ToyConfig, w, ids):
+    """The toy model, whole sequence, from the plain parts."""
+    x = P.embed(w["toy.embed.weight"], ids, 2.0)
+    kv = {}
+    for pos, (layer, reads) in enumerate(cfg.schedule):
+        p = f"toy.{layer}."
+        xn = P.rmsnorm(x, w[p + "n1.weight"], 1e-5)
+        if layer == 1:
+            mean = torch.cumsum(xn, 0) / torch.arange(1, len(ids) + 1)[:, None]
+            x = x + P.matmul(mean, w[p + "mix.proj.weight"])
+        else:
+            a = dict(heads=4, kv_heads=2, head_dim=16, rope_theta=1e4, window=None, scale=0.25)
+            y, parts = P.attention_layer(xn, *(w[p + f"mix.{k}_proj.weight"] for k in "qkvo"), return_parts=True, **a)
+            if reads is None:
+                kv[pos] = parts
+            else:                      # queries of this layer over the keys and values of entry `reads`
+                q, src, T = parts["q"], kv[reads], len(ids)
+                out = torch.zeros(T, 4, 16)
+                mask = torch.tril(torch.ones(T, T, dtype=torch.bool))
+                for h in range(4):
+                    s = (q[:, h] @ src["k"][:, h // 2].t()) * 0.25
+                    out[:, h] = P.softmax(s.masked_fill(~mask, float("-inf"))) @ src["v"][:, h // 2]
+                y = P.matmul(out.reshape(T, 64), w[p + "mix.o_proj.weight"])
+            x = x + y
+        xn = P.rmsnorm(x, w[p + "n2.weight"], 1e-5)
+        x = x + P.ffn_layer(xn, w[p + "ffn.gate_proj.weight"], w[p + "ffn.up_proj.weight"], w[p + "ffn.down_proj.weight"])
+    return P.matmul(P.rmsnorm(x, w["toy.norm.weight"], 1e-5), w["toy.embed.weight"])
+
+
+@pytest.mark.parametrize("schedule", [
+    ((0, None), (1, None)),                          # attention, then the stateful toy mixer
+    ((0, None), (1, None), (0, None), (1, None)),    # both layers run twice, each run with a cache of its own
+    ((0, None), (1, None), (2, 0)),                  # layer 2 reads the cache that entry 0 wrote
+])
+def test_toy_architecture_is_registered_built_and_stepped(toy_registered, schedule):
+    from inference_engine_rust_b200 import LoadedModel
+    from inference_engine_rust_b200.weights import RandomSource
+    raw = {"architectures": ["ToyForCausalLM"], "hidden_size": 64, "vocab_size": 97, "schedule": [list(e) for e in schedule]}
+    model = LoadedModel.random(raw, seed=4, dtype="float32", std=0.1)
+    cfg = model.config
+    src = RandomSource(model.model.expected_tensors(), 4, 0.1, dtype=torch.float32)
+    w = {n: src.get(n) for n in src.names()}
+    used = {e[0] for e in schedule}
+    assert ("toy.1.mix.proj.weight" in w) and ("toy.0.mix.q_proj.weight" in w)
+    eng = model.session(max_tokens=64 * 6, poison_cache=True).engine
+    kinds = sorted(type(g).__name__ for g in eng.cache.kv_groups + eng.cache.state_groups)
+    assert kinds == ["KVGroup", "StateGroup"]
+    n_kv = sum(1 for l, r in schedule if l != 1 and r is None)
+    assert sum(len(g.layers) for g in eng.cache.kv_groups) == n_kv
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, 97, (n,), generator=g).tolist() for n in (37, 5, 70)]
+    want = [plain_toy(cfg, w, p) for p in prompts]
+    # whole; then in a batch with the last tokens one by one; slots are used again in between
+    for p, ref in zip(prompts, want):
+        s = eng.open_sequence()
+        compare(eng.step([(s, p)], want="all"), ref, "float32", "toy model, whole")
+        eng.close_sequence(s)
+    slots = [eng.open_sequence() for _ in prompts]
+    tails = [4, 2, 6]
+    got = [[] for _ in prompts]
+    out = eng.step([(s, p[:len(p) - t]) for s, p, t in zip(slots, prompts, tails)], want="all")
+    at = 0
+    for i, (p, t) in enumerate(zip(prompts, tails)):
+        got[i].append(out[at:at + len(p) - t])
+        at += len(p) - t
+    for k in range(max(tails)):
+        live = [i for i in range(3) if tails[i] > k]
+        out = eng.step([(slots[i], [prompts[i][len(prompts[i]) - tails[i] + k]]) for i in live], want="last")
+        for r, i in enumerate(live):
+            got[i].append(out[r:r + 1])
+    eng.check_device()
+    for i in range(3):
+        compare(torch.cat(got[i]), want[i], "float32", f"toy model, request {i} batched and decoded")
+
+
+def test_unknown_part_kind_is_named(toy_registered):
+    from inference_engine_rust_b200.parts import part_class
+    with pytest.raises(KeyError) as e:
+        part_class("mixer", "convolution")
+    assert "attention" in str(e.value) and "running_mean" in str(e.value)
