@@ -82,15 +82,24 @@ def _declare(lib) -> None:
         "iert_sample_greedy": [P, c_int, c_int, c_longlong, P, P, S],
         "iert_sample_temperature": [P, c_int, c_int, c_longlong, c_float, c_ulonglong, P, P, P, P, S],
         "iert_uniform_draws": [c_ulonglong, P, P, P, c_int, S],
+        "iert_gemm_tc": [P, c_longlong, P, c_longlong, P, c_int, c_longlong, c_int, c_int, c_int, c_int,
+                         P, c_longlong, P, c_int, c_int, c_int, c_int, P, S],
     }
+    lib.iert_gemm_tc_workspace_bytes.restype = c_longlong
+    lib.iert_gemm_tc_counter_count.restype = c_int
     for name, args in sigs.items():
         fn = getattr(lib, name)
         fn.argtypes = args
         fn.restype = c_int
 
 
+launch_count = 0        # launcher calls that returned success since import (one kernel each)
+
+
 def check(status: int, what: str) -> None:
+    global launch_count
     if status == 0:
+        launch_count += 1
         return
     if status == 1:
         raise KernelError(f"{what}: the kernel does not take these sizes or options")
@@ -194,3 +203,38 @@ def uniform_draws(seed: int, request_ids, step_ids, out, stream) -> None:
     check(core().iert_uniform_draws(seed & 0xFFFFFFFFFFFFFFFF, request_ids.data_ptr(),
                                     step_ids.data_ptr(), out.data_ptr(), out.numel(), stream),
           "uniform_draws")
+
+
+class GemmScratch:
+    """Scratch memory and ticket counters of the tensor-core projection's split-K path, shared
+    by every launch on one stream of one device."""
+
+    _by_device = {}
+
+    def __init__(self, device):
+        lib = core()
+        self.ws = torch.empty(lib.iert_gemm_tc_workspace_bytes(), dtype=torch.uint8, device=device)
+        self.counters = torch.zeros(lib.iert_gemm_tc_counter_count(), dtype=torch.int32, device=device)
+
+    @classmethod
+    def get(cls, device) -> "GemmScratch":
+        key = str(torch.device(device))
+        if key not in cls._by_device:
+            cls._by_device[key] = cls(device)
+        return cls._by_device[key]
+
+
+def gemm_tc(x, w, out, M: int, mode: int, err, stream, force_bt: int = 0, force_splits: int = 0,
+            force_stages: int = 0) -> bool:
+    """out[:M] (=|+=) x[:M] @ w.T on the tensor cores (bf16 operands).  Returns False, having
+    launched nothing, when the operands do not meet the kernel's alignment rules."""
+    N, K = w.shape
+    sc = GemmScratch.get(x.device)
+    status = core().iert_gemm_tc(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(),
+                                 dtype_code(out.dtype), out.stride(0), M, N, K, mode, sc.ws.data_ptr(),
+                                 sc.ws.numel(), sc.counters.data_ptr(), sc.counters.numel(), force_bt,
+                                 force_splits, force_stages, err.data_ptr(), stream)
+    if status == 1:
+        return False
+    check(status, "gemm_tc")
+    return True

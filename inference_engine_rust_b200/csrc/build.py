@@ -34,6 +34,7 @@ NVCC_FLAGS = [
 # the model's sizes; kernels specialised on a size are separate libraries made on demand.
 CORE_SOURCES = [
     "runtime.cu", "elementwise.cu", "gemm_plain.cu", "attention_plain.cu", "sampling.cu",
+    "gemm_tc.cu",
 ]
 HEADERS = ["common.cuh"]
 

@@ -1,0 +1,404 @@
+// Tensor-core projection for sm_100a: out[t, n] = sum_k x[t, k] * w[n, k] with bf16 operands
+// and fp32 accumulation, on tcgen05.mma with the accumulator in tensor memory and both
+// operands brought into shared memory by TMA (128-byte swizzle).
+//
+// The weight matrix sits on the MMA's M side (128 weight rows per tile) and the tokens on its
+// N side (16..256 per tile), so one kernel serves a prompt of thousands of tokens and a
+// decoding step of a few: with few tokens the tile is a thin slab of the weight matrix and
+// the kernel is a stream of TMA loads at memory bandwidth.  Persistent CTAs walk a list of
+// (tile, k-split) work items.  Warp 0 issues the TMA loads, warp 1 issues the MMAs, warps
+// 2-5 read the accumulator back (each its quarter of the TMEM lanes) and write the result;
+// two accumulators in TMEM let the read-back of one tile overlap the MMAs of the next.
+//
+// Split-K (few tokens, few tiles): each split writes its fp32 partial tile to scratch memory
+// and takes a ticket; the CTA that draws the last ticket adds the partials in split order
+// (a fixed order: the result does not depend on which CTA finishes last) and writes the
+// output.  No CTA ever waits for another.
+//
+// Every wait on an mbarrier is bounded; when one runs out the kernel sets
+// IERT_ERR_WAIT_EXPIRED in the error word, drains its own TMA copies, frees its TMEM and
+// returns.
+#include "common.cuh"
+#include "sm100.cuh"
+
+#include <mutex>
+#include <unordered_map>
+
+using namespace iert;
+using namespace sm100;
+
+namespace {
+
+constexpr int TILE_N = 128;        // weight rows per tile (UMMA M)
+constexpr int TILE_K = 64;         // bf16 elements per k-block: one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 192;
+constexpr int W_STAGE_BYTES = TILE_N * TILE_K * 2;
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+
+enum : int { MODE_STORE = 0, MODE_ADD_RESIDUAL = 1 };
+
+struct GemmParams {
+  void* out;
+  long long ldo;
+  int out_dtype;
+  int mode;
+  int M, N, K;
+  int t_tiles, n_tiles, splits, kb_total, kb_per_split, stages;
+  float* ws;          // [tiles][splits][BT][TILE_N] fp32 partials (splits > 1)
+  int* counters;      // [tiles] tickets, zero between launches
+  int* err;
+};
+
+__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 255u) == 255u && *abort_flag) return false;
+  }
+  return false;
+}
+
+template <typename TO>
+__device__ __forceinline__ void write_out(const GemmParams& p, int tok, int n, float v) {
+  TO* o = (TO*)p.out + (long long)tok * p.ldo + n;
+  if (p.mode == MODE_ADD_RESIDUAL) *o = from_f32<TO>(to_f32(*o) + v);
+  else *o = from_f32<TO>(v);
+}
+__device__ __forceinline__ void write_out_any(const GemmParams& p, int tok, int n, float v) {
+  if (p.out_dtype == IERT_F32) write_out<float>(p, tok, n, v);
+  else write_out<__nv_bfloat16>(p, tok, n, v);
+}
+
+template <int BT>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+               const GemmParams p) {
+  constexpr int STAGE_BYTES = W_STAGE_BYTES + BT * TILE_K * 2;
+  constexpr uint32_t ACC_COLS = 2 * BT < 32 ? 32 : 2 * BT;      // two accumulators, power of two >= 32
+  constexpr uint32_t IDESC = instr_desc_bf16(TILE_N, BT);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const int stages = p.stages;
+  uint64_t* full = (uint64_t*)(smem + (size_t)stages * STAGE_BYTES);
+  uint64_t* empty = full + stages;
+  uint64_t* acc_full = empty + stages;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+  int* ticket_s = (int*)(tmem_slot + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 128); }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&map_w);
+    tma_prefetch_desc(&map_x);
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, ACC_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int total_work = p.n_tiles * p.t_tiles * p.splits;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int stage = 0, issued = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int work = blockIdx.x; ok && work < total_work; work += gridDim.x) {
+        const int split = work % p.splits, tile = work / p.splits;
+        const int n0 = (tile / p.t_tiles) * TILE_N, t0 = (tile % p.t_tiles) * BT;
+        const int kb0 = split * p.kb_per_split, kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!wait_or_abort(&empty[stage], phase ^ 1, abort_flag)) { ok = false; break; }
+          uint8_t* ws_ = smem + (size_t)stage * STAGE_BYTES;
+          mbar_expect_tx(&full[stage], STAGE_BYTES);
+          tma_load_2d(ws_, &map_w, &full[stage], kb * TILE_K, n0);
+          tma_load_2d(ws_ + W_STAGE_BYTES, &map_x, &full[stage], kb * TILE_K, t0);
+          ++issued;
+          if (++stage == stages) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        if (!*abort_flag) atomicOr(p.err, IERT_ERR_WAIT_EXPIRED);
+        *abort_flag = 1;
+        // drain: the copies already issued land whether or not anyone consumes them
+        int s = stage;
+        uint32_t ph = phase;
+        for (int i = 0; i < min(issued, stages); ++i) {
+          if (s == 0) { s = stages; ph ^= 1; }
+          --s;
+          mbar_wait(&full[s], ph, WAIT_LIMIT);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool ok = true;
+      for (int work = blockIdx.x; ok && work < total_work; work += gridDim.x) {
+        const int split = work % p.splits;
+        const int kb0 = split * p.kb_per_split, kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+        if (!wait_or_abort(&acc_empty[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BT);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!wait_or_abort(&full[stage], phase, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t w_addr = smem_addr(smem + (size_t)stage * STAGE_BYTES);
+          const uint64_t da = smem_desc_k128(w_addr), db = smem_desc_k128(w_addr + W_STAGE_BYTES);
+#pragma unroll
+          for (int ks = 0; ks < TILE_K / UMMA_K; ++ks)   // 32 bytes further along K per step
+            umma_bf16(d_tmem, da + 2 * ks, db + 2 * ks, IDESC, (kb > kb0 || ks > 0) ? 1u : 0u);
+          umma_commit(&empty[stage]);
+          if (++stage == stages) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(&acc_full[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
+      if (!ok) {
+        if (!*abort_flag) atomicOr(p.err, IERT_ERR_WAIT_EXPIRED);
+        *abort_flag = 1;
+      }
+    }
+  } else {
+    // ---------------- epilogue: 4 warps, warp w reads TMEM lanes 32*(w%4).. ----------------
+    const int q = warp & 3;
+    const int n_local = q * 32 + lane;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int work = blockIdx.x; ok && work < total_work; work += gridDim.x) {
+      const int split = work % p.splits, tile = work / p.splits;
+      const int n0 = (tile / p.t_tiles) * TILE_N, t0 = (tile % p.t_tiles) * BT;
+      const int n = n0 + n_local;
+      const int t_valid = min(BT, p.M - t0);
+      if (!wait_or_abort(&acc_full[acc], acc_phase, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BT);
+      float* part = p.splits > 1 ? p.ws + ((size_t)(tile * p.splits + split) * BT) * TILE_N + n_local : nullptr;
+#pragma unroll 1
+      for (int c = 0; c < BT; c += 16) {
+        if (c >= t_valid) break;                     // warp-uniform
+        float v[16];
+        tmem_ld16(taddr + c, v);
+        if (part) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if (c + j < t_valid) part[(size_t)(c + j) * TILE_N] = v[j];
+        } else if (n < p.N) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if (c + j < t_valid) write_out_any(p, t0 + c + j, n, v[j]);
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&acc_empty[acc]);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+
+      if (part) {
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (threadIdx.x == 64) *ticket_s = atomicAdd(&p.counters[tile], 1);
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (*ticket_s == p.splits - 1) {             // the last split of this tile: add in split order
+          __threadfence();
+          if (n < p.N) {
+            const float* base = p.ws + ((size_t)tile * p.splits * BT) * TILE_N + n_local;
+            for (int t = 0; t < t_valid; ++t) {
+              float sum = 0.f;
+              for (int s = 0; s < p.splits; ++s) sum += __ldcg(base + ((size_t)s * BT + t) * TILE_N);
+              write_out_any(p, t0 + t, n, sum);
+            }
+          }
+          if (threadIdx.x == 64) p.counters[tile] = 0;
+        }
+      }
+    }
+    if (!ok && lane == 0) {
+      if (!*abort_flag) atomicOr(p.err, IERT_ERR_WAIT_EXPIRED);
+      *abort_flag = 1;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, ACC_COLS);
+  }
+}
+
+// ---- host side ----------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)sym;
+  });
+  return fn;
+}
+
+struct MapKey {
+  const void* ptr; long long rows, cols, ld; int box_rows;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = (size_t)k.ptr;
+    h = h * 1000003u ^ (size_t)k.rows;
+    h = h * 1000003u ^ (size_t)k.cols;
+    h = h * 1000003u ^ (size_t)k.ld;
+    return h * 1000003u ^ (size_t)k.box_rows;
+  }
+};
+
+// A bf16 row-major matrix [rows, cols] with row stride ld, loaded in boxes of box_rows x 64.
+bool tensor_map(const void* ptr, long long rows, long long cols, long long ld, int box_rows, CUtensorMap* out) {
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  static std::mutex mu;
+  MapKey key{ptr, rows, cols, ld, box_rows};
+  std::lock_guard<std::mutex> g(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) { *out = it->second; return true; }
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)TILE_K, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMap m;
+  CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return false;
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, m);
+  *out = m;
+  return true;
+}
+
+int sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return n;
+}
+
+template <int BT>
+int launch(const CUtensorMap& mw, const CUtensorMap& mx, GemmParams p, int grid, cudaStream_t stream) {
+  constexpr int STAGE_BYTES = W_STAGE_BYTES + BT * TILE_K * 2;
+  const size_t smem = (size_t)p.stages * STAGE_BYTES + 1024 + 256;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_tc_kernel<BT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess)
+      return iert_check_launch("gemm_tc attribute");
+    configured = true;
+  }
+  gemm_tc_kernel<BT><<<grid, THREADS, smem, stream>>>(mw, mx, p);
+  return iert_check_launch("gemm_tc");
+}
+
+}  // namespace
+
+// Bytes of scratch and number of ticket counters a caller should provide.
+IERT_API long long iert_gemm_tc_workspace_bytes() { return 48ll << 20; }
+IERT_API int iert_gemm_tc_counter_count() { return 8192; }
+
+// x: [M, K] bf16, row stride ldx; w: [N, K] bf16, row stride ldw; out: [M, N] of out_dtype, row
+// stride ldo.  mode 0 stores, mode 1 adds into out.  K, ldx and ldw must be multiples of 8
+// and the pointers 16-byte aligned (TMA); otherwise IERT_BAD_ARGUMENT is returned and nothing
+// is launched.  ws / counters: scratch for split-K, shared by all launches on one stream;
+// counters must be zero before the first launch.  force_*: 0 = choose.
+IERT_API int iert_gemm_tc(const void* x, long long ldx, const void* w, long long ldw, void* out, int out_dtype,
+                          long long ldo, int M, int N, int K, int mode, float* ws, long long ws_bytes,
+                          int* counters, int n_counters, int force_bt, int force_splits, int force_stages,
+                          int* err, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return IERT_OK;
+  if (K <= 0 || (K & 7) || (ldx & 7) || (ldw & 7) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15))
+    return IERT_BAD_ARGUMENT;
+  if (mode != MODE_STORE && mode != MODE_ADD_RESIDUAL) return IERT_BAD_ARGUMENT;
+  if (out_dtype != IERT_F32 && out_dtype != IERT_BF16) return IERT_BAD_ARGUMENT;
+  if (mode == MODE_ADD_RESIDUAL && out_dtype != IERT_F32) return IERT_BAD_ARGUMENT;
+
+  int bt = force_bt;
+  if (!bt) bt = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+  if (bt != 16 && bt != 32 && bt != 64 && bt != 128 && bt != 256) return IERT_BAD_ARGUMENT;
+
+  GemmParams p;
+  p.out = out; p.ldo = ldo; p.out_dtype = out_dtype; p.mode = mode;
+  p.M = M; p.N = N; p.K = K;
+  p.n_tiles = (N + TILE_N - 1) / TILE_N;
+  p.t_tiles = (M + bt - 1) / bt;
+  p.kb_total = (K + TILE_K - 1) / TILE_K;
+  p.ws = ws; p.counters = counters; p.err = err;
+  const int tiles = p.n_tiles * p.t_tiles;
+  const int stage_bytes = W_STAGE_BYTES + bt * TILE_K * 2;
+  const int ctas_per_sm = bt <= 64 ? 2 : 1;
+  const int slots = sm_count() * ctas_per_sm;
+  const int smem_budget = (ctas_per_sm == 2 ? 113 : 226) * 1024 - 2048;
+  int stages = force_stages ? force_stages : smem_budget / stage_bytes;
+  if (stages > 12) stages = 12;
+  if (stages < 2 || (size_t)stages * stage_bytes + 1280 > 227 * 1024) return IERT_BAD_ARGUMENT;
+  p.stages = stages;
+
+  int splits = 1;
+  if (force_splits) {
+    splits = force_splits;
+  } else if (tiles * 2 <= slots) {
+    splits = slots / tiles;
+    const int max_by_k = p.kb_total / 4 > 0 ? p.kb_total / 4 : 1;     // at least 4 k-blocks per split
+    if (splits > max_by_k) splits = max_by_k;
+    if (splits > 16) splits = 16;
+  }
+  if (splits < 1) splits = 1;
+  if (splits > p.kb_total) splits = p.kb_total;
+  p.kb_per_split = (p.kb_total + splits - 1) / splits;
+  splits = (p.kb_total + p.kb_per_split - 1) / p.kb_per_split;        // no empty split
+  if (splits > 1) {
+    const long long need = (long long)tiles * splits * bt * TILE_N * 4;
+    if (!ws || !counters || need > ws_bytes || tiles > n_counters) {
+      if (force_splits) return IERT_BAD_ARGUMENT;
+      splits = 1;
+      p.kb_per_split = p.kb_total;
+    }
+  }
+  p.splits = splits;
+
+  CUtensorMap mw, mx;
+  if (!tensor_map(w, N, K, ldw, TILE_N, &mw) || !tensor_map(x, M, K, ldx, bt, &mx)) return IERT_BAD_ARGUMENT;
+  const int total_work = tiles * splits;
+  const int grid = total_work < slots ? total_work : slots;
+  switch (bt) {
+    case 16: return launch<16>(mw, mx, p, grid, stream);
+    case 32: return launch<32>(mw, mx, p, grid, stream);
+    case 64: return launch<64>(mw, mx, p, grid, stream);
+    case 128: return launch<128>(mw, mx, p, grid, stream);
+    default: return launch<256>(mw, mx, p, grid, stream);
+  }
+}

@@ -61,11 +61,44 @@ class _Staging:
         self.events[i] = ev
 
 
+class _DecodeGraph:
+    """A captured one-token step for `nb` sequences: its own metadata buffer, workspace and
+    logits buffer (a graph replays fixed addresses), and the graph."""
+
+    def __init__(self, engine: "Engine", nb: int):
+        rt, model = engine.rt, engine.model
+        from ..parts.base import Workspace
+        _, o_slot, _, o_seq, o_tok, o_rows, total = Engine._layout(nb, nb, nb)
+        self.meta = torch.zeros(total, dtype=torch.int32, device=rt.device)
+        self.meta[o_slot:o_slot + nb] = -1            # all padding until a step fills it in
+        self.meta[o_seq:o_seq + nb] = -1
+        self.meta[0:nb + 1] = torch.arange(nb + 1, dtype=torch.int32)
+        self.meta[o_rows:o_rows + nb] = torch.arange(nb, dtype=torch.int32)
+        self.logits = torch.empty((nb, model.spec.vocab_size), dtype=torch.float32, device=rt.device)
+        self.ws = Workspace(rt.device)
+        self.graph = torch.cuda.CUDAGraph()
+        saved = rt.workspace
+        rt.workspace = self.ws
+        try:
+            def run():
+                ctx = engine._context("decode", self.meta, nb, nb, [1] * nb, [0] * nb, [-1] * nb)
+                model.forward(ctx, self.meta[o_tok:o_tok + nb], engine.cache,
+                              self.meta[o_rows:o_rows + nb], nb, logits_out=self.logits)
+            run()                                      # eager once: lazy set-up happens outside the capture
+            torch.cuda.synchronize()
+            before = B.launch_count
+            with torch.cuda.graph(self.graph):
+                run()
+            self.launches = B.launch_count - before    # kernels one replay launches
+        finally:
+            rt.workspace = saved
+
+
 class Engine:
     """A model, its cache, and the step function over them."""
 
     def __init__(self, model: Model, *, max_tokens: int, max_sequences: Optional[int] = None,
-                 max_seq_len: Optional[int] = None, poison_cache: bool = False):
+                 max_seq_len: Optional[int] = None, poison_cache: bool = False, use_graphs: bool = True):
         if not model.loaded:
             raise ValueError("the model has no weights yet (load() or load_random() first)")
         B.require_device()
@@ -84,6 +117,12 @@ class Engine:
         self._staging = _Staging(self.rt.device)
         self._meta_dev: Optional[torch.Tensor] = None
         self.steps_run = 0
+        self.h2d_bytes_last_step = 0
+        self.graph_launches = 0        # kernels launched by graph replays so far
+        # one-token steps replay captured graphs when every part of the model says that its
+        # forward depends on the step only through device memory
+        self.use_graphs = use_graphs and model.graph_safe()
+        self._graphs = {}
 
     # ---- sequences ------------------------------------------------------------------------
     def open_sequence(self) -> int:
@@ -158,11 +197,36 @@ class Engine:
         for slot, p, q in zip(slots, pos0, q_lens):
             self.cache.reserve(slot, p + q)
         self.cache.upload()
+        if kind == "decode" and self.use_graphs and R in (0, n) and rows == list(range(R)):
+            logits = self._step_graph(slots, pos0, tokens, R)
+        else:
+            logits = self._step_eager(kind, slots, q_lens, pos0, tokens, cu, rows)
+        for slot, q in zip(slots, q_lens):
+            self.cache.advance(slot, q)
+        self.steps_run += 1
+        return logits
 
-        # packed metadata: cu_q | slot_ids | pos0 | tok_seq | tokens | logit_rows
+    @staticmethod
+    def _layout(n: int, T: int, R: int):
+        """Offsets of cu_q | slot_ids | pos0 | tok_seq | tokens | logit_rows in the packed
+        integer metadata of a step, and its total length."""
         o_cu, o_slot, o_pos = 0, n + 1, 2 * n + 1
         o_seq, o_tok, o_rows = 3 * n + 1, 3 * n + 1 + T, 3 * n + 1 + 2 * T
-        total = o_rows + max(R, 1)
+        return o_cu, o_slot, o_pos, o_seq, o_tok, o_rows, o_rows + max(R, 1)
+
+    def _context(self, kind, meta, n, T, q_lens, pos0, slots) -> StepContext:
+        o_cu, o_slot, o_pos, o_seq, o_tok, o_rows, _ = self._layout(n, T, 0)
+        base = meta.data_ptr()
+        batch = B.BatchView(cu_q=base + 4 * o_cu, slot_ids=base + 4 * o_slot, tok_seq=base + 4 * o_seq,
+                            pos0=base + 4 * o_pos, n_seqs=n, n_tokens=T)
+        return StepContext(kind=kind, batch=batch, n_tokens=T, n_seqs=n, q_lens=q_lens, pos0=pos0,
+                           slots=slots, stream=B.stream_ptr(), rt=self.rt,
+                           slot_ids_dev=meta[o_slot:o_slot + n], pos0_dev=meta[o_pos:o_pos + n],
+                           cu_q_dev=meta[o_cu:o_cu + n + 1])
+
+    def _step_eager(self, kind, slots, q_lens, pos0, tokens, cu, rows):
+        n, T, R = len(slots), int(cu[-1]), len(rows)
+        o_cu, o_slot, o_pos, o_seq, o_tok, o_rows, total = self._layout(n, T, R)
         host, turn = self._staging.next(total)
         h = host.numpy()
         h[o_cu:o_cu + n + 1] = cu
@@ -176,20 +240,42 @@ class Engine:
         meta = self._meta_dev
         meta[:total].copy_(host[:total], non_blocking=True)
         self._staging.sent(turn)
+        self.h2d_bytes_last_step = total * 4
+        ctx = self._context(kind, meta, n, T, q_lens, pos0, slots)
+        return self.model.forward(ctx, meta[o_tok:o_tok + T], self.cache,
+                                  meta[o_rows:o_rows + R] if R else None, R)
 
-        base = meta.data_ptr()
-        batch = B.BatchView(cu_q=base + 4 * o_cu, slot_ids=base + 4 * o_slot, tok_seq=base + 4 * o_seq,
-                            pos0=base + 4 * o_pos, n_seqs=n, n_tokens=T)
-        ctx = StepContext(kind=kind, batch=batch, n_tokens=T, n_seqs=n, q_lens=q_lens, pos0=pos0,
-                          slots=slots, stream=B.stream_ptr(), rt=self.rt,
-                          slot_ids_dev=meta[o_slot:o_slot + n], pos0_dev=meta[o_pos:o_pos + n],
-                          cu_q_dev=meta[o_cu:o_cu + n + 1])
-        logits = self.model.forward(ctx, meta[o_tok:o_tok + T], self.cache,
-                                    meta[o_rows:o_rows + R] if R else None, R)
-        for slot, q in zip(slots, q_lens):
-            self.cache.advance(slot, q)
-        self.steps_run += 1
-        return logits
+    # ---- one-token steps as replayed CUDA graphs ---------------------------------------------
+    def _step_graph(self, slots, pos0, tokens, R):
+        """A one-token step through a captured graph.  Batches are padded to the next power of
+        two with sequences whose slot is -1: kernels skip them, so padding changes no result.
+        The graph writes its logits into a buffer of its own; the caller gets a copy."""
+        n = len(slots)
+        nb = 1
+        while nb < n:
+            nb *= 2
+        g = self._graphs.get(nb)
+        if g is None:
+            g = self._graphs[nb] = _DecodeGraph(self, nb)
+        o_cu, o_slot, o_pos, o_seq, o_tok, o_rows, total = self._layout(nb, nb, nb)
+        host, turn = self._staging.next(total)
+        h = host.numpy()
+        h[o_cu:o_cu + nb + 1] = np.arange(nb + 1)
+        h[o_slot:o_slot + nb] = -1
+        h[o_slot:o_slot + n] = slots
+        h[o_pos:o_pos + nb] = 0
+        h[o_pos:o_pos + n] = pos0
+        h[o_seq:o_seq + nb] = -1
+        h[o_seq:o_seq + n] = np.arange(n)
+        h[o_tok:o_tok + nb] = 0
+        h[o_tok:o_tok + n] = tokens
+        h[o_rows:o_rows + nb] = np.arange(nb)
+        g.meta[:total].copy_(host[:total], non_blocking=True)
+        self._staging.sent(turn)
+        self.h2d_bytes_last_step = total * 4
+        g.graph.replay()
+        self.graph_launches += g.launches
+        return g.logits[:n].clone() if R else None
 
     def check_device(self) -> None:
         """Read the device error word (synchronises) and raise if a kernel set a bit."""

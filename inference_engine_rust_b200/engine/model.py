@@ -99,6 +99,15 @@ class Model:
                 out[pos] = self._layer_parts[e.layer][1].cache_request()
         return out
 
+    def graph_safe(self) -> bool:
+        """True when every part declares `graph_safe`: its forward reads the step's sequences
+        from device memory only, so a captured launch sequence stays right for later steps."""
+        parts = [self.final_norm]
+        for e in self.spec.schedule:
+            parts.extend(self._layer_parts[e.layer])
+            parts.append(self.blocks[e.layer])
+        return all(getattr(p, "graph_safe", False) for p in parts)
+
     def weight_bytes_per_step(self) -> int:
         """Bytes of weights a one-token step reads: every matrix each scheduled layer uses,
         the norm scales, the output head (the embedding rows it gathers are negligible)."""

@@ -27,6 +27,8 @@ from .linear import Linear
 
 
 class Attention(Mixer):
+    graph_safe = True
+
     def __init__(self, spec, rt: Runtime):
         self.rt = rt
         self.hidden_size = int(spec["hidden_size"])

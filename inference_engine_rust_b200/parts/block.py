@@ -7,6 +7,8 @@ from .base import Block, Runtime, StepContext, register_part
 
 
 class PreNormBlock(Block):
+    graph_safe = True
+
     def __init__(self, layer_spec, norm1, mixer, norm2, ffn, rt: Runtime):
         self.norm1, self.mixer, self.norm2, self.ffn, self.rt = norm1, mixer, norm2, ffn, rt
 

@@ -1,11 +1,18 @@
 """Dispatch of a projection to the tcgen05 tensor-core kernel."""
 from __future__ import annotations
 
+import torch
+
+from ..csrc import bindings as B
+
 
 def apply(linear, x, out, n_rows: int, mode: int, stream: int) -> bool:
-    """Run the tensor-core product if it takes these operands; False means the caller
-    runs the plain kernel."""
-    return False
+    """Run the tensor-core product if it takes these operands (bf16, K and row strides
+    multiples of 8, 16-byte aligned); False means nothing was launched and the caller runs the
+    plain kernel."""
+    if x.dtype != torch.bfloat16 or linear.weight.dtype != torch.bfloat16:
+        return False
+    return B.gemm_tc(x, linear.weight, out, n_rows, mode, linear.rt.err, stream)
 
 
 def apply_gated(linear, x, act, n_rows: int, stream: int) -> bool:

@@ -12,6 +12,8 @@ from .base import Norm, Runtime, register_part
 
 
 class RMSNorm(Norm):
+    graph_safe = True
+
     def __init__(self, spec, hidden_size: int, rt: Runtime):
         self.eps = float(spec["eps"])
         self.hidden_size = hidden_size

@@ -15,6 +15,8 @@ from .linear import Linear
 
 
 class SwiGLU(FeedForward):
+    graph_safe = True
+
     def __init__(self, spec, rt: Runtime):
         self.rt = rt
         self.hidden_size = int(spec["hidden_size"])

@@ -1,0 +1,97 @@
+"""The tensor-core projection alone against a float64 product of the same bf16 operands:
+token counts from 1 to several tiles, widths that are no multiple of the tile, forced tile
+widths, split-K with its in-kernel reduction, and pipelines shorter than the k loop."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def run(M, N, K, mode, out_dtype, **force):
+    from inference_engine_rust_b200.csrc import bindings as B
+    g = torch.Generator(device=DEV).manual_seed(M * 1000003 + N * 1009 + K)
+    x = (torch.randn(M, K, device=DEV, generator=g)).bfloat16()
+    w = (torch.randn(N, K, device=DEV, generator=g) * 0.5).bfloat16()
+    ref = (x.double() @ w.double().t())
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    if mode == B.GEMM_ADD_RESIDUAL:
+        out = torch.randn(M, N, device=DEV, generator=g)
+        ref = ref + out.double()
+    else:
+        out = torch.full((M, N), float("nan"), device=DEV, dtype=out_dtype)
+    ok = B.gemm_tc(x, w, out, M, mode, err, B.stream_ptr(), **force)
+    assert ok, "the kernel refused operands it should take"
+    torch.cuda.synchronize()
+    assert err.item() == 0, B.describe_error_bits(err.item())
+    # fp32 accumulation in another order: absolute error of the order of 1e-6 * |terms| summed;
+    # a bf16 result adds one rounding, at most 2^-8 relative to the value itself
+    scale = (K ** 0.5) * 0.5
+    bound = 2e-3 * scale + (2.0 ** -8) * ref.abs() * (out.dtype == torch.bfloat16)
+    diff = (out.double() - ref).abs()
+    assert torch.isfinite(out).all() and bool((diff <= bound).all()), \
+        f"M={M} N={N} K={K} {force}: max diff {diff.max().item():.4g}"
+    return out
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 128, 64), (8, 256, 512), (16, 384, 4096), (37, 331, 88), (64, 1000, 200),
+                                   (100, 512, 1024), (200, 130, 72), (300, 640, 520), (700, 256, 256)])
+def test_shapes(M, N, K):
+    from inference_engine_rust_b200.csrc import bindings as B
+    run(M, N, K, B.GEMM_STORE, torch.bfloat16)
+    run(M, N, K, B.GEMM_STORE, torch.float32)
+    run(M, N, K, B.GEMM_ADD_RESIDUAL, torch.float32)
+
+
+@pytest.mark.parametrize("bt", [16, 32, 64, 128, 256])
+def test_every_tile_width(bt):
+    from inference_engine_rust_b200.csrc import bindings as B
+    run(bt + 3, 300, 392, B.GEMM_STORE, torch.float32, force_bt=bt)
+    run(5, 200, 136, B.GEMM_STORE, torch.bfloat16, force_bt=bt)
+
+
+@pytest.mark.parametrize("splits", [2, 3, 7, 16])
+def test_split_k_is_exact_and_repeatable(splits):
+    from inference_engine_rust_b200.csrc import bindings as B
+    a = run(9, 520, 2048, B.GEMM_STORE, torch.float32, force_splits=splits)
+    b = run(9, 520, 2048, B.GEMM_STORE, torch.float32, force_splits=splits)
+    assert torch.equal(a, b), "split-K must add its partials in a fixed order"
+    run(40, 200, 1096, B.GEMM_ADD_RESIDUAL, torch.float32, force_splits=splits)
+    run(3, 4096, 1024, B.GEMM_STORE, torch.bfloat16, force_splits=splits)      # more work items than CTAs
+
+
+def test_short_pipelines_wrap():
+    from inference_engine_rust_b200.csrc import bindings as B
+    run(24, 300, 4096, B.GEMM_STORE, torch.float32, force_stages=2)
+    run(130, 1100, 2048, B.GEMM_STORE, torch.float32, force_stages=3)          # several tiles per CTA
+
+
+def test_many_tiles_per_cta():
+    from inference_engine_rust_b200.csrc import bindings as B
+    run(1500, 4096, 256, B.GEMM_STORE, torch.bfloat16)                         # 32 x 6 tiles on 148 CTAs
+    run(33, 40000, 128, B.GEMM_STORE, torch.float32)                           # 313 thin tiles
+
+
+def test_refuses_what_tma_cannot_load():
+    from inference_engine_rust_b200.csrc import bindings as B
+    x = torch.randn(4, 100, device=DEV).bfloat16()
+    w = torch.randn(64, 100, device=DEV).bfloat16()
+    out = torch.empty(4, 64, device=DEV)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    assert B.gemm_tc(x, w, out, 4, B.GEMM_STORE, err, B.stream_ptr()) is False     # K = 100 is no multiple of 8
+
+
+def test_row_results_do_not_depend_on_the_batch():
+    """A token's projection is the same alone, among 7 others, and in a prompt of hundreds,
+    up to the rounding of split-K partial sums."""
+    from inference_engine_rust_b200.csrc import bindings as B
+    g = torch.Generator(device=DEV).manual_seed(1)
+    x = torch.randn(300, 1024, device=DEV, generator=g).bfloat16()
+    w = torch.randn(768, 1024, device=DEV, generator=g).bfloat16()
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    outs = []
+    for M in (1, 8, 300):
+        out = torch.empty(M, 768, device=DEV)
+        assert B.gemm_tc(x, w, out, M, B.GEMM_STORE, err, B.stream_ptr())
+        outs.append(out[0].clone())
+    assert torch.allclose(outs[0], outs[1], atol=1e-3, rtol=1e-4) and torch.allclose(outs[0], outs[2], atol=1e-3, rtol=1e-4)
