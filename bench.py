@@ -105,6 +105,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the configuration (reported)")
     ap.add_argument("--points", default="1,64", help="other decode batch sizes to report, comma separated ('' = none)")
     ap.add_argument("--no-prefill", action="store_true")
+    ap.add_argument("--context", type=int, default=CONTEXT, help="tokens each sequence holds when decoding starts")
     a = ap.parse_args()
 
     if a.impl == "reference":
@@ -131,7 +132,7 @@ def main() -> int:
     load_s = time.time() - t0
     batches = [a.batch] + [int(b) for b in a.points.split(",") if b.strip()]
     biggest = max(batches)
-    per_seq = -(-(CONTEXT + a.steps + a.warmup + 8) // 64) * 64
+    per_seq = -(-(a.context + a.steps + a.warmup + 8) // 64) * 64
     session = model.session(max_tokens=biggest * per_seq, max_sequences=biggest, max_seq_len=MAX_CONTEXT)
     eng = session.engine
     sampler = Sampler(SamplingParams(temperature=0.0), eng.rt.err)
@@ -144,7 +145,7 @@ def main() -> int:
         slots = []
         for _ in range(n):
             s = eng.open_sequence()
-            eng.step([(s, rng.integers(0, vocab, CONTEXT).tolist())], want=None)
+            eng.step([(s, rng.integers(0, vocab, a.context).tolist())], want=None)
             slots.append(s)
         torch.cuda.synchronize()
         return slots
@@ -245,7 +246,7 @@ def main() -> int:
                    "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
                    "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
                    "intermediate": cfg["intermediate_size"], "vocab": vocab, "sliding_window": cfg["sliding_window"],
-                   "global_batch": a.batch, "seq_len": CONTEXT, "max_context": MAX_CONTEXT,
+                   "global_batch": a.batch, "seq_len": a.context, "max_context": MAX_CONTEXT,
                    "prefill_tokens": PREFILL_TOKENS, "parallelism": "single GPU",
                    "l2": "inputs larger than L2 (weights read per step exceed 126 MB many times)",
                    "peaks": pk["source"]},

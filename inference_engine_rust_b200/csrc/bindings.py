@@ -85,6 +85,10 @@ def _declare(lib) -> None:
         "iert_gemm_tc": [P, c_longlong, P, c_longlong, P, c_int, c_longlong, c_int, c_int, c_int, c_int,
                          P, c_longlong, P, c_int, c_int, c_int, c_int, P, S],
     }
+    lib.iert_attention_decode.argtypes = [P, P, POINTER(BatchView), POINTER(KvView), c_int, c_float, c_int, P, P, S]
+    lib.iert_attention_decode.restype = c_int
+    lib.iert_attention_decode_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
+    lib.iert_attention_decode_scratch_floats.restype = c_longlong
     lib.iert_gemm_tc_workspace_bytes.restype = c_longlong
     lib.iert_gemm_tc_counter_count.restype = c_int
     for name, args in sigs.items():
@@ -237,4 +241,50 @@ def gemm_tc(x, w, out, M: int, mode: int, err, stream, force_bt: int = 0, force_
     if status == 1:
         return False
     check(status, "gemm_tc")
+    return True
+
+
+def attention_decode_scratch_floats(n_tokens: int, heads: int, head_dim: int, splits: int) -> int:
+    return core().iert_attention_decode_scratch_floats(n_tokens, heads, head_dim, splits)
+
+
+def attention_decode(qkv, out, batch: BatchView, kv: KvView, heads: int, scale: float, splits: int,
+                     scratch, err, stream) -> bool:
+    """Split-KV decode attention (bf16 cache).  Returns False, having launched nothing, when
+    the kernel does not take the cache's geometry."""
+    status = core().iert_attention_decode(qkv.data_ptr(), out.data_ptr(), byref(batch), byref(kv), heads,
+                                          scale, splits, scratch.data_ptr(), err.data_ptr(), stream)
+    if status == 1:
+        return False
+    check(status, "attention_decode")
+    global launch_count
+    launch_count += 1          # the combine pass
+    return True
+
+
+_prefill_libs = {}
+
+
+def attention_prefill(qkv, out, batch: BatchView, heads: int, kv_heads: int, head_dim: int, window: int,
+                      scale: float, max_q_len: int, stream) -> bool:
+    """Flash prompt attention (bf16) over the step's own keys and values.  The kernel is
+    compiled per head size (multiples of 16 up to 256) the first time it is needed; other
+    head sizes return False and nothing is launched."""
+    if head_dim % 16 or not 16 <= head_dim <= 256:
+        return False
+    lib = _prefill_libs.get(head_dim)
+    if lib is None:
+        lib = build.load_library(*build.prefill_attention_library(head_dim))
+        lib.iert_attention_prefill.argtypes = [c_void_p, c_void_p, POINTER(BatchView), c_int, c_int, c_int,
+                                               c_float, c_int, c_void_p]
+        lib.iert_attention_prefill.restype = c_int
+        _prefill_libs[head_dim] = lib
+    status = lib.iert_attention_prefill(qkv.data_ptr(), out.data_ptr(), byref(batch), heads, kv_heads,
+                                        window, scale, max_q_len, stream)
+    if status == 1:
+        return False
+    if status != 0:
+        raise KernelError("attention_prefill: the launch failed")
+    global launch_count
+    launch_count += 1
     return True

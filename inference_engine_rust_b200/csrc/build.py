@@ -34,7 +34,7 @@ NVCC_FLAGS = [
 # the model's sizes; kernels specialised on a size are separate libraries made on demand.
 CORE_SOURCES = [
     "runtime.cu", "elementwise.cu", "gemm_plain.cu", "attention_plain.cu", "sampling.cu",
-    "gemm_tc.cu",
+    "gemm_tc.cu", "attention_decode.cu",
 ]
 HEADERS = ["common.cuh"]
 
@@ -164,8 +164,20 @@ def load_library(name: str, sources: Sequence[str], defines: Sequence[str] = ())
         return lib
 
 
+# Head sizes whose prompt-attention library is built ahead of time by build_all(); any other
+# multiple of 16 up to 256 is compiled the first time a model with that head size runs.
+PREBUILT_HEAD_DIMS = (16, 32, 48, 64, 128)
+
+
+def prefill_attention_library(head_dim: int):
+    """(name, sources, defines) of the prompt-attention library for one head size."""
+    return f"iert_attn_prefill_hd{head_dim}", ["attention_prefill.cu"], [f"HEAD_DIM={head_dim}"]
+
+
 def build_all(verbose: bool = True) -> List[str]:
-    """Every library the package can need that does not depend on a model's sizes, plus
-    the size-specialised ones for the sizes listed in `SPECIALISED_DEFAULTS`."""
+    """Every library the package can need that does not depend on a model's sizes, plus the
+    size-specialised ones for the head sizes in `PREBUILT_HEAD_DIMS`."""
     paths = [build_library("iert_core", CORE_SOURCES, verbose=verbose)]
+    for hd in PREBUILT_HEAD_DIMS:
+        paths.append(build_library(*prefill_attention_library(hd), verbose=verbose))
     return paths

@@ -1,7 +1,36 @@
 """Dispatch of attention to the fast kernels (flash prompt attention, split-KV decode)."""
 from __future__ import annotations
 
+import torch
+
+from ..csrc import bindings as B
+
+_TARGET_CTAS = 6 * 148           # several resident CTAs per SM: the kernel hides latency by occupancy
+_MAX_SPLITS = 16
+
+
+def decode_splits(n_tokens: int, kv_heads: int, group: int) -> int:
+    """How many ways the keys of each sequence are split: enough CTAs to fill the GPU at
+    small batches, one split once the batch alone does.  Depends on the (padded) batch size
+    only, never on the sequences' lengths, so a captured graph stays valid."""
+    gt = 8 if group >= 8 else 4 if group > 2 else group
+    slices = -(-group // gt)
+    ctas = max(1, n_tokens * kv_heads * slices)
+    return max(1, min(_MAX_SPLITS, -(-_TARGET_CTAS // ctas)))
+
 
 def apply(attn, qkv, out, ctx, cache_view, from_cache: bool) -> bool:
     """Run a fast kernel if one takes this case; False means the caller runs the plain one."""
+    rt = attn.rt
+    if qkv.dtype != torch.bfloat16:
+        return False
+    if ctx.kind == "decode":
+        splits = decode_splits(ctx.n_tokens, attn.kv_heads, attn.heads // attn.kv_heads)
+        n = B.attention_decode_scratch_floats(ctx.n_tokens, attn.heads, attn.head_dim, splits)
+        scratch = rt.workspace.take("attn.decode_scratch", (n,), torch.float32)
+        return B.attention_decode(qkv, out, ctx.batch, cache_view.struct, attn.heads, attn.scale, splits,
+                                  scratch, rt.err, ctx.stream)
+    if not from_cache:
+        return B.attention_prefill(qkv, out, ctx.batch, attn.heads, attn.kv_heads, attn.head_dim,
+                                   attn.window or 0, attn.scale, ctx.max_q_len, ctx.stream)
     return False

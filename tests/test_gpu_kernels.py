@@ -249,6 +249,61 @@ def test_attention_plain_prompt_and_cache(heads, kvh, hd, window, dtype):
         ref = _plain_attention(y[r:r + 1, :heads], k_all, v_all, heads, kvh, scale, window)
         got = out1[r].float().cpu().view(1, heads, hd)
         assert torch.allclose(got, ref, atol=tol, rtol=tol), f"decode after {q_lens[r]}"
+    if dtype == torch.bfloat16:
+        # the split-KV kernel against its plain sibling, for several ways of splitting the keys
+        for splits in (1, 3, 16):
+            n = b.attention_decode_scratch_floats(3, heads, hd, splits)
+            scratch = torch.full((n,), float("nan"), device=DEV)
+            fast = torch.full_like(out1, float("nan"))
+            assert b.attention_decode(nxt, fast, view1, cache.layer_view(0).struct, heads, scale, splits,
+                                      scratch, err, stream())
+            assert err.item() == 0
+            assert torch.allclose(fast.float(), out1.float(), atol=tol, rtol=tol), f"split-KV, {splits} splits"
+
+
+@pytest.mark.parametrize("heads,kvh,hd,window", [(32, 8, 128, 4096), (12, 2, 64, None), (3, 1, 48, 40), (8, 1, 256, None)])
+def test_attention_decode_batch_with_padding(heads, kvh, hd, window):
+    """A decoding batch of unequal lengths (1 to several pages), with padding sequences in
+    between, against the plain kernel."""
+    b = B()
+    torch.manual_seed(7)
+    dtype = torch.bfloat16
+    cache = make_cache(kvh, hd, window, dtype, max_tokens=64 * 40, max_seq_len=1024, slots=8)
+    lens = [1, 31, 32, 33, 64, 700, 437]
+    slots = [cache.open_sequence() for _ in lens]
+    W = heads + 2 * kvh
+    scale = 1.0 / math.sqrt(hd)
+    ident = torch.zeros(hd // 2, device=DEV)
+    err = err_word()
+    kvs = cache.layer_view(0).struct
+    for s, n in zip(slots, lens):           # fill each sequence's cache with n - 1 tokens
+        cache.reserve(s, n)
+    cache.upload()
+    filled = [n - 1 for n in lens]
+    if any(filled):
+        keep = [(s, n) for s, n in zip(slots, filled) if n]
+        view, arrs = make_batch([n for _, n in keep], [0] * len(keep), [s for s, _ in keep])
+        fill = (torch.randn(sum(filled), W * hd, device=DEV) * 0.7).to(dtype)
+        b.rope_kv_store(fill, view, kvs, ident, heads, hd, b.PAIR_HALF, True, err, stream())
+    # the step: 7 real sequences and 1 padding sequence (slot -1) in the middle
+    order = slots[:3] + [-1] + slots[3:]
+    pos0 = filled[:3] + [0] + filled[3:]
+    nxt = (torch.randn(8, W, hd, device=DEV) * 0.7)
+    nxt[6, :heads] *= 5.0                   # a peaked distribution for the 700-token sequence
+    view1, arrs1 = make_batch([1] * 8, pos0, order)
+    arrs1[2][3] = -1                         # tok_seq of the padding token
+    nxt = nxt.to(dtype).view(8, W * hd)
+    b.rope_kv_store(nxt, view1, kvs, ident, heads, hd, b.PAIR_HALF, True, err, stream())
+    plain = torch.empty(8, heads * hd, device=DEV, dtype=dtype)
+    b.attention_plain(nxt, plain, view1, kvs, heads, scale, True, err, stream())
+    for splits in (1, 2, 5, 16):
+        n = b.attention_decode_scratch_floats(8, heads, hd, splits)
+        scratch = torch.full((n,), float("nan"), device=DEV)
+        fast = torch.full_like(plain, float("nan"))
+        assert b.attention_decode(nxt, fast, view1, kvs, heads, scale, splits, scratch, err, stream())
+        assert err.item() == 0
+        assert torch.isfinite(fast).all() and float(fast[3].abs().sum()) == 0     # padding row: zeros
+        assert torch.allclose(fast.float(), plain.float(), atol=2e-2, rtol=2e-2), f"{splits} splits"
 
 
 def test_sampling_greedy_and_errors():
@@ -302,3 +357,38 @@ def test_sampling_temperature_follows_the_cdf(vocab, temperature):
     peaked[0, vocab - 1] = 50.0
     b.sample_temperature(peaked, temperature, seed, req[:1], step[:1], out2[:1], err, stream())
     assert out2[0].item() == vocab - 1
+
+
+@pytest.mark.parametrize("heads,kvh,hd,window", [(4, 2, 16, 16), (6, 1, 32, None), (3, 3, 48, 70), (8, 2, 128, None),
+                                                 (4, 4, 128, 100), (5, 5, 80, 33), (2, 1, 256, 130)])
+def test_attention_prefill_against_plain_kernel(heads, kvh, hd, window):
+    """The tensor-core prompt attention against its plain sibling: unequal prompts (a single
+    token, lengths around the 64-wide tiles, several tiles), windows that cut tiles at odd
+    places, and one far key that carries the output of the last query."""
+    b = B()
+    torch.manual_seed(8)
+    dtype = torch.bfloat16
+    q_lens = [1, 63, 64, 65, 300, 129]
+    T, Wd = sum(q_lens), heads + 2 * kvh
+    scale = 1.0 / math.sqrt(hd)
+    cache = make_cache(kvh, hd, window, dtype)          # only its geometry is used
+    view, keep = make_batch(q_lens, [0] * len(q_lens), list(range(len(q_lens))))
+    qkv = torch.randn(T, Wd, hd, device=DEV) * 0.7
+    last = sum(q_lens[:5]) - 1                           # last query of the 300-token prompt
+    far = last - (window - 1) if window else last - 299
+    qkv[last, :heads] *= 4.0
+    qkv[far, heads:heads + kvh] = qkv[last, 0:heads:heads // kvh]
+    qkv = qkv.to(dtype).view(T, Wd * hd)
+    err = err_word()
+    plain = torch.empty(T, heads * hd, device=DEV, dtype=dtype)
+    b.attention_plain(qkv, plain, view, cache.layer_view(0).struct, heads, scale, False, err, stream())
+    fast = torch.full_like(plain, float("nan"))
+    assert b.attention_prefill(qkv, fast, view, heads, kvh, hd, window or 0, scale, max(q_lens), stream())
+    torch.cuda.synchronize()
+    assert torch.isfinite(fast).all()
+    assert torch.allclose(fast.float(), plain.float(), atol=2e-2, rtol=2e-2), \
+        f"max diff {(fast.float() - plain.float()).abs().max().item():.4g}"
+    x = qkv.float().cpu().view(T, Wd, hd)
+    lo = far
+    p_far = P.softmax((x[lo:last + 1, heads] @ x[last, 0]) * scale)
+    assert p_far[0] > 0.5, "the far key does not dominate"
