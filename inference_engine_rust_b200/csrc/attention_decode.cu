@@ -283,3 +283,66 @@ IERT_API int iert_attention_decode(const void* qkv, void* out, const IertBatchVi
   attention_decode_combine_kernel<<<dim3(T, heads), hd >= 128 ? 128 : 64, 0, stream>>>(p, hd);
   return iert_check_launch("attention_decode_combine");
 }
+
+// ---------------------------------------------------------------------------------------
+// The variant that allocates nothing: see attention_decode_static.h for who needs it and
+// for the rules.  The scratch lives in this translation unit's image.
+#include "attention_decode_static.h"
+
+#include <mutex>
+
+namespace {
+
+static __device__ __align__(256) float g_static_scratch[IERT_STATIC_SCRATCH_FLOATS];
+
+constexpr int MAX_DEVICES = 64;
+float* g_static_scratch_addr[MAX_DEVICES] = {};   // device address of the array, per device
+std::mutex g_static_mu;
+
+// In host code `g_static_scratch` is only a handle for the runtime, not a device address: the
+// address a kernel can use has to be asked for, once per device, with that device current.
+int static_scratch_address(float** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return IERT_STATIC_SETUP_FAILED;
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  if (!g_static_scratch_addr[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || !p) {
+      cudaGetLastError();
+      return IERT_STATIC_SETUP_FAILED;
+    }
+    g_static_scratch_addr[dev] = (float*)p;
+  }
+  *out = g_static_scratch_addr[dev];
+  return IERT_OK;
+}
+
+}  // namespace
+
+IERT_API long long iert_attention_decode_static_capacity() { return (long long)IERT_STATIC_SCRATCH_FLOATS; }
+
+IERT_API const char* iert_attention_decode_static_message(int status) {
+  switch (status) {
+    case IERT_OK: return "launched";
+    case IERT_BAD_ARGUMENT: return "the kernel does not take this cache geometry or these sizes";
+    case IERT_CUDA_ERROR: return "the launch failed (see iert_last_cuda_error)";
+    case IERT_STATIC_SCRATCH_TOO_SMALL:
+      return "the call needs more scratch than the library's fixed 8 MiB array holds: use fewer splits, a "
+             "smaller batch, or iert_attention_decode with a buffer of your own";
+    case IERT_STATIC_SETUP_FAILED: return "the device address of the fixed scratch array could not be obtained";
+    default: return "unknown status";
+  }
+}
+
+IERT_API int iert_attention_decode_static(const void* qkv, void* out, const IertBatchView* batch,
+                                          const IertKvView* cache, int heads, float scale, int splits,
+                                          int* err, cudaStream_t stream) {
+  if (batch->n_tokens <= 0) return IERT_OK;
+  if (splits < 1 || heads <= 0 || cache->head_dim <= 0) return IERT_BAD_ARGUMENT;
+  const long long need = iert_attention_decode_scratch_floats(batch->n_tokens, heads, cache->head_dim, splits);
+  if (need > (long long)IERT_STATIC_SCRATCH_FLOATS) return IERT_STATIC_SCRATCH_TOO_SMALL;
+  float* scratch = nullptr;
+  const int st = static_scratch_address(&scratch);
+  if (st != IERT_OK) return st;
+  return iert_attention_decode(qkv, out, batch, cache, heads, scale, splits, scratch, err, stream);
+}
