@@ -47,6 +47,8 @@ attention_decode_kernel(DecodeParams p, IertBatchView b, IertKvView c) {
   float* o_s = p_s + WARPS * KEY_BLOCK * GT;      // [WARPS][GT][hd]
   float* ml_s = o_s + WARPS * GT * hd;            // [WARPS][GT][2]
 
+  pdl_wait();
+  pdl_launch_dependents();
   const int split = blockIdx.x, t = blockIdx.z;
   const int kvh = blockIdx.y / p.slices, slice = blockIdx.y % p.slices;
   const int group = p.heads / c.kv_heads;
@@ -216,6 +218,8 @@ attention_decode_kernel(DecodeParams p, IertBatchView b, IertKvView c) {
 
 // One block per (token, head): merge the splits in split order, normalise, write bf16.
 __global__ void attention_decode_combine_kernel(DecodeParams p, int hd) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int t = blockIdx.x, head = blockIdx.y;
   const float* po = p.part_out + ((size_t)t * p.heads + head) * p.splits * hd;
   const float* pml = p.part_ml + ((size_t)t * p.heads + head) * p.splits * 2;
@@ -273,14 +277,14 @@ IERT_API int iert_attention_decode(const void* qkv, void* out, const IertBatchVi
   const size_t smem = smem_bytes(gt, hd);
   if (smem > 48 * 1024) return IERT_BAD_ARGUMENT;
   switch (gt) {
-    case 1: attention_decode_kernel<1><<<grid, THREADS, smem, stream>>>(p, *batch, *cache); break;
-    case 2: attention_decode_kernel<2><<<grid, THREADS, smem, stream>>>(p, *batch, *cache); break;
-    case 4: attention_decode_kernel<4><<<grid, THREADS, smem, stream>>>(p, *batch, *cache); break;
-    default: attention_decode_kernel<8><<<grid, THREADS, smem, stream>>>(p, *batch, *cache); break;
+    case 1: launch_dep(attention_decode_kernel<1>, grid, THREADS, smem, stream, p, *batch, *cache); break;
+    case 2: launch_dep(attention_decode_kernel<2>, grid, THREADS, smem, stream, p, *batch, *cache); break;
+    case 4: launch_dep(attention_decode_kernel<4>, grid, THREADS, smem, stream, p, *batch, *cache); break;
+    default: launch_dep(attention_decode_kernel<8>, grid, THREADS, smem, stream, p, *batch, *cache); break;
   }
   int st = iert_check_launch("attention_decode");
   if (st != IERT_OK) return st;
-  attention_decode_combine_kernel<<<dim3(T, heads), hd >= 128 ? 128 : 64, 0, stream>>>(p, hd);
+  launch_dep(attention_decode_combine_kernel, dim3(T, heads), dim3(hd >= 128 ? 128 : 64), 0, stream, p, hd);
   return iert_check_launch("attention_decode_combine");
 }
 

@@ -1,0 +1,295 @@
+// Decode attention on the tensor cores: one query token per sequence against the paged cache,
+// split over the keys, bf16 operands (mma.sync m16n8k16), fp32 scores / softmax / output.
+// Compiled once per head size (-DHEAD_DIM, multiple of 16 up to 256), like the prompt kernel.
+//
+//   grid (splits, kv_heads * slices, sequences).  The up to 16 query heads that share one kv
+//   head are the 16 rows of the MMA tile, so every key and value is read once per group and
+//   the arithmetic is a handful of MMAs per page: the kernel is a stream of page loads.
+//   A CTA walks its share of the sequence's 64-position pages; each page's keys and values
+//   (two contiguous runs of 64 * HEAD_DIM bf16) are fetched with cp.async into double-buffered
+//   shared memory with padded rows (conflict-free ldmatrix); rows outside [j_min, pos] are
+//   zero-filled, so memory that was never written cannot reach the arithmetic.
+//   Each of the 4 warps takes 16 of a page's 64 keys with its own running maximum and sum;
+//   the warps are merged through shared memory in warp order at the end, and the split's
+//   partial result (unnormalised output, maximum, sum) goes to scratch memory.  A second
+//   kernel merges the splits in split order.
+//
+// Visible keys: [max(0, pos + 1 - W), pos] (src/layers/attention.rs:609-613); scale from the
+// caller; softmax in fp32 (src/ops/softmax.rs:11-25).
+#include "common.cuh"
+
+#ifndef HEAD_DIM
+#error "compile with -DHEAD_DIM=<multiple of 16>"
+#endif
+
+using namespace iert;
+
+namespace {
+
+constexpr int HD = HEAD_DIM;
+constexpr int PAGE = 64, WARPS = 4, THREADS = WARPS * 32, ROWS = 16;
+constexpr int ROW_BYTES = HD * 2 + 16;
+constexpr int TILE_BYTES = PAGE * ROW_BYTES;
+constexpr int KSTEPS = HD / 16;
+
+struct DecodeTcParams {
+  const __nv_bfloat16* qkv;   // [T, (heads + 2 kv_heads) * HD], queries rotated
+  float* part_out;            // [T, heads, splits, HD]
+  float* part_ml;             // [T, heads, splits, 2]  (maximum in base-2 units, sum)
+  __nv_bfloat16* out;         // [T, heads * HD]
+  int heads, splits, slices, gt;
+  float scale_log2e;
+  int* err;
+};
+
+__device__ __forceinline__ void cp16(void* smem_dst, const void* gsrc, bool valid) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+  const int n = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gsrc), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void ldsm4(uint32_t (&r)[4], const void* p) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldsm4t(uint32_t (&r)[4], const void* p) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// One page's rows [0, 64) of one kv head into a padded tile; rows outside [lo, hi] are zeros.
+__device__ __forceinline__ void load_page(uint8_t* tile, const __nv_bfloat16* src, int lo, int hi) {
+  constexpr int CHUNKS = HD / 8;
+  for (int i = threadIdx.x; i < PAGE * CHUNKS; i += THREADS) {
+    const int r = i / CHUNKS, c = i % CHUNKS;
+    const bool ok = r >= lo && r <= hi;
+    cp16(tile + r * ROW_BYTES + c * 16, src + (ok ? r * HD + c * 8 : 0), ok);
+  }
+}
+
+__global__ void __launch_bounds__(THREADS)
+attention_decode_tc_kernel(DecodeTcParams p, IertBatchView b, IertKvView c) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  auto k_tile = [&](int i) { return smem + (size_t)i * TILE_BYTES; };
+  auto v_tile = [&](int i) { return smem + (size_t)(2 + i) * TILE_BYTES; };
+  uint8_t* q_tile = smem + 4 * TILE_BYTES;               // [16][ROW_BYTES]
+
+  pdl_wait();
+  pdl_launch_dependents();
+  const int split = blockIdx.x, t = blockIdx.z;
+  const int kvh = blockIdx.y / p.slices, slice = blockIdx.y % p.slices;
+  const int group = p.heads / c.kv_heads;
+  const int g0 = slice * p.gt;
+  const int n_g = min(p.gt, group - g0);
+  const int head0 = kvh * group + g0;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
+
+  const int s = b.tok_seq[t];
+  const int slot = s >= 0 ? b.slot_ids[s] : -1;
+  float* po = p.part_out + (((size_t)t * p.heads + head0) * p.splits + split) * HD;
+  float* pml = p.part_ml + (((size_t)t * p.heads + head0) * p.splits + split) * 2;
+  if (slot < 0) {
+    if (threadIdx.x < n_g) { pml[(size_t)threadIdx.x * p.splits * 2] = -INFINITY; pml[(size_t)threadIdx.x * p.splits * 2 + 1] = 0.f; }
+    return;
+  }
+  const int pos = b.pos0[s] + (t - b.cu_q[s]);
+  const int j_min = c.window > 0 ? max(0, pos + 1 - c.window) : 0;
+  const int pg_lo = j_min / PAGE, pg_hi = pos / PAGE + 1;           // logical pages [pg_lo, pg_hi)
+  const int per = (pg_hi - pg_lo + p.splits - 1) / p.splits;
+  const int my_lo = pg_lo + split * per, my_hi = min(pg_hi, my_lo + per);
+
+  // queries of the group: rows 0..n_g-1 of a 16-row tile, the other rows zero
+  {
+    const __nv_bfloat16* q = p.qkv + (size_t)t * ((size_t)(p.heads + 2 * c.kv_heads) * HD) + (size_t)head0 * HD;
+    constexpr int CHUNKS = HD / 8;
+    for (int i = threadIdx.x; i < ROWS * CHUNKS; i += THREADS) {
+      const int r = i / CHUNKS, cc = i % CHUNKS;
+      cp16(q_tile + r * ROW_BYTES + cc * 16, q + (r < n_g ? r * HD + cc * 8 : 0), r < n_g);
+    }
+  }
+  auto issue = [&](int pg, int buf) {
+    const int page = c.page_table[(size_t)slot * c.table_width + pg % c.ring_pages];
+    const bool ok = page >= 0 && page < c.n_pages;
+    if (!ok && threadIdx.x == 0) atomicOr(p.err, IERT_ERR_PAGE_RANGE);
+    const size_t off = (((size_t)(ok ? page : 0) * c.kv_heads + kvh) * PAGE) * HD;
+    const int lo = ok ? max(0, j_min - pg * PAGE) : PAGE, hi = ok ? min(PAGE - 1, pos - pg * PAGE) : -1;
+    load_page(k_tile(buf), (const __nv_bfloat16*)c.k + off, lo, hi);
+    load_page(v_tile(buf), (const __nv_bfloat16*)c.v + off, lo, hi);
+  };
+  if (my_lo < my_hi) issue(my_lo, 0);
+  cp_commit();
+
+  uint32_t qf[KSTEPS][4];
+  float o[KSTEPS * 2][4];
+#pragma unroll
+  for (int n = 0; n < KSTEPS * 2; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  float m_row = -INFINITY, l_row = 0.f;          // row g (a head of the group); rows >= 8 are padding
+
+  for (int pg = my_lo; pg < my_hi; ++pg) {
+    const int buf = (pg - my_lo) & 1;
+    if (pg + 1 < my_hi) { issue(pg + 1, buf ^ 1); cp_commit(); cp_wait<1>(); }
+    else cp_wait<0>();
+    __syncthreads();
+    if (pg == my_lo) {
+#pragma unroll
+      for (int ks = 0; ks < KSTEPS; ++ks)
+        ldsm4(qf[ks], q_tile + (lane & 15) * ROW_BYTES + (ks * 16 + (lane >> 4) * 8) * 2);
+    }
+    // ---- scores of this warp's 16 keys: S[16 rows][16 keys]
+    float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ++ks) {
+      uint32_t kb[4];
+      ldsm4(kb, k_tile(buf) + (warp * 16 + (lane & 7) + ((lane >> 4) << 3)) * ROW_BYTES + (ks * 16 + ((lane >> 3) & 1) * 8) * 2);
+      mma16816(sc[0], qf[ks], kb[0], kb[1]);
+      mma16816(sc[1], qf[ks], kb[2], kb[3]);
+    }
+    // ---- mask and running softmax for row g (elements 0,1 of each tile; 2,3 belong to row g+8)
+    const int jbase = pg * PAGE + warp * 16;
+    float mx = m_row;
+    float v[2][2];
+#pragma unroll
+    for (int n = 0; n < 2; ++n)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int j = jbase + n * 8 + tq * 2 + e;
+        v[n][e] = (j >= j_min && j <= pos) ? sc[n][e] * p.scale_log2e : -INFINITY;
+        mx = fmaxf(mx, v[n][e]);
+      }
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float alpha = m_row == -INFINITY ? 0.f : exp2f(m_row - mx);
+    m_row = mx;
+    l_row *= alpha;
+    float pr[2][2];
+#pragma unroll
+    for (int n = 0; n < 2; ++n)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        pr[n][e] = (v[n][e] == -INFINITY || mx == -INFINITY) ? 0.f : exp2f(v[n][e] - mx);
+        l_row += pr[n][e];
+      }
+#pragma unroll
+    for (int n = 0; n < KSTEPS * 2; ++n) { o[n][0] *= alpha; o[n][1] *= alpha; }
+    // ---- O += P V over the warp's 16 keys (rows g+8 of P are zero)
+    const uint32_t pa[4] = {pack2(pr[0][0], pr[0][1]), 0u, pack2(pr[1][0], pr[1][1]), 0u};
+#pragma unroll
+    for (int dp = 0; dp < KSTEPS; ++dp) {
+      uint32_t vb[4];
+      ldsm4t(vb, v_tile(buf) + (warp * 16 + (lane & 7) + (((lane >> 3) & 1) << 3)) * ROW_BYTES + (dp * 16 + (lane >> 4) * 8) * 2);
+      mma16816(o[2 * dp], pa, vb[0], vb[1]);
+      mma16816(o[2 * dp + 1], pa, vb[2], vb[3]);
+    }
+    __syncthreads();
+  }
+
+  // ---- merge the four warps in warp order (shared memory is free now), write the partial
+  cp_wait<0>();
+  __syncthreads();
+  l_row += __shfl_xor_sync(0xffffffffu, l_row, 1);
+  l_row += __shfl_xor_sync(0xffffffffu, l_row, 2);
+  float* o_s = reinterpret_cast<float*>(smem);                 // [WARPS][8][HD]
+  float* ml_s = o_s + WARPS * 8 * HD;                          // [WARPS][8][2]
+#pragma unroll
+  for (int n = 0; n < KSTEPS * 2; ++n) {
+    o_s[(warp * 8 + g) * HD + n * 8 + tq * 2] = o[n][0];
+    o_s[(warp * 8 + g) * HD + n * 8 + tq * 2 + 1] = o[n][1];
+  }
+  if (tq == 0) { ml_s[(warp * 8 + g) * 2] = m_row; ml_s[(warp * 8 + g) * 2 + 1] = l_row; }
+  __syncthreads();
+  for (int r = 0; r < n_g && r < 8; ++r) {
+    float mm = -INFINITY;
+    for (int w = 0; w < WARPS; ++w) mm = fmaxf(mm, ml_s[(w * 8 + r) * 2]);
+    float wgt[WARPS], ll = 0.f;
+    for (int w = 0; w < WARPS; ++w) {
+      const float mw = ml_s[(w * 8 + r) * 2];
+      wgt[w] = mw == -INFINITY ? 0.f : exp2f(mw - mm);
+      ll += wgt[w] * ml_s[(w * 8 + r) * 2 + 1];
+    }
+    for (int d = threadIdx.x; d < HD; d += THREADS) {
+      float acc = 0.f;
+      for (int w = 0; w < WARPS; ++w) acc += wgt[w] * o_s[(w * 8 + r) * HD + d];
+      po[(size_t)r * p.splits * HD + d] = acc;
+    }
+    if (threadIdx.x == 0) { pml[(size_t)r * p.splits * 2] = mm; pml[(size_t)r * p.splits * 2 + 1] = ll; }
+  }
+}
+
+// One block per (token, head): merge the splits in split order, normalise, write bf16.
+__global__ void attention_decode_tc_combine_kernel(DecodeTcParams p) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x, head = blockIdx.y;
+  const float* po = p.part_out + ((size_t)t * p.heads + head) * p.splits * HD;
+  const float* pml = p.part_ml + ((size_t)t * p.heads + head) * p.splits * 2;
+  float mm = -INFINITY;
+  for (int s = 0; s < p.splits; ++s) mm = fmaxf(mm, pml[2 * s]);
+  float ll = 0.f;
+  for (int s = 0; s < p.splits; ++s) ll += pml[2 * s] == -INFINITY ? 0.f : exp2f(pml[2 * s] - mm) * pml[2 * s + 1];
+  const float inv = ll > 0.f ? 1.0f / ll : 0.f;
+  __nv_bfloat16* o = p.out + ((size_t)t * p.heads + head) * HD;
+  for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < p.splits; ++s)
+      if (pml[2 * s] != -INFINITY) acc += exp2f(pml[2 * s] - mm) * po[(size_t)s * HD + d];
+    o[d] = __float2bfloat16_rn(acc * inv);
+  }
+}
+
+}  // namespace
+
+IERT_API long long iert_attention_decode_tc_scratch_floats(int n_tokens, int heads, int splits) {
+  return (long long)n_tokens * heads * splits * (HD + 2);
+}
+
+// Same contract as the core library's iert_attention_decode, for caches with head_dim ==
+// HEAD_DIM, bf16, 64-position pages.  Anything else: IERT_BAD_ARGUMENT, nothing launched.
+IERT_API int iert_attention_decode_tc(const void* qkv, void* out, const IertBatchView* batch,
+                                      const IertKvView* cache, int heads, float scale, int splits,
+                                      float* scratch, int* err, cudaStream_t stream) {
+  const int T = batch->n_tokens;
+  if (T <= 0) return IERT_OK;
+  if (cache->dtype != IERT_BF16 || cache->head_dim != HD || cache->page_tokens != PAGE || splits < 1 || heads <= 0 ||
+      cache->kv_heads <= 0 || heads % cache->kv_heads != 0 || T > 65535)
+    return IERT_BAD_ARGUMENT;
+  const int group = heads / cache->kv_heads;
+  DecodeTcParams p;
+  p.qkv = (const __nv_bfloat16*)qkv;
+  p.out = (__nv_bfloat16*)out;
+  p.heads = heads; p.splits = splits;
+  p.gt = group < 8 ? group : 8;                      // heads per CTA (rows 0..7 of the MMA tile)
+  p.slices = (group + p.gt - 1) / p.gt;
+  p.scale_log2e = scale * 1.4426950408889634f;
+  p.err = err;
+  p.part_out = scratch;
+  p.part_ml = scratch + (size_t)T * heads * splits * HD;
+  if ((long long)cache->kv_heads * p.slices > 65535) return IERT_BAD_ARGUMENT;
+  size_t smem = 4 * (size_t)TILE_BYTES + ROWS * ROW_BYTES;
+  const size_t merge = (size_t)(WARPS * 8 * HD + WARPS * 8 * 2) * sizeof(float);
+  if (merge > smem) smem = merge;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(attention_decode_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+      cudaGetLastError();
+      return IERT_CUDA_ERROR;
+    }
+    configured = true;
+  }
+  launch_dep(attention_decode_tc_kernel, dim3(splits, cache->kv_heads * p.slices, T), dim3(THREADS), smem, stream,
+             p, *batch, *cache);
+  if (cudaGetLastError() != cudaSuccess) return IERT_CUDA_ERROR;
+  launch_dep(attention_decode_tc_combine_kernel, dim3(T, heads), dim3(HD >= 128 ? 128 : 64), 0, stream, p);
+  return cudaGetLastError() == cudaSuccess ? IERT_OK : IERT_CUDA_ERROR;
+}

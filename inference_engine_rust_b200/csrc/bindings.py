@@ -5,6 +5,7 @@ machine without the built library (or without a GPU) gets an error, not a fallba
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import POINTER, Structure, byref, c_char_p, c_float, c_int, c_longlong, c_ulonglong, c_void_p
 from typing import Optional
 
@@ -60,6 +61,8 @@ def core() -> ctypes.CDLL:
     if _core is None:
         lib = build.load_library("iert_core", build.CORE_SOURCES)
         _declare(lib)
+        if os.environ.get("IERT_PDL", "1") == "0":      # programmatic dependent launch off (for measurements)
+            lib.iert_set_pdl(0)
         _core = lib
     return _core
 
@@ -262,7 +265,24 @@ def attention_decode(qkv, out, batch: BatchView, kv: KvView, heads: int, scale: 
     return True
 
 
-_prefill_libs = {}
+_attn_libs = {}
+
+
+def _attention_lib(head_dim: int):
+    """The tensor-core attention library for one head size, compiled on first use."""
+    lib = _attn_libs.get(head_dim)
+    if lib is None:
+        lib = build.load_library(*build.attention_library(head_dim))
+        lib.iert_attention_prefill.argtypes = [c_void_p, c_void_p, POINTER(BatchView), c_int, c_int, c_int,
+                                               c_float, c_int, c_void_p]
+        lib.iert_attention_prefill.restype = c_int
+        lib.iert_attention_decode_tc.argtypes = [c_void_p, c_void_p, POINTER(BatchView), POINTER(KvView), c_int,
+                                                 c_float, c_int, c_void_p, c_void_p, c_void_p]
+        lib.iert_attention_decode_tc.restype = c_int
+        if os.environ.get("IERT_PDL", "1") == "0":
+            lib.iert_set_pdl(0)
+        _attn_libs[head_dim] = lib
+    return lib
 
 
 def attention_prefill(qkv, out, batch: BatchView, heads: int, kv_heads: int, head_dim: int, window: int,
@@ -272,19 +292,31 @@ def attention_prefill(qkv, out, batch: BatchView, heads: int, kv_heads: int, hea
     head sizes return False and nothing is launched."""
     if head_dim % 16 or not 16 <= head_dim <= 256:
         return False
-    lib = _prefill_libs.get(head_dim)
-    if lib is None:
-        lib = build.load_library(*build.prefill_attention_library(head_dim))
-        lib.iert_attention_prefill.argtypes = [c_void_p, c_void_p, POINTER(BatchView), c_int, c_int, c_int,
-                                               c_float, c_int, c_void_p]
-        lib.iert_attention_prefill.restype = c_int
-        _prefill_libs[head_dim] = lib
-    status = lib.iert_attention_prefill(qkv.data_ptr(), out.data_ptr(), byref(batch), heads, kv_heads,
-                                        window, scale, max_q_len, stream)
+    status = _attention_lib(head_dim).iert_attention_prefill(qkv.data_ptr(), out.data_ptr(), byref(batch), heads,
+                                                             kv_heads, window, scale, max_q_len, stream)
     if status == 1:
         return False
     if status != 0:
         raise KernelError("attention_prefill: the launch failed")
     global launch_count
     launch_count += 1
+    return True
+
+
+def attention_decode_tc(qkv, out, batch: BatchView, kv: KvView, heads: int, scale: float, splits: int,
+                        scratch, err, stream) -> bool:
+    """Tensor-core split-KV decode attention (bf16 cache, 64-position pages, head sizes that
+    are multiples of 16 up to 256).  Returns False, having launched nothing, otherwise."""
+    hd = kv.head_dim
+    if hd % 16 or not 16 <= hd <= 256:
+        return False
+    status = _attention_lib(hd).iert_attention_decode_tc(qkv.data_ptr(), out.data_ptr(), byref(batch), byref(kv),
+                                                         heads, scale, splits, scratch.data_ptr(), err.data_ptr(),
+                                                         stream)
+    if status == 1:
+        return False
+    if status != 0:
+        raise KernelError("attention_decode_tc: the launch failed")
+    global launch_count
+    launch_count += 2
     return True

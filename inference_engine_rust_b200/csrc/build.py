@@ -169,9 +169,11 @@ def load_library(name: str, sources: Sequence[str], defines: Sequence[str] = ())
 PREBUILT_HEAD_DIMS = (16, 32, 48, 64, 128)
 
 
-def prefill_attention_library(head_dim: int):
-    """(name, sources, defines) of the prompt-attention library for one head size."""
-    return f"iert_attn_prefill_hd{head_dim}", ["attention_prefill.cu"], [f"HEAD_DIM={head_dim}"]
+def attention_library(head_dim: int):
+    """(name, sources, defines) of the tensor-core attention library (prompt and decode
+    kernels) for one head size."""
+    return (f"iert_attn_hd{head_dim}", ["runtime.cu", "attention_prefill.cu", "attention_decode_tc.cu"],
+            [f"HEAD_DIM={head_dim}"])
 
 
 def build_all(verbose: bool = True) -> List[str]:
@@ -179,5 +181,5 @@ def build_all(verbose: bool = True) -> List[str]:
     size-specialised ones for the head sizes in `PREBUILT_HEAD_DIMS`."""
     paths = [build_library("iert_core", CORE_SOURCES, verbose=verbose)]
     for hd in PREBUILT_HEAD_DIMS:
-        paths.append(build_library(*prefill_attention_library(hd), verbose=verbose))
+        paths.append(build_library(*attention_library(hd), verbose=verbose))
     return paths

@@ -134,7 +134,36 @@ __device__ __forceinline__ long long kv_row_offset(const IertKvView& c, int slot
   return (((long long)page * c.kv_heads + h) * c.page_tokens + row) * c.head_dim;
 }
 
+// Programmatic dependent launch: a kernel launched with `launch_dep` may start while the
+// kernel before it in the stream is still running.  It must call pdl_wait() before it reads
+// anything an earlier kernel wrote and before it writes anything an earlier kernel may
+// still read; what it does before that (set-up, loads of weights) overlaps the earlier
+// kernel.  pdl_launch_dependents() lets the NEXT kernel start its own preamble early.
+// Both are no-ops for a kernel launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 }  // namespace iert
 
 // Defined in runtime.cu.
 int iert_check_launch(const char* what);
+extern int iert_pdl_enabled;
+
+// Launch `kernel` with programmatic stream serialization (see pdl_wait) when enabled.
+template <typename... KArgs, typename... Args>
+inline void launch_dep(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                       Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = iert_pdl_enabled ? 1 : 0;
+  cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}

@@ -13,6 +13,8 @@ template <typename TW>
 __global__ void embed_gather_kernel(const TW* __restrict__ table, const int* __restrict__ ids,
                                     float* __restrict__ x, int hidden, int vocab, float scale,
                                     int* __restrict__ err) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int t = blockIdx.x;
   const int id = ids[t];
   float* row = x + (size_t)t * hidden;
@@ -32,9 +34,9 @@ IERT_API int iert_embed_gather(const void* table, int table_dtype, const int* id
   if (hidden <= 0 || vocab <= 0) return IERT_BAD_ARGUMENT;
   const int threads = hidden >= 1024 ? 256 : 128;
   if (table_dtype == IERT_F32)
-    embed_gather_kernel<float><<<n_tokens, threads, 0, stream>>>((const float*)table, ids, x, hidden, vocab, scale, err);
+    launch_dep(embed_gather_kernel<float>, n_tokens, threads, 0, stream, (const float*)table, ids, x, hidden, vocab, scale, err);
   else if (table_dtype == IERT_BF16)
-    embed_gather_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>((const __nv_bfloat16*)table, ids, x, hidden, vocab, scale, err);
+    launch_dep(embed_gather_kernel<__nv_bfloat16>, n_tokens, threads, 0, stream, (const __nv_bfloat16*)table, ids, x, hidden, vocab, scale, err);
   else
     return IERT_BAD_ARGUMENT;
   return iert_check_launch("embed_gather");
@@ -49,6 +51,8 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const TW* __restrict
                                TO* __restrict__ out, const int* __restrict__ rows_idx,
                                int hidden, float eps) {
   __shared__ float scratch[33];
+  pdl_wait();
+  pdl_launch_dependents();
   const int r = blockIdx.x;
   const int src_row = rows_idx ? rows_idx[r] : r;
   const float* xr = x + (size_t)src_row * hidden;
@@ -64,14 +68,58 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const TW* __restrict
     o[i] = from_f32<TO>(xr[i] * to_f32(w[i]) * rinv);
 }
 
+// The same with the row held in registers (one read of x) and the scale vector fetched
+// before the wait on the previous kernel, which it never depends on.
+template <typename TW, typename TO, int NPT>
+__global__ void rmsnorm_reg_kernel(const float* __restrict__ x, const TW* __restrict__ w,
+                                   TO* __restrict__ out, const int* __restrict__ rows_idx,
+                                   int hidden, float eps) {
+  __shared__ float scratch[33];
+  float wv[NPT], xv[NPT];
+#pragma unroll
+  for (int k = 0; k < NPT; ++k) {
+    const int i = threadIdx.x + k * blockDim.x;
+    wv[k] = i < hidden ? to_f32(w[i]) : 0.f;
+  }
+  pdl_wait();
+  pdl_launch_dependents();
+  const int r = blockIdx.x;
+  const int src_row = rows_idx ? rows_idx[r] : r;
+  const float* xr = x + (size_t)src_row * hidden;
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < NPT; ++k) {
+    const int i = threadIdx.x + k * blockDim.x;
+    xv[k] = i < hidden ? xr[i] : 0.f;
+    ss += xv[k] * xv[k];
+  }
+  ss = block_sum(ss, scratch);
+  const float rinv = 1.0f / sqrtf(ss / (float)hidden + eps);
+  TO* o = out + (size_t)r * hidden;
+#pragma unroll
+  for (int k = 0; k < NPT; ++k) {
+    const int i = threadIdx.x + k * blockDim.x;
+    if (i < hidden) o[i] = from_f32<TO>(xv[k] * wv[k] * rinv);
+  }
+}
+
 IERT_API int iert_rmsnorm(const float* x, const void* w, int w_dtype, void* out, int out_dtype,
                           const int* rows_idx, int rows, int hidden, float eps,
                           cudaStream_t stream) {
   if (rows <= 0) return IERT_OK;
   if (hidden <= 0) return IERT_BAD_ARGUMENT;
   const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
-#define LAUNCH(TW, TO) rmsnorm_kernel<TW, TO><<<rows, threads, 0, stream>>>( \
-    x, (const TW*)w, (TO*)out, rows_idx, hidden, eps)
+#define LAUNCH(TW, TO)                                                                                   \
+  do {                                                                                                   \
+    if (hidden <= 4 * 256) launch_dep(rmsnorm_reg_kernel<TW, TO, 4>, rows, 256, 0, stream,               \
+                                      x, (const TW*)w, (TO*)out, rows_idx, hidden, eps);                 \
+    else if (hidden <= 8 * 512) launch_dep(rmsnorm_reg_kernel<TW, TO, 8>, rows, 512, 0, stream,          \
+                                           x, (const TW*)w, (TO*)out, rows_idx, hidden, eps);            \
+    else if (hidden <= 16 * 512) launch_dep(rmsnorm_reg_kernel<TW, TO, 16>, rows, 512, 0, stream,        \
+                                             x, (const TW*)w, (TO*)out, rows_idx, hidden, eps);          \
+    else launch_dep(rmsnorm_kernel<TW, TO>, rows, threads, 0, stream,                                    \
+                    x, (const TW*)w, (TO*)out, rows_idx, hidden, eps);                                   \
+  } while (0)
   if (w_dtype == IERT_F32 && out_dtype == IERT_F32) LAUNCH(float, float);
   else if (w_dtype == IERT_F32 && out_dtype == IERT_BF16) LAUNCH(float, __nv_bfloat16);
   else if (w_dtype == IERT_BF16 && out_dtype == IERT_F32) LAUNCH(__nv_bfloat16, float);
@@ -96,6 +144,8 @@ __global__ void rope_kv_store_kernel(T* __restrict__ qkv, IertBatchView b, IertK
                                      const float* __restrict__ inv_freq, int heads,
                                      int rotary_dim, int pairing, int write_cache,
                                      int* __restrict__ err) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int t = blockIdx.x;
   const int head = blockIdx.y;
   const int s = b.tok_seq[t];
@@ -152,9 +202,9 @@ IERT_API int iert_rope_kv_store(void* qkv, int dtype, const IertBatchView* batch
   dim3 grid(batch->n_tokens, total_heads);
   const int threads = cache->head_dim >= 128 ? 64 : 32;
   if (dtype == IERT_F32)
-    rope_kv_store_kernel<float><<<grid, threads, 0, stream>>>((float*)qkv, *batch, *cache, inv_freq, heads, rotary_dim, pairing, write_cache, err);
+    launch_dep(rope_kv_store_kernel<float>, grid, threads, 0, stream, (float*)qkv, *batch, *cache, inv_freq, heads, rotary_dim, pairing, write_cache, err);
   else if (dtype == IERT_BF16)
-    rope_kv_store_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>((__nv_bfloat16*)qkv, *batch, *cache, inv_freq, heads, rotary_dim, pairing, write_cache, err);
+    launch_dep(rope_kv_store_kernel<__nv_bfloat16>, grid, threads, 0, stream, (__nv_bfloat16*)qkv, *batch, *cache, inv_freq, heads, rotary_dim, pairing, write_cache, err);
   else
     return IERT_BAD_ARGUMENT;
   return iert_check_launch("rope_kv_store");
@@ -172,6 +222,8 @@ __device__ __forceinline__ float stable_sigmoid(float x) {
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter,
                                 size_t total) {
+  pdl_wait();
+  pdl_launch_dependents();
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (size_t)gridDim.x * blockDim.x) {
     const size_t t = idx / inter;
@@ -190,9 +242,9 @@ IERT_API int iert_silu_mul(const void* gu, void* out, int dtype, int n_tokens, i
   const int threads = 256;
   const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
   if (dtype == IERT_F32)
-    silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, inter, total);
+    launch_dep(silu_mul_kernel<float>, blocks, threads, 0, stream, (const float*)gu, (float*)out, inter, total);
   else if (dtype == IERT_BF16)
-    silu_mul_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter, total);
+    launch_dep(silu_mul_kernel<__nv_bfloat16>, blocks, threads, 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter, total);
   else
     return IERT_BAD_ARGUMENT;
   return iert_check_launch("silu_mul");

@@ -102,28 +102,45 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) pdl_launch_dependents();
 
   const int total_work = p.n_tiles * p.t_tiles * p.splits;
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
+      // The weight tiles do not depend on the kernel before this one, the token tiles do:
+      // the first `stages` weight loads are issued at once, then the dependency is awaited,
+      // then their token tiles follow.  (With an ordinary launch the wait returns at once.)
       int stage = 0, issued = 0;
       uint32_t phase = 0;
-      bool ok = true;
+      bool ok = true, dep_ready = false;
+      int pend_kb[12], pend_t0[12];
       for (int work = blockIdx.x; ok && work < total_work; work += gridDim.x) {
         const int split = work % p.splits, tile = work / p.splits;
         const int n0 = (tile / p.t_tiles) * TILE_N, t0 = (tile % p.t_tiles) * BT;
         const int kb0 = split * p.kb_per_split, kb1 = min(p.kb_total, kb0 + p.kb_per_split);
         for (int kb = kb0; kb < kb1; ++kb) {
+          if (!dep_ready && issued == stages) {
+            pdl_wait();
+            for (int i = 0; i < issued; ++i)
+              tma_load_2d(smem + (size_t)i * STAGE_BYTES + W_STAGE_BYTES, &map_x, &full[i], pend_kb[i] * TILE_K, pend_t0[i]);
+            dep_ready = true;
+          }
           if (!wait_or_abort(&empty[stage], phase ^ 1, abort_flag)) { ok = false; break; }
           uint8_t* ws_ = smem + (size_t)stage * STAGE_BYTES;
           mbar_expect_tx(&full[stage], STAGE_BYTES);
           tma_load_2d(ws_, &map_w, &full[stage], kb * TILE_K, n0);
-          tma_load_2d(ws_ + W_STAGE_BYTES, &map_x, &full[stage], kb * TILE_K, t0);
+          if (dep_ready) tma_load_2d(ws_ + W_STAGE_BYTES, &map_x, &full[stage], kb * TILE_K, t0);
+          else { pend_kb[issued] = kb; pend_t0[issued] = t0; }
           ++issued;
           if (++stage == stages) { stage = 0; phase ^= 1; }
         }
+      }
+      if (!dep_ready) {
+        pdl_wait();
+        for (int i = 0; i < issued; ++i)
+          tma_load_2d(smem + (size_t)i * STAGE_BYTES + W_STAGE_BYTES, &map_x, &full[i], pend_kb[i] * TILE_K, pend_t0[i]);
       }
       if (!ok) {
         if (!*abort_flag) atomicOr(p.err, IERT_ERR_WAIT_EXPIRED);
@@ -173,6 +190,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     }
   } else {
     // ---------------- epilogue: 4 warps, warp w reads TMEM lanes 32*(w%4).. ----------------
+    pdl_wait();
     const int q = warp & 3;
     const int n_local = q * 32 + lane;
     int acc = 0;
@@ -320,7 +338,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, GemmParams p, int grid,
       return iert_check_launch("gemm_tc attribute");
     configured = true;
   }
-  gemm_tc_kernel<BT><<<grid, THREADS, smem, stream>>>(mw, mx, p);
+  launch_dep(gemm_tc_kernel<BT>, dim3(grid), dim3(THREADS), smem, stream, mw, mx, p);
   return iert_check_launch("gemm_tc");
 }
 

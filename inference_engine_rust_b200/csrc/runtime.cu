@@ -7,6 +7,11 @@
 
 static thread_local char g_last_error[512] = "";
 
+int iert_pdl_enabled = 1;
+
+// Programmatic dependent launch on (1, default) or off (0) for every later launch.
+IERT_API void iert_set_pdl(int on) { iert_pdl_enabled = on ? 1 : 0; }
+
 int iert_check_launch(const char* what) {
   cudaError_t e = cudaGetLastError();
   if (e == cudaSuccess) return IERT_OK;

@@ -41,6 +41,8 @@ argmax_kernel(const float* __restrict__ logits, int vocab, long long ld, int* __
               int* __restrict__ err) {
   __shared__ float vs[32];
   __shared__ int is[32];
+  pdl_wait();
+  pdl_launch_dependents();
   const float* row = logits + (long long)blockIdx.x * ld;
   float best = -INFINITY;
   int best_i = 0x7fffffff;
@@ -83,6 +85,8 @@ temperature_kernel(const float* __restrict__ logits, int vocab, long long ld, fl
   __shared__ float scratch[33];
   __shared__ float warp_tot[32];
   __shared__ int owner;
+  pdl_wait();
+  pdl_launch_dependents();
   const float* row = logits + (long long)blockIdx.x * ld;
   const int chunk = (vocab + THREADS - 1) / THREADS;
   const int lo = min(vocab, (int)threadIdx.x * chunk), hi = min(vocab, lo + chunk);
@@ -158,7 +162,7 @@ IERT_API int iert_sample_greedy(const float* logits, int rows, int vocab, long l
                                 int* err, cudaStream_t stream) {
   if (rows <= 0) return IERT_OK;
   if (vocab <= 0) return IERT_BAD_ARGUMENT;
-  argmax_kernel<<<rows, THREADS, 0, stream>>>(logits, vocab, ld, out, err);
+  launch_dep(argmax_kernel, rows, THREADS, 0, stream, logits, vocab, ld, out, err);
   return iert_check_launch("sample_greedy");
 }
 
@@ -168,7 +172,7 @@ IERT_API int iert_sample_temperature(const float* logits, int rows, int vocab, l
                                      int* err, cudaStream_t stream) {
   if (rows <= 0) return IERT_OK;
   if (vocab <= 0 || !(temperature > 0.f) || !isfinite(temperature)) return IERT_BAD_ARGUMENT;
-  temperature_kernel<<<rows, THREADS, 0, stream>>>(logits, vocab, ld, temperature, seed,
+  launch_dep(temperature_kernel, rows, THREADS, 0, stream, logits, vocab, ld, temperature, seed,
                                                    request_ids, step_ids, out, err);
   return iert_check_launch("sample_temperature");
 }

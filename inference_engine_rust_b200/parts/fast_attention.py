@@ -5,7 +5,7 @@ import torch
 
 from ..csrc import bindings as B
 
-_TARGET_CTAS = 6 * 148           # several resident CTAs per SM: the kernel hides latency by occupancy
+_TARGET_CTAS = 3 * 148           # three resident CTAs per SM keep enough page loads in flight
 _MAX_SPLITS = 16
 
 
@@ -13,8 +13,7 @@ def decode_splits(n_tokens: int, kv_heads: int, group: int) -> int:
     """How many ways the keys of each sequence are split: enough CTAs to fill the GPU at
     small batches, one split once the batch alone does.  Depends on the (padded) batch size
     only, never on the sequences' lengths, so a captured graph stays valid."""
-    gt = 8 if group >= 8 else 4 if group > 2 else group
-    slices = -(-group // gt)
+    slices = -(-group // 8)
     ctas = max(1, n_tokens * kv_heads * slices)
     return max(1, min(_MAX_SPLITS, -(-_TARGET_CTAS // ctas)))
 
@@ -28,6 +27,9 @@ def apply(attn, qkv, out, ctx, cache_view, from_cache: bool) -> bool:
         splits = decode_splits(ctx.n_tokens, attn.kv_heads, attn.heads // attn.kv_heads)
         n = B.attention_decode_scratch_floats(ctx.n_tokens, attn.heads, attn.head_dim, splits)
         scratch = rt.workspace.take("attn.decode_scratch", (n,), torch.float32)
+        if B.attention_decode_tc(qkv, out, ctx.batch, cache_view.struct, attn.heads, attn.scale, splits,
+                                 scratch, rt.err, ctx.stream):
+            return True
         return B.attention_decode(qkv, out, ctx.batch, cache_view.struct, attn.heads, attn.scale, splits,
                                   scratch, rt.err, ctx.stream)
     if not from_cache:

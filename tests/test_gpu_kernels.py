@@ -304,6 +304,14 @@ def test_attention_decode_batch_with_padding(heads, kvh, hd, window):
         assert err.item() == 0
         assert torch.isfinite(fast).all() and float(fast[3].abs().sum()) == 0     # padding row: zeros
         assert torch.allclose(fast.float(), plain.float(), atol=2e-2, rtol=2e-2), f"{splits} splits"
+        # the tensor-core variant of the same kernel
+        scratch.fill_(float("nan"))
+        tc = torch.full_like(plain, float("nan"))
+        assert b.attention_decode_tc(nxt, tc, view1, kvs, heads, scale, splits, scratch, err, stream())
+        assert err.item() == 0
+        assert torch.isfinite(tc).all() and float(tc[3].abs().sum()) == 0
+        assert torch.allclose(tc.float(), plain.float(), atol=2e-2, rtol=2e-2), \
+            f"tensor cores, {splits} splits: {(tc.float() - plain.float()).abs().max().item():.4g}"
 
 
 def test_sampling_greedy_and_errors():
