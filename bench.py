@@ -132,7 +132,7 @@ def main() -> int:
     load_s = time.time() - t0
     batches = [a.batch] + [int(b) for b in a.points.split(",") if b.strip()]
     biggest = max(batches)
-    per_seq = -(-(a.context + a.steps + a.warmup + 8) // 64) * 64
+    per_seq = -(-(a.context + 2 * (a.steps + a.warmup) + 8) // 64) * 64     # the timed run and the end-to-end run
     session = model.session(max_tokens=biggest * per_seq, max_sequences=biggest, max_seq_len=MAX_CONTEXT)
     eng = session.engine
     sampler = Sampler(SamplingParams(temperature=0.0), eng.rt.err)

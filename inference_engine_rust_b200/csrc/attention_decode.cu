@@ -47,8 +47,8 @@ attention_decode_kernel(DecodeParams p, IertBatchView b, IertKvView c) {
   float* o_s = p_s + WARPS * KEY_BLOCK * GT;      // [WARPS][GT][hd]
   float* ml_s = o_s + WARPS * GT * hd;            // [WARPS][GT][2]
 
-  pdl_wait();
-  pdl_launch_dependents();
+  pdl_launch_dependents();     // the next kernel may start its preamble now
+  pdl_wait();                  // everything below may depend on the kernel before
   const int split = blockIdx.x, t = blockIdx.z;
   const int kvh = blockIdx.y / p.slices, slice = blockIdx.y % p.slices;
   const int group = p.heads / c.kv_heads;
@@ -218,8 +218,8 @@ attention_decode_kernel(DecodeParams p, IertBatchView b, IertKvView c) {
 
 // One block per (token, head): merge the splits in split order, normalise, write bf16.
 __global__ void attention_decode_combine_kernel(DecodeParams p, int hd) {
-  pdl_wait();
-  pdl_launch_dependents();
+  pdl_launch_dependents();     // the next kernel may start its preamble now
+  pdl_wait();                  // everything below may depend on the kernel before
   const int t = blockIdx.x, head = blockIdx.y;
   const float* po = p.part_out + ((size_t)t * p.heads + head) * p.splits * hd;
   const float* pml = p.part_ml + ((size_t)t * p.heads + head) * p.splits * 2;

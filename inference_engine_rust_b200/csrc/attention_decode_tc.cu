@@ -86,8 +86,8 @@ attention_decode_tc_kernel(DecodeTcParams p, IertBatchView b, IertKvView c) {
   auto v_tile = [&](int i) { return smem + (size_t)(2 + i) * TILE_BYTES; };
   uint8_t* q_tile = smem + 4 * TILE_BYTES;               // [16][ROW_BYTES]
 
-  pdl_wait();
-  pdl_launch_dependents();
+  pdl_launch_dependents();     // the next kernel may start its preamble now
+  pdl_wait();                  // everything below may depend on the kernel before
   const int split = blockIdx.x, t = blockIdx.z;
   const int kvh = blockIdx.y / p.slices, slice = blockIdx.y % p.slices;
   const int group = p.heads / c.kv_heads;
@@ -229,8 +229,8 @@ attention_decode_tc_kernel(DecodeTcParams p, IertBatchView b, IertKvView c) {
 
 // One block per (token, head): merge the splits in split order, normalise, write bf16.
 __global__ void attention_decode_tc_combine_kernel(DecodeTcParams p) {
-  pdl_wait();
-  pdl_launch_dependents();
+  pdl_launch_dependents();     // the next kernel may start its preamble now
+  pdl_wait();                  // everything below may depend on the kernel before
   const int t = blockIdx.x, head = blockIdx.y;
   const float* po = p.part_out + ((size_t)t * p.heads + head) * p.splits * HD;
   const float* pml = p.part_ml + ((size_t)t * p.heads + head) * p.splits * 2;

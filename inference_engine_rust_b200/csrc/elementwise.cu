@@ -13,8 +13,8 @@ template <typename TW>
 __global__ void embed_gather_kernel(const TW* __restrict__ table, const int* __restrict__ ids,
                                     float* __restrict__ x, int hidden, int vocab, float scale,
                                     int* __restrict__ err) {
-  pdl_wait();
-  pdl_launch_dependents();
+  pdl_launch_dependents();     // the next kernel may start its preamble now
+  pdl_wait();                  // everything below may depend on the kernel before
   const int t = blockIdx.x;
   const int id = ids[t];
   float* row = x + (size_t)t * hidden;
@@ -51,8 +51,8 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const TW* __restrict
                                TO* __restrict__ out, const int* __restrict__ rows_idx,
                                int hidden, float eps) {
   __shared__ float scratch[33];
-  pdl_wait();
-  pdl_launch_dependents();
+  pdl_launch_dependents();     // the next kernel may start its preamble now
+  pdl_wait();                  // everything below may depend on the kernel before
   const int r = blockIdx.x;
   const int src_row = rows_idx ? rows_idx[r] : r;
   const float* xr = x + (size_t)src_row * hidden;
@@ -75,14 +75,14 @@ __global__ void rmsnorm_reg_kernel(const float* __restrict__ x, const TW* __rest
                                    TO* __restrict__ out, const int* __restrict__ rows_idx,
                                    int hidden, float eps) {
   __shared__ float scratch[33];
+  pdl_launch_dependents();     // the next kernel may start its preamble now
   float wv[NPT], xv[NPT];
 #pragma unroll
   for (int k = 0; k < NPT; ++k) {
     const int i = threadIdx.x + k * blockDim.x;
     wv[k] = i < hidden ? to_f32(w[i]) : 0.f;
   }
-  pdl_wait();
-  pdl_launch_dependents();
+  pdl_wait();                  // everything below may depend on the kernel before
   const int r = blockIdx.x;
   const int src_row = rows_idx ? rows_idx[r] : r;
   const float* xr = x + (size_t)src_row * hidden;
@@ -144,8 +144,8 @@ __global__ void rope_kv_store_kernel(T* __restrict__ qkv, IertBatchView b, IertK
                                      const float* __restrict__ inv_freq, int heads,
                                      int rotary_dim, int pairing, int write_cache,
                                      int* __restrict__ err) {
-  pdl_wait();
-  pdl_launch_dependents();
+  pdl_launch_dependents();     // the next kernel may start its preamble now
+  pdl_wait();                  // everything below may depend on the kernel before
   const int t = blockIdx.x;
   const int head = blockIdx.y;
   const int s = b.tok_seq[t];
@@ -222,8 +222,8 @@ __device__ __forceinline__ float stable_sigmoid(float x) {
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter,
                                 size_t total) {
-  pdl_wait();
-  pdl_launch_dependents();
+  pdl_launch_dependents();     // the next kernel may start its preamble now
+  pdl_wait();                  // everything below may depend on the kernel before
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (size_t)gridDim.x * blockDim.x) {
     const size_t t = idx / inter;

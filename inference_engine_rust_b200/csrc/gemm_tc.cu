@@ -22,6 +22,7 @@
 #include "sm100.cuh"
 
 #include <mutex>
+#include <stdlib.h>
 #include <unordered_map>
 
 using namespace iert;
@@ -232,12 +233,36 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (*ticket_s == p.splits - 1) {             // the last split of this tile: add in split order
           __threadfence();
-          if (n < p.N) {
-            const float* base = p.ws + ((size_t)tile * p.splits * BT) * TILE_N + n_local;
-            for (int t = 0; t < t_valid; ++t) {
-              float sum = 0.f;
-              for (int s = 0; s < p.splits; ++s) sum += __ldcg(base + ((size_t)s * BT + t) * TILE_N);
-              write_out_any(p, t0 + t, n, sum);
+          // 128 threads: 32 four-column chunks x 4 token rows per pass; all loads of a pass are
+          // issued before any is used, so a pass costs one round trip to L2
+          const int et = (int)threadIdx.x - 64, c4 = et & 31, tr = et >> 5;
+          const float* base = p.ws + ((size_t)tile * p.splits * BT) * TILE_N;
+          for (int t = tr; t < t_valid; t += 8) {
+            float4 acc[2] = {make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f)};
+            for (int s0 = 0; s0 < p.splits; s0 += 4) {
+              float4 v[2][4];
+#pragma unroll
+              for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                  v[h][u] = (s0 + u < p.splits && t + 4 * h < t_valid)
+                                ? __ldcg(reinterpret_cast<const float4*>(base + ((size_t)(s0 + u) * BT + t + 4 * h) * TILE_N) + c4)
+                                : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+              for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                  acc[h].x += v[h][u].x; acc[h].y += v[h][u].y; acc[h].z += v[h][u].z; acc[h].w += v[h][u].w;
+                }
+            }
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              if (t + 4 * h >= t_valid) break;
+              const int nn = n0 + c4 * 4, tok = t0 + t + 4 * h;
+              const float r[4] = {acc[h].x, acc[h].y, acc[h].z, acc[h].w};
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+                if (nn + i < p.N) write_out_any(p, tok, nn + i, r[i]);
             }
           }
           if (threadIdx.x == 64) p.counters[tile] = 0;
@@ -380,7 +405,8 @@ IERT_API int iert_gemm_tc(const void* x, long long ldx, const void* w, long long
   const int ctas_per_sm = bt <= 64 ? 2 : 1;
   const int slots = sm_count() * ctas_per_sm;
   const int smem_budget = (ctas_per_sm == 2 ? 113 : 226) * 1024 - 2048;
-  int stages = force_stages ? force_stages : smem_budget / stage_bytes;
+  static const int env_stages = getenv("IERT_GEMM_STAGES") ? atoi(getenv("IERT_GEMM_STAGES")) : 0;
+  int stages = force_stages ? force_stages : (env_stages && bt <= 64 ? env_stages : smem_budget / stage_bytes);
   if (stages > 12) stages = 12;
   if (stages < 2 || (size_t)stages * stage_bytes + 1280 > 227 * 1024) return IERT_BAD_ARGUMENT;
   p.stages = stages;

@@ -41,8 +41,8 @@ argmax_kernel(const float* __restrict__ logits, int vocab, long long ld, int* __
               int* __restrict__ err) {
   __shared__ float vs[32];
   __shared__ int is[32];
-  pdl_wait();
-  pdl_launch_dependents();
+  pdl_launch_dependents();     // the next kernel may start its preamble now
+  pdl_wait();                  // everything below may depend on the kernel before
   const float* row = logits + (long long)blockIdx.x * ld;
   float best = -INFINITY;
   int best_i = 0x7fffffff;
@@ -85,8 +85,8 @@ temperature_kernel(const float* __restrict__ logits, int vocab, long long ld, fl
   __shared__ float scratch[33];
   __shared__ float warp_tot[32];
   __shared__ int owner;
-  pdl_wait();
-  pdl_launch_dependents();
+  pdl_launch_dependents();     // the next kernel may start its preamble now
+  pdl_wait();                  // everything below may depend on the kernel before
   const float* row = logits + (long long)blockIdx.x * ld;
   const int chunk = (vocab + THREADS - 1) / THREADS;
   const int lo = min(vocab, (int)threadIdx.x * chunk), hi = min(vocab, lo + chunk);
