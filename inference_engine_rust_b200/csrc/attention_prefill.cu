@@ -3,7 +3,7 @@
 // scores, softmax and accumulation, in one pass over the keys (running maximum and sum).
 // Compiled once per head size: -DHEAD_DIM=<multiple of 16, up to 256>.
 //
-//   grid (query tiles, heads, sequences); a CTA of 4 warps owns 64 consecutive queries of one
+//   grid (query tiles, heads, sequences); a CTA of 8 warps owns 128 consecutive queries of one
 //   head of one sequence, each warp 16 of them.  Key/value tiles of 64 positions come from
 //   the step's own packed projection (a prompt starts at position 0, so every key it attends
 //   to is in the step) through cp.async into double-buffered shared memory whose rows are
@@ -24,9 +24,10 @@ namespace {
 
 constexpr int HD = HEAD_DIM;
 static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head size must be a multiple of 16 up to 256");
-constexpr int BM = 64, BN = 64, WARPS = 4, THREADS = WARPS * 32;
+constexpr int BN = 64, WARPS = 8, BM = WARPS * 16, THREADS = WARPS * 32;
 constexpr int ROW_BYTES = HD * 2 + 16;                 // padded row of a tile in shared memory
-constexpr int TILE_BYTES = BN * ROW_BYTES;
+constexpr int TILE_BYTES = BN * ROW_BYTES;                // a key or value tile
+constexpr int Q_TILE_BYTES = BM * ROW_BYTES;
 constexpr int KSTEPS = HD / 16;                        // k-steps of Q.K^T; also 16-wide column pairs of the output
 constexpr bool Q_IN_REGS = HD <= 128;
 
@@ -54,15 +55,22 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 2^x on the special-function unit (fp32 in, fp32 out, about 2 ulp).
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// Copy `rows` x HD bf16 (row stride `ld` elements) into a padded tile; rows >= n_valid become zeros.
+// Copy ROWS x HD bf16 (row stride `ld` elements) into a padded tile; rows >= n_valid become zeros.
+template <int ROWS>
 __device__ __forceinline__ void load_tile(uint8_t* tile, const __nv_bfloat16* src, long long ld, int n_valid) {
   constexpr int CHUNKS = HD / 8;                       // 16-byte chunks per row
-  for (int i = threadIdx.x; i < BN * CHUNKS; i += THREADS) {
+  for (int i = threadIdx.x; i < ROWS * CHUNKS; i += THREADS) {
     const int r = i / CHUNKS, c = i % CHUNKS;
     const bool ok = r < n_valid;
     cp_async16(tile + r * ROW_BYTES + c * 16, src + (ok ? (long long)r * ld + c * 8 : 0), ok);
@@ -74,8 +82,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* _
                          IertBatchView b, int heads, int kv_heads, int window, float scale_log2e) {
   extern __shared__ __align__(16) uint8_t smem[];
   uint8_t* q_tile = smem;
-  auto k_tile = [&](int i) { return smem + (1 + i) * TILE_BYTES; };
-  auto v_tile = [&](int i) { return smem + (3 + i) * TILE_BYTES; };
+  auto k_tile = [&](int i) { return smem + Q_TILE_BYTES + i * TILE_BYTES; };
+  auto v_tile = [&](int i) { return smem + Q_TILE_BYTES + (2 + i) * TILE_BYTES; };
 
   const int s = blockIdx.z, head = blockIdx.y;
   if (b.slot_ids[s] < 0) return;
@@ -95,9 +103,9 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* _
   const int j_lo = window > 0 ? max(0, i0 - (window - 1)) : 0;
   const int kt_lo = j_lo / BN, kt_hi = i_hi / BN;       // key tiles to visit, inclusive
 
-  load_tile(q_tile, q_src, ld, len - i0);
-  load_tile(k_tile(0), k_src + (long long)kt_lo * BN * ld, ld, len - kt_lo * BN);
-  load_tile(v_tile(0), v_src + (long long)kt_lo * BN * ld, ld, len - kt_lo * BN);
+  load_tile<BM>(q_tile, q_src, ld, len - i0);
+  load_tile<BN>(k_tile(0), k_src + (long long)kt_lo * BN * ld, ld, len - kt_lo * BN);
+  load_tile<BN>(v_tile(0), v_src + (long long)kt_lo * BN * ld, ld, len - kt_lo * BN);
   cp_async_commit();
 
   uint32_t q_frag[Q_IN_REGS ? KSTEPS : 1][4];
@@ -110,8 +118,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* _
   for (int kt = kt_lo; kt <= kt_hi; ++kt) {
     const int buf = (kt - kt_lo) & 1;
     if (kt < kt_hi) {                                   // prefetch the next tile into the other buffer
-      load_tile(k_tile(buf ^ 1), k_src + (long long)(kt + 1) * BN * ld, ld, len - (kt + 1) * BN);
-      load_tile(v_tile(buf ^ 1), v_src + (long long)(kt + 1) * BN * ld, ld, len - (kt + 1) * BN);
+      load_tile<BN>(k_tile(buf ^ 1), k_src + (long long)(kt + 1) * BN * ld, ld, len - (kt + 1) * BN);
+      load_tile<BN>(v_tile(buf ^ 1), v_src + (long long)(kt + 1) * BN * ld, ld, len - (kt + 1) * BN);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -169,7 +177,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* _
     for (int r = 0; r < 2; ++r) {
       m_new[r] = fmaxf(m_new[r], __shfl_xor_sync(0xffffffffu, m_new[r], 1));
       m_new[r] = fmaxf(m_new[r], __shfl_xor_sync(0xffffffffu, m_new[r], 2));
-      alpha[r] = m_row[r] == -INFINITY ? 0.f : exp2f(m_row[r] - m_new[r]);
+      alpha[r] = m_row[r] == -INFINITY ? 0.f : fast_exp2(m_row[r] - m_new[r]);
       m_row[r] = m_new[r];
       l_row[r] *= alpha[r];
     }
@@ -178,7 +186,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* _
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const float mr = m_new[e >> 1];
-        const float pv = (sc[n][e] == -INFINITY || mr == -INFINITY) ? 0.f : exp2f(sc[n][e] - mr);
+        const float pv = (sc[n][e] == -INFINITY || mr == -INFINITY) ? 0.f : fast_exp2(sc[n][e] - mr);
         sc[n][e] = pv;
         l_row[e >> 1] += pv;                            // this thread's share; reduced over the quad at the end
       }
@@ -236,7 +244,7 @@ IERT_API int iert_attention_prefill(const void* qkv, void* out, const IertBatchV
   if (batch->n_tokens <= 0 || max_q_len <= 0) return IERT_OK;
   if (heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || heads > 65535 || batch->n_seqs > 65535)
     return IERT_BAD_ARGUMENT;
-  const size_t smem = 5 * (size_t)TILE_BYTES;
+  const size_t smem = (size_t)Q_TILE_BYTES + 4 * (size_t)TILE_BYTES;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(attention_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {

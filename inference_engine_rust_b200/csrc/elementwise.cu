@@ -132,8 +132,9 @@ IERT_API int iert_rmsnorm(const float* x, const void* w, int w_dtype, void* out,
 // ---------------------------------------------------------------------------------------
 // Rotary encoding of the query and key heads of a packed [T, (heads + 2*kv_heads)*head_dim]
 // projection, in place, fused with the write of the rotated keys and the values into the
-// paged cache.  One block per (token, head); heads [0, heads) are queries, the next
-// kv_heads are keys, the last kv_heads are values.
+// paged cache.  A block serves one token and a run of its heads (all of them when the step
+// has many tokens); heads [0, heads) are queries, the next kv_heads are keys, the last
+// kv_heads are values.  The token's cos/sin table is computed once per block.
 //   angle(pos, k) = pos * inv_freq[k] in fp32; (a, b) -> (a cos - b sin, a sin + b cos)
 // Reference: src/ops/rope.rs:40-57 (rotation), src/layers/attention.rs:314-352 (order:
 // rotate, then append), :518-520 (decode position = cache length before the append).
@@ -143,49 +144,52 @@ template <typename T>
 __global__ void rope_kv_store_kernel(T* __restrict__ qkv, IertBatchView b, IertKvView c,
                                      const float* __restrict__ inv_freq, int heads,
                                      int rotary_dim, int pairing, int write_cache,
-                                     int* __restrict__ err) {
+                                     int heads_per_block, int* __restrict__ err) {
+  extern __shared__ float cs[];                 // [rotary_dim / 2] cos, then [rotary_dim / 2] sin
   pdl_launch_dependents();     // the next kernel may start its preamble now
-  pdl_wait();                  // everything below may depend on the kernel before
   const int t = blockIdx.x;
-  const int head = blockIdx.y;
+  const int hd = c.head_dim, nkv = c.kv_heads;
+  const int half = rotary_dim / 2;
+  const int total_heads = heads + 2 * nkv;
+  pdl_wait();                  // everything below may depend on the kernel before
   const int s = b.tok_seq[t];
   if (s < 0) return;
   const int slot = b.slot_ids[s];
   if (slot < 0) return;
-  const int hd = c.head_dim, nkv = c.kv_heads;
   const int q_begin = b.cu_q[s], q_len = b.cu_q[s + 1] - q_begin;
   const int pos = b.pos0[s] + (t - q_begin);
   const int final_len = b.pos0[s] + q_len;
-  T* vec = qkv + ((size_t)t * (heads + 2 * nkv) + head) * hd;
-
-  const bool is_q = head < heads;
-  const bool is_k = !is_q && head < heads + nkv;
-  const int kvh = is_q ? 0 : (is_k ? head - heads : head - heads - nkv);
-  T* dst = nullptr;
-  if (!is_q && write_cache && pos >= final_len - c.ring_pages * c.page_tokens) {
-    const long long off = kv_row_offset(c, slot, pos, kvh, err);
-    if (off >= 0) dst = (T*)(is_k ? c.k : c.v) + off;
+  for (int k = threadIdx.x; k < half; k += blockDim.x) {   // the token's angles, once for all heads
+    float sn, cs_;
+    sincosf((float)pos * inv_freq[k], &sn, &cs_);
+    cs[k] = cs_;
+    cs[half + k] = sn;
   }
-
-  if (is_q || is_k) {
-    const int half = rotary_dim / 2;
-    for (int k = threadIdx.x; k < half; k += blockDim.x) {
-      const int i0 = pairing == IERT_PAIR_HALF ? k : 2 * k;
-      const int i1 = pairing == IERT_PAIR_HALF ? k + half : 2 * k + 1;
-      const float angle = (float)pos * inv_freq[k];
-      float sn, cs;
-      sincosf(angle, &sn, &cs);
-      const float a = to_f32(vec[i0]), bb = to_f32(vec[i1]);
-      const T r0 = from_f32<T>(a * cs - bb * sn);
-      const T r1 = from_f32<T>(a * sn + bb * cs);
-      vec[i0] = r0;
-      vec[i1] = r1;
-      if (dst) { dst[i0] = r0; dst[i1] = r1; }
-    }
-    if (dst)
-      for (int i = rotary_dim + threadIdx.x; i < hd; i += blockDim.x) dst[i] = vec[i];
-  } else if (dst) {
-    for (int i = threadIdx.x; i < hd; i += blockDim.x) dst[i] = vec[i];
+  __syncthreads();
+  const bool store = write_cache && pos >= final_len - c.ring_pages * c.page_tokens;
+  T* row = qkv + (size_t)t * total_heads * hd;
+  // this block's heads: [h0, h1) of [queries | keys | values]
+  const int h0 = blockIdx.y * heads_per_block, h1 = min(total_heads, h0 + heads_per_block);
+  const int rot_end = min(h1, heads + nkv);            // heads below this index are rotated
+  for (int i = threadIdx.x; i < (rot_end - h0) * half; i += blockDim.x) {
+    const int head = h0 + i / half, k = i % half;
+    const int i0 = pairing == IERT_PAIR_HALF ? k : 2 * k;
+    const int i1 = pairing == IERT_PAIR_HALF ? k + half : 2 * k + 1;
+    T* vec = row + (size_t)head * hd;
+    const float a = to_f32(vec[i0]), bb = to_f32(vec[i1]);
+    vec[i0] = from_f32<T>(a * cs[k] - bb * cs[half + k]);
+    vec[i1] = from_f32<T>(a * cs[half + k] + bb * cs[k]);
+  }
+  const int kv0 = max(h0, heads);                       // this block's key and value heads
+  if (!store || kv0 >= h1) return;
+  __syncthreads();                                      // the rotated keys are read back below
+  for (int i = threadIdx.x; i < (h1 - kv0) * hd; i += blockDim.x) {
+    const int hh = kv0 + i / hd - heads, d = i % hd;    // hh in [0, 2 nkv): keys then values
+    const bool is_k = hh < nkv;
+    const int kvh = is_k ? hh : hh - nkv;
+    const long long off = kv_row_offset(c, slot, pos, kvh, err);
+    if (off < 0) continue;
+    ((T*)(is_k ? c.k : c.v))[off + d] = row[(size_t)(heads + hh) * hd + d];
   }
 }
 
@@ -197,14 +201,18 @@ IERT_API int iert_rope_kv_store(void* qkv, int dtype, const IertBatchView* batch
   if (rotary_dim < 0 || rotary_dim > cache->head_dim || (rotary_dim & 1) || cache->dtype != dtype)
     return IERT_BAD_ARGUMENT;
   if (pairing != IERT_PAIR_HALF && pairing != IERT_PAIR_INTERLEAVED) return IERT_BAD_ARGUMENT;
+  // few tokens: spread the heads over many blocks; many tokens: one block per token
   const int total_heads = heads + 2 * cache->kv_heads;
-  if (total_heads > 65535) return IERT_BAD_ARGUMENT;
-  dim3 grid(batch->n_tokens, total_heads);
-  const int threads = cache->head_dim >= 128 ? 64 : 32;
+  const int heads_per_block = batch->n_tokens >= 512 ? total_heads : (total_heads >= 8 ? 8 : total_heads);
+  const int work = heads_per_block * (rotary_dim / 2 > 0 ? rotary_dim / 2 : 1);
+  const int threads = work >= 2048 ? 256 : work >= 512 ? 128 : 64;
+  const size_t smem = (size_t)rotary_dim * sizeof(float);
+  if (smem > 48 * 1024) return IERT_BAD_ARGUMENT;
+  dim3 grid(batch->n_tokens, (total_heads + heads_per_block - 1) / heads_per_block);
   if (dtype == IERT_F32)
-    launch_dep(rope_kv_store_kernel<float>, grid, threads, 0, stream, (float*)qkv, *batch, *cache, inv_freq, heads, rotary_dim, pairing, write_cache, err);
+    launch_dep(rope_kv_store_kernel<float>, grid, dim3(threads), smem, stream, (float*)qkv, *batch, *cache, inv_freq, heads, rotary_dim, pairing, write_cache, heads_per_block, err);
   else if (dtype == IERT_BF16)
-    launch_dep(rope_kv_store_kernel<__nv_bfloat16>, grid, threads, 0, stream, (__nv_bfloat16*)qkv, *batch, *cache, inv_freq, heads, rotary_dim, pairing, write_cache, err);
+    launch_dep(rope_kv_store_kernel<__nv_bfloat16>, grid, dim3(threads), smem, stream, (__nv_bfloat16*)qkv, *batch, *cache, inv_freq, heads, rotary_dim, pairing, write_cache, heads_per_block, err);
   else
     return IERT_BAD_ARGUMENT;
   return iert_check_launch("rope_kv_store");
@@ -234,12 +242,45 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
   }
 }
 
+// bf16, 8 elements (16 bytes) per thread; `inter` a multiple of 8.
+__global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out,
+                                       int inter, size_t total8) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int per_row = inter / 8;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total8;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / per_row;
+    const int i = (int)(idx - t * per_row) * 8;
+    const uint4 g4 = *reinterpret_cast<const uint4*>(gu + t * 2 * inter + i);
+    const uint4 u4 = *reinterpret_cast<const uint4*>(gu + t * 2 * inter + inter + i);
+    const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&g4);
+    const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&u4);
+    uint4 o4;
+    __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o4);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 g = __bfloat1622float2(gp[e]), u = __bfloat1622float2(up[e]);
+      op[e] = __floats2bfloat162_rn(g.x * stable_sigmoid(g.x) * u.x, g.y * stable_sigmoid(g.y) * u.y);
+    }
+    *reinterpret_cast<uint4*>(out + t * inter + i) = o4;
+  }
+}
+
 IERT_API int iert_silu_mul(const void* gu, void* out, int dtype, int n_tokens, int inter,
                            cudaStream_t stream) {
   if (n_tokens <= 0) return IERT_OK;
   if (inter <= 0) return IERT_BAD_ARGUMENT;
   const size_t total = (size_t)n_tokens * inter;
   const int threads = 256;
+  if (dtype == IERT_BF16 && inter % 8 == 0 && ((uintptr_t)gu & 15) == 0 && ((uintptr_t)out & 15) == 0) {
+    const size_t total8 = total / 8;
+    const size_t want = (total8 + threads - 1) / threads;
+    const int blocks = (int)(want < 148 * 32 ? want : 148 * 32);
+    launch_dep(silu_mul_bf16x8_kernel, blocks, threads, 0, stream, (const __nv_bfloat16*)gu,
+               (__nv_bfloat16*)out, inter, total8);
+    return iert_check_launch("silu_mul");
+  }
   const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
   if (dtype == IERT_F32)
     launch_dep(silu_mul_kernel<float>, blocks, threads, 0, stream, (const float*)gu, (float*)out, inter, total);

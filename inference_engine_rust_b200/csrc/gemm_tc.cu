@@ -216,9 +216,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           for (int j = 0; j < 16; ++j)
             if (c + j < t_valid) part[(size_t)(c + j) * TILE_N] = v[j];
         } else if (n < p.N) {
+          if (p.mode == MODE_ADD_RESIDUAL) {
+            // all 16 reads of the residual first, then the 16 writes: one memory round trip
+            float* o = (float*)p.out + (long long)(t0 + c) * p.ldo + n;
+            float r[16];
 #pragma unroll
-          for (int j = 0; j < 16; ++j)
-            if (c + j < t_valid) write_out_any(p, t0 + c + j, n, v[j]);
+            for (int j = 0; j < 16; ++j) r[j] = c + j < t_valid ? o[(long long)j * p.ldo] : 0.f;
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (c + j < t_valid) o[(long long)j * p.ldo] = r[j] + v[j];
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (c + j < t_valid) write_out_any(p, t0 + c + j, n, v[j]);
+          }
         }
       }
       tc_fence_before();
