@@ -6,8 +6,8 @@
 //   head are the 16 rows of the MMA tile, so every key and value is read once per group and
 //   the arithmetic is a handful of MMAs per page: the kernel is a stream of page loads.
 //   A CTA walks its share of the sequence's 64-position pages; each page's keys and values
-//   (two contiguous runs of 64 * HEAD_DIM bf16) are fetched with cp.async into double-buffered
-//   shared memory with padded rows (conflict-free ldmatrix); rows outside [j_min, pos] are
+//   (two contiguous runs of 64 * HEAD_DIM bf16) are fetched with cp.async into a three-deep ring
+//   of shared memory with padded rows (conflict-free ldmatrix); rows outside [j_min, pos] are
 //   zero-filled, so memory that was never written cannot reach the arithmetic.
 //   Each of the 4 warps takes 16 of a page's 64 keys with its own running maximum and sum;
 //   the warps are merged through shared memory in warp order at the end, and the split's
@@ -31,6 +31,7 @@ constexpr int PAGE = 64, WARPS = 4, THREADS = WARPS * 32, ROWS = 16;
 constexpr int ROW_BYTES = HD * 2 + 16;
 constexpr int TILE_BYTES = PAGE * ROW_BYTES;
 constexpr int KSTEPS = HD / 16;
+constexpr int NSTAGE = 3;                       // pages in flight per CTA: the one in use and two behind it
 
 struct DecodeTcParams {
   const __nv_bfloat16* qkv;   // [T, (heads + 2 kv_heads) * HD], queries rotated
@@ -82,9 +83,9 @@ __device__ __forceinline__ void load_page(uint8_t* tile, const __nv_bfloat16* sr
 __global__ void __launch_bounds__(THREADS)
 attention_decode_tc_kernel(DecodeTcParams p, IertBatchView b, IertKvView c) {
   extern __shared__ __align__(16) uint8_t smem[];
-  auto k_tile = [&](int i) { return smem + (size_t)i * TILE_BYTES; };
-  auto v_tile = [&](int i) { return smem + (size_t)(2 + i) * TILE_BYTES; };
-  uint8_t* q_tile = smem + 4 * TILE_BYTES;               // [16][ROW_BYTES]
+  auto k_tile = [&](int i) { return smem + (size_t)(2 * i) * TILE_BYTES; };
+  auto v_tile = [&](int i) { return smem + (size_t)(2 * i + 1) * TILE_BYTES; };
+  uint8_t* q_tile = smem + 2 * NSTAGE * TILE_BYTES;      // [16][ROW_BYTES]
 
   pdl_launch_dependents();     // the next kernel may start its preamble now
   pdl_wait();                  // everything below may depend on the kernel before
@@ -128,8 +129,13 @@ attention_decode_tc_kernel(DecodeTcParams p, IertBatchView b, IertKvView c) {
     load_page(k_tile(buf), (const __nv_bfloat16*)c.k + off, lo, hi);
     load_page(v_tile(buf), (const __nv_bfloat16*)c.v + off, lo, hi);
   };
-  if (my_lo < my_hi) issue(my_lo, 0);
-  cp_commit();
+  // one commit group per page, empty groups included, so that "all but the newest NSTAGE - 1
+  // groups have landed" always means "the page about to be used has landed"
+#pragma unroll
+  for (int i = 0; i < NSTAGE - 1; ++i) {
+    if (my_lo + i < my_hi) issue(my_lo + i, i);
+    cp_commit();
+  }
 
   uint32_t qf[KSTEPS][4];
   float o[KSTEPS * 2][4];
@@ -138,9 +144,10 @@ attention_decode_tc_kernel(DecodeTcParams p, IertBatchView b, IertKvView c) {
   float m_row = -INFINITY, l_row = 0.f;          // row g (a head of the group); rows >= 8 are padding
 
   for (int pg = my_lo; pg < my_hi; ++pg) {
-    const int buf = (pg - my_lo) & 1;
-    if (pg + 1 < my_hi) { issue(pg + 1, buf ^ 1); cp_commit(); cp_wait<1>(); }
-    else cp_wait<0>();
+    const int buf = (pg - my_lo) % NSTAGE;
+    if (pg + NSTAGE - 1 < my_hi) issue(pg + NSTAGE - 1, (pg - my_lo + NSTAGE - 1) % NSTAGE);
+    cp_commit();
+    cp_wait<NSTAGE - 1>();
     __syncthreads();
     if (pg == my_lo) {
 #pragma unroll
@@ -276,7 +283,7 @@ IERT_API int iert_attention_decode_tc(const void* qkv, void* out, const IertBatc
   p.part_out = scratch;
   p.part_ml = scratch + (size_t)T * heads * splits * HD;
   if ((long long)cache->kv_heads * p.slices > 65535) return IERT_BAD_ARGUMENT;
-  size_t smem = 4 * (size_t)TILE_BYTES + ROWS * ROW_BYTES;
+  size_t smem = 2 * NSTAGE * (size_t)TILE_BYTES + ROWS * ROW_BYTES;
   const size_t merge = (size_t)(WARPS * 8 * HD + WARPS * 8 * 2) * sizeof(float);
   if (merge > smem) smem = merge;
   static bool configured = false;

@@ -5,7 +5,7 @@ import torch
 
 from ..csrc import bindings as B
 
-_TARGET_CTAS = 3 * 148           # three resident CTAs per SM keep enough page loads in flight
+_RESIDENT_CTAS = 2 * 148         # two CTAs fit an SM (three-page rings of keys and values)
 _MAX_SPLITS = 16
 
 
@@ -15,7 +15,7 @@ def decode_splits(n_tokens: int, kv_heads: int, group: int) -> int:
     only, never on the sequences' lengths, so a captured graph stays valid."""
     slices = -(-group // 8)
     ctas = max(1, n_tokens * kv_heads * slices)
-    return max(1, min(_MAX_SPLITS, -(-_TARGET_CTAS // ctas)))
+    return max(1, min(_MAX_SPLITS, _RESIDENT_CTAS // ctas))      # as many splits as stay one wave
 
 
 def apply(attn, qkv, out, ctx, cache_view, from_cache: bool) -> bool:
