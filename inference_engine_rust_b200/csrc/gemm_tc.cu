@@ -248,26 +248,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           // issued before any is used, so a pass costs one round trip to L2
           const int et = (int)threadIdx.x - 64, c4 = et & 31, tr = et >> 5;
           const float* base = p.ws + ((size_t)tile * p.splits * BT) * TILE_N;
-          for (int t = tr; t < t_valid; t += 8) {
-            float4 acc[2] = {make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f)};
-            for (int s0 = 0; s0 < p.splits; s0 += 4) {
-              float4 v[2][4];
+          for (int t = tr; t < t_valid; t += 16) {      // 4 token rows x 4 splits = 16 loads in flight
+            float4 acc[4];
 #pragma unroll
-              for (int h = 0; h < 2; ++h)
+            for (int h = 0; h < 4; ++h) acc[h] = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int s0 = 0; s0 < p.splits; s0 += 4) {
+              float4 v[4][4];
+#pragma unroll
+              for (int h = 0; h < 4; ++h)
 #pragma unroll
                 for (int u = 0; u < 4; ++u)
                   v[h][u] = (s0 + u < p.splits && t + 4 * h < t_valid)
                                 ? __ldcg(reinterpret_cast<const float4*>(base + ((size_t)(s0 + u) * BT + t + 4 * h) * TILE_N) + c4)
                                 : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-              for (int h = 0; h < 2; ++h)
+              for (int h = 0; h < 4; ++h)
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
                   acc[h].x += v[h][u].x; acc[h].y += v[h][u].y; acc[h].z += v[h][u].z; acc[h].w += v[h][u].w;
                 }
             }
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
+            for (int h = 0; h < 4; ++h) {
               if (t + 4 * h >= t_valid) break;
               const int nn = n0 + c4 * 4, tok = t0 + t + 4 * h;
               const float r[4] = {acc[h].x, acc[h].y, acc[h].z, acc[h].w};
@@ -429,7 +431,8 @@ IERT_API int iert_gemm_tc(const void* x, long long ldx, const void* w, long long
     splits = slots / tiles;
     const int max_by_k = p.kb_total / 4 > 0 ? p.kb_total / 4 : 1;     // at least 4 k-blocks per split
     if (splits > max_by_k) splits = max_by_k;
-    if (splits > 16) splits = 16;
+    const int cap = bt >= 64 ? 4 : bt == 32 ? 8 : 16;   // partial tiles grow with the token tile
+    if (splits > cap) splits = cap;
   }
   if (splits < 1) splits = 1;
   if (splits > p.kb_total) splits = p.kb_total;
