@@ -92,6 +92,9 @@ def _declare(lib) -> None:
     lib.iert_attention_decode.restype = c_int
     lib.iert_attention_decode_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
     lib.iert_attention_decode_scratch_floats.restype = c_longlong
+    lib.iert_gemm_tc_gated.argtypes = [P, c_longlong, P, c_longlong, P, c_longlong, c_int, c_int, c_int, c_int,
+                                       c_int, P, S]
+    lib.iert_gemm_tc_gated.restype = c_int
     lib.iert_gemm_tc_workspace_bytes.restype = c_longlong
     lib.iert_gemm_tc_counter_count.restype = c_int
     for name, args in sigs.items():
@@ -319,4 +322,18 @@ def attention_decode_tc(qkv, out, batch: BatchView, kv: KvView, heads: int, scal
         raise KernelError("attention_decode_tc: the launch failed")
     global launch_count
     launch_count += 2
+    return True
+
+
+def gemm_tc_gated(x, w, act, M: int, err, stream, force_bt: int = 0, force_stages: int = 0) -> bool:
+    """act[:M] = silu(x @ w[:I].T) * (x @ w[I:].T) for w = [gate; up] with 2 I rows, on the tensor
+    cores in one kernel.  Returns False, having launched nothing, when the operands do not meet
+    the kernel's alignment rules."""
+    two_i, K = w.shape
+    status = core().iert_gemm_tc_gated(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), act.data_ptr(),
+                                       act.stride(0), M, two_i // 2, K, force_bt, force_stages,
+                                       err.data_ptr(), stream)
+    if status == 1:
+        return False
+    check(status, "gemm_tc_gated")
     return True

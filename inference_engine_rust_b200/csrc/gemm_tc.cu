@@ -15,6 +15,12 @@
 // (a fixed order: the result does not depend on which CTA finishes last) and writes the
 // output.  No CTA ever waits for another.
 //
+// Gated variant (GATED = true): the weight matrix is [gate; up] stacked by rows, a tile holds
+// 128 gate rows and the 128 up rows that belong to them as ONE 256-row operand on the MMA's N
+// side with 128 tokens on its M side (the full-rate 128 x 256 x 16 instruction), and the
+// epilogue (one token per thread) writes silu(gate) * up: the feed-forward's activation never goes
+// to memory unfused.  It runs whole tiles only (no split-K).
+//
 // Every wait on an mbarrier is bounded; when one runs out the kernel sets
 // IERT_ERR_WAIT_EXPIRED in the error word, drains its own TMA copies, frees its TMEM and
 // returns.
@@ -37,14 +43,14 @@ constexpr int THREADS = 192;
 constexpr int W_STAGE_BYTES = TILE_N * TILE_K * 2;
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 
-enum : int { MODE_STORE = 0, MODE_ADD_RESIDUAL = 1 };
+enum : int { MODE_STORE = 0, MODE_ADD_RESIDUAL = 1, MODE_GATED_SILU = 2 };
 
 struct GemmParams {
   void* out;
   long long ldo;
   int out_dtype;
   int mode;
-  int M, N, K;
+  int M, N, K;        // gated: N = rows of the gate half = columns of the output
   int t_tiles, n_tiles, splits, kb_total, kb_per_split, stages;
   float* ws;          // [tiles][splits][BT][TILE_N] fp32 partials (splits > 1)
   int* counters;      // [tiles] tickets, zero between launches
@@ -70,13 +76,24 @@ __device__ __forceinline__ void write_out_any(const GemmParams& p, int tok, int 
   else write_out<__nv_bfloat16>(p, tok, n, v);
 }
 
-template <int BT>
+__device__ __forceinline__ float silu_mul(float g, float u) {
+  const float sg = g >= 0.f ? 1.0f / (1.0f + __expf(-g)) : __expf(g) / (1.0f + __expf(g));
+  return g * sg * u;
+}
+
+template <int BT, bool GATED>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                const GemmParams p) {
-  constexpr int STAGE_BYTES = W_STAGE_BYTES + BT * TILE_K * 2;
-  constexpr uint32_t ACC_COLS = 2 * BT < 32 ? 32 : 2 * BT;      // two accumulators, power of two >= 32
-  constexpr uint32_t IDESC = instr_desc_bf16(TILE_N, BT);
+  constexpr int NW = GATED ? 2 : 1;                             // weight tiles per stage
+  constexpr int X_OFF = NW * W_STAGE_BYTES;
+  constexpr int STAGE_BYTES = X_OFF + BT * TILE_K * 2;
+  constexpr int ACC_STRIDE = NW * BT;                           // TMEM columns of one accumulator stage
+  static_assert(2 * ACC_STRIDE <= 512, "two accumulator stages must fit tensor memory");
+  constexpr uint32_t ACC_COLS = 2 * ACC_STRIDE < 32 ? 32 : 2 * ACC_STRIDE;   // power of two >= 32
+  // plain: 128 weight rows x BT tokens; gated: BT (= 128) tokens x 256 stacked weight rows
+  constexpr uint32_t IDESC = GATED ? instr_desc_bf16(BT, 2 * TILE_N) : instr_desc_bf16(TILE_N, BT);
+  static_assert(!GATED || BT == 128, "the gated kernel puts 128 tokens on the MMA's M side");
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -125,14 +142,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           if (!dep_ready && issued == stages) {
             pdl_wait();
             for (int i = 0; i < issued; ++i)
-              tma_load_2d(smem + (size_t)i * STAGE_BYTES + W_STAGE_BYTES, &map_x, &full[i], pend_kb[i] * TILE_K, pend_t0[i]);
+              tma_load_2d(smem + (size_t)i * STAGE_BYTES + X_OFF, &map_x, &full[i], pend_kb[i] * TILE_K, pend_t0[i]);
             dep_ready = true;
           }
           if (!wait_or_abort(&empty[stage], phase ^ 1, abort_flag)) { ok = false; break; }
           uint8_t* ws_ = smem + (size_t)stage * STAGE_BYTES;
           mbar_expect_tx(&full[stage], STAGE_BYTES);
           tma_load_2d(ws_, &map_w, &full[stage], kb * TILE_K, n0);
-          if (dep_ready) tma_load_2d(ws_ + W_STAGE_BYTES, &map_x, &full[stage], kb * TILE_K, t0);
+          if (GATED) tma_load_2d(ws_ + W_STAGE_BYTES, &map_w, &full[stage], kb * TILE_K, p.N + n0);   // the up rows
+          if (dep_ready) tma_load_2d(ws_ + X_OFF, &map_x, &full[stage], kb * TILE_K, t0);
           else { pend_kb[issued] = kb; pend_t0[issued] = t0; }
           ++issued;
           if (++stage == stages) { stage = 0; phase ^= 1; }
@@ -141,7 +159,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       if (!dep_ready) {
         pdl_wait();
         for (int i = 0; i < issued; ++i)
-          tma_load_2d(smem + (size_t)i * STAGE_BYTES + W_STAGE_BYTES, &map_x, &full[i], pend_kb[i] * TILE_K, pend_t0[i]);
+          tma_load_2d(smem + (size_t)i * STAGE_BYTES + X_OFF, &map_x, &full[i], pend_kb[i] * TILE_K, pend_t0[i]);
       }
       if (!ok) {
         if (!*abort_flag) atomicOr(p.err, IERT_ERR_WAIT_EXPIRED);
@@ -167,15 +185,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const int kb0 = split * p.kb_per_split, kb1 = min(p.kb_total, kb0 + p.kb_per_split);
         if (!wait_or_abort(&acc_empty[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BT);
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * ACC_STRIDE);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!wait_or_abort(&full[stage], phase, abort_flag)) { ok = false; break; }
           tc_fence_after();
           const uint32_t w_addr = smem_addr(smem + (size_t)stage * STAGE_BYTES);
-          const uint64_t da = smem_desc_k128(w_addr), db = smem_desc_k128(w_addr + W_STAGE_BYTES);
+          const uint64_t da = smem_desc_k128(w_addr), db = smem_desc_k128(w_addr + X_OFF);
 #pragma unroll
-          for (int ks = 0; ks < TILE_K / UMMA_K; ++ks)   // 32 bytes further along K per step
-            umma_bf16(d_tmem, da + 2 * ks, db + 2 * ks, IDESC, (kb > kb0 || ks > 0) ? 1u : 0u);
+          for (int ks = 0; ks < TILE_K / UMMA_K; ++ks) { // 32 bytes further along K per step
+            if (GATED)   // tokens on the M side, the 256 stacked weight rows (gate, up) on the N side
+              umma_bf16(d_tmem, db + 2 * ks, da + 2 * ks, IDESC, (kb > kb0 || ks > 0) ? 1u : 0u);
+            else
+              umma_bf16(d_tmem, da + 2 * ks, db + 2 * ks, IDESC, (kb > kb0 || ks > 0) ? 1u : 0u);
+          }
           umma_commit(&empty[stage]);
           if (++stage == stages) { stage = 0; phase ^= 1; }
         }
@@ -204,14 +226,41 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       const int t_valid = min(BT, p.M - t0);
       if (!wait_or_abort(&acc_full[acc], acc_phase, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BT);
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * ACC_STRIDE);
       float* part = p.splits > 1 ? p.ws + ((size_t)(tile * p.splits + split) * BT) * TILE_N + n_local : nullptr;
+      if (GATED) {
+        // lane = token, columns [0, 128) = gate rows, [128, 256) = their up rows
+        const int tok = t0 + n_local;
 #pragma unroll 1
-      for (int c = 0; c < BT; c += 16) {
+        for (int c = 0; c < TILE_N; c += 16) {
+          float v[16], u[16];
+          tmem_ld16(taddr + c, v);
+          tmem_ld16(taddr + TILE_N + c, u);
+          if (tok < p.M) {
+            __nv_bfloat16* o = (__nv_bfloat16*)p.out + (long long)tok * p.ldo + n0 + c;
+            if (n0 + c + 16 <= p.N && (p.ldo & 7) == 0 && ((uintptr_t)p.out & 15) == 0) {
+              uint4 w2[2];
+              __nv_bfloat162* wp = reinterpret_cast<__nv_bfloat162*>(w2);
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                wp[j] = __floats2bfloat162_rn(silu_mul(v[2 * j], u[2 * j]), silu_mul(v[2 * j + 1], u[2 * j + 1]));
+              reinterpret_cast<uint4*>(o)[0] = w2[0];
+              reinterpret_cast<uint4*>(o)[1] = w2[1];
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (n0 + c + j < p.N) o[j] = __float2bfloat16_rn(silu_mul(v[j], u[j]));
+            }
+          }
+        }
+      }
+#pragma unroll 1
+      for (int c = 0; !GATED && c < BT; c += 16) {
         if (c >= t_valid) break;                     // warp-uniform
         float v[16];
         tmem_ld16(taddr + c, v);
-        if (part) {
+        if (false) {
+        } else if (part) {
 #pragma unroll
           for (int j = 0; j < 16; ++j)
             if (c + j < t_valid) part[(size_t)(c + j) * TILE_N] = v[j];
@@ -366,17 +415,17 @@ int sm_count() {
   return n;
 }
 
-template <int BT>
+template <int BT, bool GATED>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, GemmParams p, int grid, cudaStream_t stream) {
-  constexpr int STAGE_BYTES = W_STAGE_BYTES + BT * TILE_K * 2;
+  constexpr int STAGE_BYTES = (GATED ? 2 : 1) * W_STAGE_BYTES + BT * TILE_K * 2;
   const size_t smem = (size_t)p.stages * STAGE_BYTES + 1024 + 256;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(gemm_tc_kernel<BT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess)
+    if (cudaFuncSetAttribute(gemm_tc_kernel<BT, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess)
       return iert_check_launch("gemm_tc attribute");
     configured = true;
   }
-  launch_dep(gemm_tc_kernel<BT>, dim3(grid), dim3(THREADS), smem, stream, mw, mx, p);
+  launch_dep(gemm_tc_kernel<BT, GATED>, dim3(grid), dim3(THREADS), smem, stream, mw, mx, p);
   return iert_check_launch("gemm_tc");
 }
 
@@ -453,10 +502,43 @@ IERT_API int iert_gemm_tc(const void* x, long long ldx, const void* w, long long
   const int total_work = tiles * splits;
   const int grid = total_work < slots ? total_work : slots;
   switch (bt) {
-    case 16: return launch<16>(mw, mx, p, grid, stream);
-    case 32: return launch<32>(mw, mx, p, grid, stream);
-    case 64: return launch<64>(mw, mx, p, grid, stream);
-    case 128: return launch<128>(mw, mx, p, grid, stream);
-    default: return launch<256>(mw, mx, p, grid, stream);
+    case 16: return launch<16, false>(mw, mx, p, grid, stream);
+    case 32: return launch<32, false>(mw, mx, p, grid, stream);
+    case 64: return launch<64, false>(mw, mx, p, grid, stream);
+    case 128: return launch<128, false>(mw, mx, p, grid, stream);
+    default: return launch<256, false>(mw, mx, p, grid, stream);
   }
+}
+
+// act[t, i] = silu(x[t] . w[i]) * (x[t] . w[inter + i]) for w = [gate; up] of 2 * inter rows,
+// in one kernel (two accumulators per tile).  act: bf16 [M, inter], row stride ldo.  Whole
+// tiles only; same alignment rules as iert_gemm_tc.
+IERT_API int iert_gemm_tc_gated(const void* x, long long ldx, const void* w, long long ldw, void* act,
+                                long long ldo, int M, int inter, int K, int force_bt, int force_stages,
+                                int* err, cudaStream_t stream) {
+  if (M <= 0 || inter <= 0) return IERT_OK;
+  if (K <= 0 || (K & 7) || (ldx & 7) || (ldw & 7) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15))
+    return IERT_BAD_ARGUMENT;
+  const int bt = 128;                                  // tokens per tile: the MMA's M side
+  (void)force_bt;
+  GemmParams p;
+  p.out = act; p.ldo = ldo; p.out_dtype = IERT_BF16; p.mode = MODE_GATED_SILU;
+  p.M = M; p.N = inter; p.K = K;
+  p.n_tiles = (inter + TILE_N - 1) / TILE_N;
+  p.t_tiles = (M + bt - 1) / bt;
+  p.kb_total = (K + TILE_K - 1) / TILE_K;
+  p.splits = 1; p.kb_per_split = p.kb_total;
+  p.ws = nullptr; p.counters = nullptr; p.err = err;
+  const int tiles = p.n_tiles * p.t_tiles;
+  const int stage_bytes = 2 * W_STAGE_BYTES + bt * TILE_K * 2;
+  const int slots = sm_count();
+  const int smem_budget = 226 * 1024 - 2048;
+  int stages = force_stages ? force_stages : smem_budget / stage_bytes;
+  if (stages > 12) stages = 12;
+  if (stages < 2 || (size_t)stages * stage_bytes + 1280 > 227 * 1024) return IERT_BAD_ARGUMENT;
+  p.stages = stages;
+  CUtensorMap mw, mx;
+  if (!tensor_map(w, 2ll * inter, K, ldw, TILE_N, &mw) || !tensor_map(x, M, K, ldx, bt, &mx)) return IERT_BAD_ARGUMENT;
+  const int grid = tiles < slots ? tiles : slots;
+  return launch<128, true>(mw, mx, p, grid, stream);
 }

@@ -6,6 +6,11 @@ import torch
 from ..csrc import bindings as B
 
 
+# Below this many tokens the fused kernel has too few tiles to fill the GPU (it cannot split K)
+# and the separate product + activation is faster.
+GATED_MIN_ROWS = int(__import__("os").environ.get("IERT_GATED_MIN_ROWS", "128"))
+
+
 def apply(linear, x, out, n_rows: int, mode: int, stream: int) -> bool:
     """Run the tensor-core product if it takes these operands (bf16, K and row strides
     multiples of 8, 16-byte aligned); False means nothing was launched and the caller runs the
@@ -18,4 +23,8 @@ def apply(linear, x, out, n_rows: int, mode: int, stream: int) -> bool:
 def apply_gated(linear, x, act, n_rows: int, stream: int) -> bool:
     """act = silu(x . Wgate^T) * (x . Wup^T) in one kernel, for a row-concatenated
     [gate; up] weight.  False means the caller runs product and activation separately."""
-    return False
+    if x.dtype != torch.bfloat16 or linear.weight.dtype != torch.bfloat16 or act.dtype != torch.bfloat16:
+        return False
+    if n_rows < GATED_MIN_ROWS:
+        return False
+    return B.gemm_tc_gated(x, linear.weight, act, n_rows, linear.rt.err, stream)

@@ -95,3 +95,26 @@ def test_row_results_do_not_depend_on_the_batch():
         assert B.gemm_tc(x, w, out, M, B.GEMM_STORE, err, B.stream_ptr())
         outs.append(out[0].clone())
     assert torch.allclose(outs[0], outs[1], atol=1e-3, rtol=1e-4) and torch.allclose(outs[0], outs[2], atol=1e-3, rtol=1e-4)
+
+
+@pytest.mark.parametrize("M,I,K", [(1, 128, 64), (8, 200, 136), (40, 160, 96), (100, 384, 512), (300, 1000, 264),
+                                   (64, 14336, 256)])
+def test_gated_product_is_silu_gate_times_up(M, I, K):
+    """The fused feed-forward entry: two accumulators per tile, activation in the epilogue."""
+    from inference_engine_rust_b200.csrc import bindings as B
+    g = torch.Generator(device=DEV).manual_seed(M + I + K)
+    x = torch.randn(M, K, device=DEV, generator=g).bfloat16()
+    w = (torch.randn(2 * I, K, device=DEV, generator=g) * (2.0 / K ** 0.5)).bfloat16()
+    act = torch.full((M, I), float("nan"), device=DEV, dtype=torch.bfloat16)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for force in ({}, {"force_stages": 2}):
+        act.fill_(float("nan"))
+        assert B.gemm_tc_gated(x, w, act, M, err, B.stream_ptr(), **force)
+        torch.cuda.synchronize()
+        assert err.item() == 0
+        gate = x.double() @ w[:I].double().t()
+        up = x.double() @ w[I:].double().t()
+        ref = gate * torch.sigmoid(gate) * up
+        diff = (act.double() - ref).abs()
+        bound = 1e-3 + (2.0 ** -8) * ref.abs() + 1e-3 * (gate.abs() + 1) * up.abs()
+        assert torch.isfinite(act).all() and bool((diff <= bound).all()), f"{force}: max diff {diff.max().item():.4g}"
