@@ -1,0 +1,322 @@
+// Prompt attention on the 5th-generation tensor cores (tcgen05) for head sizes 64 and 128:
+// causal, optional sliding window, grouped heads, prompts of unequal lengths packed back to
+// back.  Scores and the output accumulate in tensor memory; queries, keys, values come by TMA
+// (128-byte swizzle) straight from the step's packed projection.
+//
+//   grid (query tiles, heads, sequences); a CTA owns 128 consecutive queries of one head.
+//   warp 4      TMA producer: the query tile once, then key and value tiles of 128 positions
+//               into a two-deep ring.
+//   warp 5      MMA issuer.  S = Q K^T  (128 x 128 x HEAD_DIM, both operands K-major) into one
+//               of two score buffers in TMEM, so the scores of the next tile are computed while
+//               the softmax of this one runs;  O += P V  (128 x HEAD_DIM x 128: P from shared
+//               memory, V as an MN-major operand, i.e. exactly as the projection stores it).
+//   warps 0-3   softmax, one query row per thread (a row of TMEM is one lane): read the row
+//               of scores, mask, running maximum and sum in fp32, exponentials on the
+//               special-function unit, P as bf16 into (swizzled) shared memory.  The output
+//               is rescaled in TMEM only when a row's maximum has grown by more than 2^8 since
+//               the value the exponentials refer to, which keeps P within bf16 range and makes
+//               rescaling rare; the final division uses the same reference maximum, so the
+//               result is the exact softmax.
+//   Every mbarrier wait is bounded; on expiry the kernel records IERT_ERR_WAIT_EXPIRED, frees
+//   its TMEM and returns.
+//
+// Visible keys of query i: j in [max(0, i - (W - 1)), i] (src/layers/attention.rs:364-368);
+// formulas src/layers/attention.rs:357-415, src/ops/softmax.rs:11-25.
+#include "common.cuh"
+#include "sm100.cuh"
+#include "tma_host.cuh"
+
+#ifndef HEAD_DIM
+#error "compile with -DHEAD_DIM=<64 or 128>"
+#endif
+
+#if HEAD_DIM == 64 || HEAD_DIM == 128
+
+using namespace iert;
+using namespace sm100;
+
+namespace {
+
+constexpr int HD = HEAD_DIM;
+constexpr int NSUB = HD / 64;                  // 64-element (128-byte) column blocks of a head
+constexpr int BM = 128, BN = 128;
+constexpr int SUB_BYTES = 128 * 128;           // 128 rows x 128 bytes
+constexpr int THREADS = 192;
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+constexpr uint32_t TMEM_COLS = 512;            // S0 [0,128) S1 [128,256) O [256, 256 + HD)
+constexpr uint32_t O_COL = 256;
+
+struct PrefillTcParams {
+  __nv_bfloat16* out;         // [T, heads * HD]
+  int heads, kv_heads, window;
+  float scale_log2e;
+  int* err;
+};
+
+__device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 255u) == 255u && *abort_flag) return false;
+  }
+  return false;
+}
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map, PrefillTcParams p, IertBatchView b) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* q_s = smem;                                       // NSUB blocks
+  uint8_t* k_s = q_s + NSUB * SUB_BYTES;                     // 2 stages x NSUB blocks
+  uint8_t* v_s = k_s + 2 * NSUB * SUB_BYTES;                 // 2 stages x NSUB blocks
+  uint8_t* p_s = v_s + 2 * NSUB * SUB_BYTES;                 // 2 blocks (keys 0-63, 64-127)
+  uint64_t* bars = (uint64_t*)(p_s + 2 * SUB_BYTES);
+  uint64_t* q_full = bars;          // 1
+  uint64_t* k_full = bars + 1;      // 2
+  uint64_t* v_full = bars + 3;      // 2
+  uint64_t* kv_empty = bars + 5;    // 2
+  uint64_t* s_full = bars + 7;      // 2
+  uint64_t* s_free = bars + 9;      // 2
+  uint64_t* p_ready = bars + 11;    // 1
+  uint64_t* pv_done = bars + 12;    // 1
+  uint32_t* tmem_slot = (uint32_t*)(bars + 13);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  const int s = blockIdx.z, head = blockIdx.y;
+  if (b.slot_ids[s] < 0) return;
+  const int q_begin = b.cu_q[s], len = b.cu_q[s + 1] - q_begin;
+  const int n_qt = (len + BM - 1) / BM;
+  const int qt = n_qt - 1 - (int)blockIdx.x;                 // the longest tiles start first
+  if (qt < 0) return;
+  const int i0 = qt * BM;
+  const int kvh = head / (p.heads / p.kv_heads);
+  const int i_hi = min(len, i0 + BM) - 1;
+  const int j_lo = p.window > 0 ? max(0, i0 - (p.window - 1)) : 0;
+  const int kt_lo = j_lo / BN, kt_hi = i_hi / BN;
+  const int n_tiles = kt_hi - kt_lo + 1;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1); mbar_init(&v_full[i], 1); mbar_init(&kv_empty[i], 1);
+      mbar_init(&s_full[i], 1); mbar_init(&s_free[i], 128);
+    }
+    mbar_init(p_ready, 128);
+    mbar_init(pv_done, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&map);
+  }
+  if (warp == 5) tmem_alloc(tmem_slot, TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  bool ok = true;
+
+  if (warp == 4) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      const int q_col = head * HD, k_col = (p.heads + kvh) * HD, v_col = (p.heads + p.kv_heads + kvh) * HD;
+      mbar_expect_tx(q_full, NSUB * SUB_BYTES);
+      for (int sb = 0; sb < NSUB; ++sb) tma_load_2d(q_s + sb * SUB_BYTES, &map, q_full, q_col + 64 * sb, q_begin + i0);
+      for (int it = 0; ok && it < n_tiles; ++it) {
+        const int st = it & 1;
+        if (!wait_bar(&kv_empty[st], ((it >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+        const int row = q_begin + (kt_lo + it) * BN;
+        mbar_expect_tx(&k_full[st], NSUB * SUB_BYTES);
+        for (int sb = 0; sb < NSUB; ++sb)
+          tma_load_2d(k_s + (st * NSUB + sb) * SUB_BYTES, &map, &k_full[st], k_col + 64 * sb, row);
+        mbar_expect_tx(&v_full[st], NSUB * SUB_BYTES);
+        for (int sb = 0; sb < NSUB; ++sb)
+          tma_load_2d(v_s + (st * NSUB + sb) * SUB_BYTES, &map, &v_full[st], v_col + 64 * sb, row);
+      }
+    }
+  } else if (warp == 5) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t IDESC_S = instr_desc_bf16(BM, BN);
+      constexpr uint32_t IDESC_O = instr_desc_bf16_b_mn(BM, HD);
+      auto scores = [&](int it) -> bool {                    // S[it & 1] = Q K_it^T
+        const int st = it & 1;
+        if (!wait_bar(&k_full[st], (it >> 1) & 1, abort_flag)) return false;
+        if (!wait_bar(&s_free[st], ((it >> 1) & 1) ^ 1, abort_flag)) return false;
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+          const uint32_t qa = smem_addr(q_s + (ks / 4) * SUB_BYTES) + (ks % 4) * 32;
+          const uint32_t kb = smem_addr(k_s + (st * NSUB + ks / 4) * SUB_BYTES) + (ks % 4) * 32;
+          umma_bf16(tmem_base + st * BN, smem_desc_k128(qa), smem_desc_k128(kb), IDESC_S, ks > 0 ? 1u : 0u);
+        }
+        umma_commit(&s_full[st]);
+        return true;
+      };
+      if (!wait_bar(q_full, 0, abort_flag)) ok = false;
+      if (ok) ok = scores(0);
+      for (int it = 0; ok && it < n_tiles; ++it) {
+        const int st = it & 1;
+        if (it + 1 < n_tiles && !scores(it + 1)) { ok = false; break; }
+        if (!wait_bar(p_ready, it & 1, abort_flag)) { ok = false; break; }
+        if (!wait_bar(&v_full[st], (it >> 1) & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk) {               // 16 keys per instruction
+          const uint32_t pa = smem_addr(p_s + (kk / 4) * SUB_BYTES) + (kk % 4) * 32;
+          const uint32_t vb = smem_addr(v_s + st * NSUB * SUB_BYTES) + kk * 16 * 128;
+          umma_bf16(tmem_base + O_COL, smem_desc_k128(pa), smem_desc_mn128(vb, SUB_BYTES), IDESC_O,
+                    (it > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(pv_done);
+        umma_commit(&kv_empty[st]);
+      }
+    }
+  } else {
+    // ---------------- softmax: thread = query row ----------------
+    const int r = warp * 32 + lane;
+    const int i = i0 + r;                                    // position of this row's query
+    const uint32_t lane_bits = (uint32_t)(warp * 32) << 16;
+    float m_used = -INFINITY, l = 0.f;
+    for (int it = 0; ok && it < n_tiles; ++it) {
+      const int st = it & 1, j0 = (kt_lo + it) * BN;
+      if (!wait_bar(&s_full[st], (it >> 1) & 1, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      float sc[BN];
+#pragma unroll
+      for (int c = 0; c < BN; c += 16) tmem_ld16(tmem_base + lane_bits + st * BN + c, sc + c);
+      tc_fence_before();
+      mbar_arrive(&s_free[st]);
+      const bool need_mask = (j0 + BN - 1 > i0) || (p.window > 0 && j0 < i0 + BM - 1 - (p.window - 1)) || (j0 + BN > len);
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < BN; ++c) {
+        float v = sc[c] * p.scale_log2e;
+        if (need_mask) {
+          const int j = j0 + c;
+          const bool vis = j <= i && j < len && (p.window <= 0 || j >= i - (p.window - 1));
+          if (!vis) v = -INFINITY;
+        }
+        sc[c] = v;
+        mx = fmaxf(mx, v);
+      }
+      const bool grow = mx > m_used + 8.0f || (m_used == -INFINITY && mx != -INFINITY);
+      const bool warp_grow = __any_sync(0xffffffffu, grow);
+      if (it > 0 && !wait_bar(pv_done, (it - 1) & 1, abort_flag)) { ok = false; break; }
+      if (warp_grow) {
+        const float m_new = grow ? fmaxf(m_used, mx) : m_used;
+        const float alpha = !grow ? 1.f : (m_used == -INFINITY ? 0.f : ex2(m_used - m_new));
+        m_used = m_new;
+        l *= alpha;
+        if (it > 0) {                                        // the output so far refers to the old maximum
+          tc_fence_after();
+#pragma unroll
+          for (int c = 0; c < HD; c += 16) {
+            float o[16];
+            tmem_ld16(tmem_base + lane_bits + O_COL + c, o);
+#pragma unroll
+            for (int e = 0; e < 16; ++e) o[e] *= alpha;
+            tmem_st16(tmem_base + lane_bits + O_COL + c, o);
+          }
+          tc_fence_before();
+        }
+      }
+      // P = 2^(s - m_used) as bf16 into the swizzled tile: 16-byte chunk q of row r lives at
+      // chunk (q ^ (r & 7)) of the row
+#pragma unroll
+      for (int q8 = 0; q8 < BN / 8; ++q8) {
+        uint4 pk;
+        __nv_bfloat162* pp = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float a = sc[q8 * 8 + 2 * e], bb = sc[q8 * 8 + 2 * e + 1];
+          const float pa = a == -INFINITY ? 0.f : ex2(a - m_used);
+          const float pb = bb == -INFINITY ? 0.f : ex2(bb - m_used);
+          l += pa + pb;
+          pp[e] = __floats2bfloat162_rn(pa, pb);
+        }
+        const int blk = q8 / 8, chunk = q8 % 8;
+        *reinterpret_cast<uint4*>(p_s + blk * SUB_BYTES + r * 128 + ((chunk ^ (r & 7)) << 4)) = pk;
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(p_ready);
+    }
+    if (ok && !wait_bar(pv_done, (n_tiles - 1) & 1, abort_flag)) ok = false;
+    if (ok) {
+      tc_fence_after();
+      const float inv = l > 0.f ? 1.0f / l : 0.f;
+      __nv_bfloat16* dst = p.out + ((long long)(q_begin + i) * p.heads + head) * HD;
+#pragma unroll
+      for (int c = 0; c < HD; c += 16) {
+        float o[16];
+        tmem_ld16(tmem_base + lane_bits + O_COL + c, o);
+        if (i < len) {
+          uint4 w2[2];
+          __nv_bfloat162* wp = reinterpret_cast<__nv_bfloat162*>(w2);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) wp[e] = __floats2bfloat162_rn(o[2 * e] * inv, o[2 * e + 1] * inv);
+          reinterpret_cast<uint4*>(dst + c)[0] = w2[0];
+          reinterpret_cast<uint4*>(dst + c)[1] = w2[1];
+        }
+      }
+    }
+  }
+  if (!ok && lane == 0) {
+    if (!*abort_flag) atomicOr(p.err, IERT_ERR_WAIT_EXPIRED);
+    *abort_flag = 1;
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace
+
+IERT_API int iert_attention_prefill_tc_available() { return 1; }
+
+// Same contract as iert_attention_prefill; additionally qkv must be 16-byte aligned.  Returns
+// IERT_BAD_ARGUMENT (nothing launched) when the tensor map cannot be made.
+IERT_API int iert_attention_prefill_tc(const void* qkv, void* out, const IertBatchView* batch, int heads,
+                                       int kv_heads, int window, float scale, int max_q_len, int* err,
+                                       cudaStream_t stream) {
+  if (batch->n_tokens <= 0 || max_q_len <= 0) return IERT_OK;
+  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || heads > 65535 || batch->n_seqs > 65535 ||
+      ((uintptr_t)qkv & 15) || ((uintptr_t)out & 15))
+    return IERT_BAD_ARGUMENT;
+  const long long width = (long long)(heads + 2 * kv_heads) * HD;
+  CUtensorMap map;
+  if (!tma_host::tensor_map_2d(qkv, batch->n_tokens, width, width, 128, &map)) return IERT_BAD_ARGUMENT;
+  PrefillTcParams p;
+  p.out = (__nv_bfloat16*)out;
+  p.heads = heads; p.kv_heads = kv_heads; p.window = window;
+  p.scale_log2e = scale * 1.4426950408889634f;
+  p.err = err;
+  const size_t smem = (size_t)(NSUB * 5 + 2) * SUB_BYTES + 1024 + 256;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+      cudaGetLastError();
+      return IERT_CUDA_ERROR;
+    }
+    configured = true;
+  }
+  dim3 grid((max_q_len + BM - 1) / BM, heads, batch->n_seqs);
+  attention_prefill_tc_kernel<<<grid, THREADS, smem, stream>>>(map, p, *batch);
+  return cudaGetLastError() == cudaSuccess ? IERT_OK : IERT_CUDA_ERROR;
+}
+
+#else   // other head sizes: the mma.sync kernel serves them
+
+IERT_API int iert_attention_prefill_tc_available() { return 0; }
+IERT_API int iert_attention_prefill_tc(const void*, void*, const IertBatchView*, int, int, int, float, int, int*,
+                                       cudaStream_t) {
+  return IERT_BAD_ARGUMENT;
+}
+
+#endif

@@ -282,6 +282,10 @@ def _attention_lib(head_dim: int):
         lib.iert_attention_decode_tc.argtypes = [c_void_p, c_void_p, POINTER(BatchView), POINTER(KvView), c_int,
                                                  c_float, c_int, c_void_p, c_void_p, c_void_p]
         lib.iert_attention_decode_tc.restype = c_int
+        lib.iert_attention_prefill_tc.argtypes = [c_void_p, c_void_p, POINTER(BatchView), c_int, c_int, c_int,
+                                                  c_float, c_int, c_void_p, c_void_p]
+        lib.iert_attention_prefill_tc.restype = c_int
+        lib.iert_attention_prefill_tc_available.restype = c_int
         if os.environ.get("IERT_PDL", "1") == "0":
             lib.iert_set_pdl(0)
         _attn_libs[head_dim] = lib
@@ -289,19 +293,30 @@ def _attention_lib(head_dim: int):
 
 
 def attention_prefill(qkv, out, batch: BatchView, heads: int, kv_heads: int, head_dim: int, window: int,
-                      scale: float, max_q_len: int, stream) -> bool:
-    """Flash prompt attention (bf16) over the step's own keys and values.  The kernel is
-    compiled per head size (multiples of 16 up to 256) the first time it is needed; other
-    head sizes return False and nothing is launched."""
+                      scale: float, max_q_len: int, stream, err=None, legacy: bool = False) -> bool:
+    """Flash prompt attention (bf16) over the step's own keys and values.  Head sizes 64 and
+    128 run on tcgen05 with the scores and the output in tensor memory (unless `legacy`); other
+    multiples of 16 up to 256 run the mma.sync kernel.  The library is compiled per head size
+    the first time it is needed; anything else returns False and nothing is launched."""
     if head_dim % 16 or not 16 <= head_dim <= 256:
         return False
-    status = _attention_lib(head_dim).iert_attention_prefill(qkv.data_ptr(), out.data_ptr(), byref(batch), heads,
-                                                             kv_heads, window, scale, max_q_len, stream)
+    lib = _attention_lib(head_dim)
+    global launch_count
+    if not legacy and err is not None and lib.iert_attention_prefill_tc_available() \
+            and os.environ.get("IERT_ATTN_TC", "1") != "0":
+        status = lib.iert_attention_prefill_tc(qkv.data_ptr(), out.data_ptr(), byref(batch), heads, kv_heads,
+                                               window, scale, max_q_len, err.data_ptr(), stream)
+        if status == 0:
+            launch_count += 1
+            return True
+        if status != 1:
+            raise KernelError("attention_prefill_tc: the launch failed")
+    status = lib.iert_attention_prefill(qkv.data_ptr(), out.data_ptr(), byref(batch), heads, kv_heads,
+                                        window, scale, max_q_len, stream)
     if status == 1:
         return False
     if status != 0:
         raise KernelError("attention_prefill: the launch failed")
-    global launch_count
     launch_count += 1
     return True
 

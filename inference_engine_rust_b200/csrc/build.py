@@ -172,7 +172,7 @@ PREBUILT_HEAD_DIMS = (16, 32, 48, 64, 128)
 def attention_library(head_dim: int):
     """(name, sources, defines) of the tensor-core attention library (prompt and decode
     kernels) for one head size."""
-    return (f"iert_attn_hd{head_dim}", ["runtime.cu", "attention_prefill.cu", "attention_decode_tc.cu"],
+    return (f"iert_attn_hd{head_dim}", ["runtime.cu", "attention_prefill.cu", "attention_prefill_tc.cu", "attention_decode_tc.cu"],
             [f"HEAD_DIM={head_dim}"])
 
 

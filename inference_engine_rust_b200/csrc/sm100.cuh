@@ -107,6 +107,26 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// The mirror image of tmem_ld16: 16 consecutive fp32 columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const float* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+        "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])),
+        "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])),
+        "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+        "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])),
+        "r"(__float_as_uint(v[15]))
+      : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory writes made with ordinary stores become visible to the tensor core / TMA
+// (the asynchronous proxy) after this fence.
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
 // ---- descriptors --------------------------------------------------------------------------
 // Shared-memory operand descriptor for a K-major bf16 tile whose rows are 128 bytes (64
 // elements) and were written by TMA with the 128-byte swizzle: 8-row groups are 1024 bytes
@@ -120,6 +140,19 @@ __device__ __forceinline__ uint64_t smem_desc_k128(uint32_t saddr) {
   d |= (uint64_t)2 << 61;                         // layout: 128-byte swizzle
   return d;
 }
+// Shared-memory operand descriptor for an MN-major bf16 tile written by TMA with the 128-byte
+// swizzle: each row of the tile is one K index holding 64 consecutive MN elements (128 bytes);
+// 8-row groups (8 K indices) are 1024 bytes apart (stride byte offset); the next 64 MN
+// elements start `mn_block_bytes` further on (leading byte offset).
+__device__ __forceinline__ uint64_t smem_desc_mn128(uint32_t saddr, uint32_t mn_block_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
+  d |= (uint64_t)((mn_block_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
 // Instruction descriptor: bf16 x bf16 -> fp32, both operands K-major, tile M x N.
 __host__ __device__ constexpr uint32_t instr_desc_bf16(uint32_t M, uint32_t N) {
   return (1u << 4)            // D format fp32
@@ -127,6 +160,11 @@ __host__ __device__ constexpr uint32_t instr_desc_bf16(uint32_t M, uint32_t N) {
          | (1u << 10)         // B format bf16
          | ((N >> 3) << 17)   // N / 8
          | ((M >> 4) << 24);  // M / 16
+}
+
+// The same with the B operand MN-major (bit 16).
+__host__ __device__ constexpr uint32_t instr_desc_bf16_b_mn(uint32_t M, uint32_t N) {
+  return instr_desc_bf16(M, N) | (1u << 16);
 }
 
 }  // namespace sm100

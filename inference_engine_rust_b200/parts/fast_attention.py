@@ -34,5 +34,5 @@ def apply(attn, qkv, out, ctx, cache_view, from_cache: bool) -> bool:
                                   scratch, rt.err, ctx.stream)
     if not from_cache:
         return B.attention_prefill(qkv, out, ctx.batch, attn.heads, attn.kv_heads, attn.head_dim,
-                                   attn.window or 0, attn.scale, ctx.max_q_len, ctx.stream)
+                                   attn.window or 0, attn.scale, ctx.max_q_len, ctx.stream, err=rt.err)
     return False

@@ -368,7 +368,8 @@ def test_sampling_temperature_follows_the_cdf(vocab, temperature):
 
 
 @pytest.mark.parametrize("heads,kvh,hd,window", [(4, 2, 16, 16), (6, 1, 32, None), (3, 3, 48, 70), (8, 2, 128, None),
-                                                 (4, 4, 128, 100), (5, 5, 80, 33), (2, 1, 256, 130)])
+                                                 (4, 4, 128, 100), (5, 5, 80, 33), (2, 1, 256, 130), (6, 2, 64, None),
+                                                 (3, 1, 64, 200), (2, 2, 128, 129)])
 def test_attention_prefill_against_plain_kernel(heads, kvh, hd, window):
     """The tensor-core prompt attention against its plain sibling: unequal prompts (a single
     token, lengths around the 64-wide tiles, several tiles), windows that cut tiles at odd
@@ -390,12 +391,15 @@ def test_attention_prefill_against_plain_kernel(heads, kvh, hd, window):
     err = err_word()
     plain = torch.empty(T, heads * hd, device=DEV, dtype=dtype)
     b.attention_plain(qkv, plain, view, cache.layer_view(0).struct, heads, scale, False, err, stream())
-    fast = torch.full_like(plain, float("nan"))
-    assert b.attention_prefill(qkv, fast, view, heads, kvh, hd, window or 0, scale, max(q_lens), stream())
-    torch.cuda.synchronize()
-    assert torch.isfinite(fast).all()
-    assert torch.allclose(fast.float(), plain.float(), atol=2e-2, rtol=2e-2), \
-        f"max diff {(fast.float() - plain.float()).abs().max().item():.4g}"
+    for legacy in (True, False):        # the mma.sync kernel; then tcgen05 where the head size has it
+        fast = torch.full_like(plain, float("nan"))
+        assert b.attention_prefill(qkv, fast, view, heads, kvh, hd, window or 0, scale, max(q_lens), stream(),
+                                   err=err, legacy=legacy)
+        torch.cuda.synchronize()
+        assert err.item() == 0, b.describe_error_bits(err.item())
+        assert torch.isfinite(fast).all()
+        assert torch.allclose(fast.float(), plain.float(), atol=2e-2, rtol=2e-2), \
+            f"legacy={legacy}: max diff {(fast.float() - plain.float()).abs().max().item():.4g}"
     x = qkv.float().cpu().view(T, Wd, hd)
     lo = far
     p_far = P.softmax((x[lo:last + 1, heads] @ x[last, 0]) * scale)
