@@ -4,11 +4,13 @@
 // (128-byte swizzle) straight from the step's packed projection.
 //
 //   grid (query tiles, heads, sequences); a CTA owns 128 consecutive queries of one head.
-//   warp 4      TMA producer: the query tile once, then key and value tiles of 128 positions
+//   Two CTAs share an SM (half of its shared memory, tensor memory and registers each), so one
+//   CTA's softmax overlaps the other's MMAs and loads.
+//   warp 4      TMA producer: the query tile once, then key and value tiles of 64 positions
 //               into a two-deep ring.
-//   warp 5      MMA issuer.  S = Q K^T  (128 x 128 x HEAD_DIM, both operands K-major) into one
+//   warp 5      MMA issuer.  S = Q K^T  (128 x 64 x HEAD_DIM, both operands K-major) into one
 //               of two score buffers in TMEM, so the scores of the next tile are computed while
-//               the softmax of this one runs;  O += P V  (128 x HEAD_DIM x 128: P from shared
+//               the softmax of this one runs;  O += P V  (128 x HEAD_DIM x 64: P from shared
 //               memory, V as an MN-major operand, i.e. exactly as the projection stores it).
 //   warps 0-3   softmax, one query row per thread (a row of TMEM is one lane): read the row
 //               of scores, mask, running maximum and sum in fp32, exponentials on the
@@ -39,12 +41,13 @@ namespace {
 
 constexpr int HD = HEAD_DIM;
 constexpr int NSUB = HD / 64;                  // 64-element (128-byte) column blocks of a head
-constexpr int BM = 128, BN = 128;
-constexpr int SUB_BYTES = 128 * 128;           // 128 rows x 128 bytes
+constexpr int BM = 128, BN = 64;               // queries per CTA, keys per tile
+constexpr int SUB_BYTES = BM * 128;            // a block of the query / probability tile: 128 rows x 128 bytes
+constexpr int KV_SUB_BYTES = BN * 128;         // a block of a key / value tile: 64 rows x 128 bytes
 constexpr int THREADS = 192;
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
-constexpr uint32_t TMEM_COLS = 512;            // S0 [0,128) S1 [128,256) O [256, 256 + HD)
-constexpr uint32_t O_COL = 256;
+constexpr uint32_t TMEM_COLS = 256;            // S0 [0,64) S1 [64,128) O [128, 128 + HD): two CTAs share an SM
+constexpr uint32_t O_COL = 128;
 
 struct PrefillTcParams {
   __nv_bfloat16* out;         // [T, heads * HD]
@@ -66,28 +69,35 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
-__global__ void __launch_bounds__(THREADS, 1)
-attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map, PrefillTcParams p, IertBatchView b) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint8_t* q_s = smem;                                       // NSUB blocks
-  uint8_t* k_s = q_s + NSUB * SUB_BYTES;                     // 2 stages x NSUB blocks
-  uint8_t* v_s = k_s + 2 * NSUB * SUB_BYTES;                 // 2 stages x NSUB blocks
-  uint8_t* p_s = v_s + 2 * NSUB * SUB_BYTES;                 // 2 blocks (keys 0-63, 64-127)
-  uint64_t* bars = (uint64_t*)(p_s + 2 * SUB_BYTES);
+__global__ void __launch_bounds__(THREADS, 2)
+attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
+                            PrefillTcParams p, IertBatchView b) {
+  // No static shared memory in this kernel: the dynamic window starts at the block's base,
+  // which is 1024-byte aligned as the swizzled tiles need (checked below).
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint8_t* q_s = smem;                                       // NSUB blocks of 128 rows
+  uint8_t* k_s = q_s + NSUB * SUB_BYTES;                     // 2 stages x NSUB blocks of 64 rows
+  uint8_t* v_s = k_s + 2 * NSUB * KV_SUB_BYTES;              // 2 stages x NSUB blocks of 64 rows
+  uint8_t* p_s = v_s + 2 * NSUB * KV_SUB_BYTES;              // one block: 128 rows x 64 keys
+  uint64_t* bars = (uint64_t*)(p_s + SUB_BYTES);
   uint64_t* q_full = bars;          // 1
   uint64_t* k_full = bars + 1;      // 2
   uint64_t* v_full = bars + 3;      // 2
-  uint64_t* kv_empty = bars + 5;    // 2
-  uint64_t* s_full = bars + 7;      // 2
-  uint64_t* s_free = bars + 9;      // 2
-  uint64_t* p_ready = bars + 11;    // 1
-  uint64_t* pv_done = bars + 12;    // 1
-  uint32_t* tmem_slot = (uint32_t*)(bars + 13);
+  uint64_t* k_empty = bars + 5;     // 2: a key buffer is free once its score MMAs have finished
+  uint64_t* v_empty = bars + 7;     // 2: a value buffer is free once its output MMAs have finished
+  uint64_t* s_full = bars + 9;      // 2
+  uint64_t* s_free = bars + 11;     // 2
+  uint64_t* p_ready = bars + 13;    // 1
+  uint64_t* pv_done = bars + 14;    // 1
+  uint32_t* tmem_slot = (uint32_t*)(bars + 15);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
   const int s = blockIdx.z, head = blockIdx.y;
   if (b.slot_ids[s] < 0) return;
+  if (smem_addr(smem) & 1023u) {                             // never expected; refuse rather than compute garbage
+    if (threadIdx.x == 0) atomicOr(p.err, IERT_ERR_WAIT_EXPIRED);
+    return;
+  }
   const int q_begin = b.cu_q[s], len = b.cu_q[s + 1] - q_begin;
   const int n_qt = (len + BM - 1) / BM;
   const int qt = n_qt - 1 - (int)blockIdx.x;                 // the longest tiles start first
@@ -103,14 +113,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map, PrefillTcPa
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&k_full[i], 1); mbar_init(&v_full[i], 1); mbar_init(&kv_empty[i], 1);
+      mbar_init(&k_full[i], 1); mbar_init(&v_full[i], 1); mbar_init(&k_empty[i], 1); mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1); mbar_init(&s_free[i], 128);
     }
     mbar_init(p_ready, 128);
     mbar_init(pv_done, 1);
     *abort_flag = 0;
     mbar_fence_init();
-    tma_prefetch_desc(&map);
+    tma_prefetch_desc(&map_q);
+    tma_prefetch_desc(&map_kv);
   }
   if (warp == 5) tmem_alloc(tmem_slot, TMEM_COLS);
   tc_fence_before();
@@ -124,17 +135,31 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map, PrefillTcPa
     if (lane == 0) {
       const int q_col = head * HD, k_col = (p.heads + kvh) * HD, v_col = (p.heads + p.kv_heads + kvh) * HD;
       mbar_expect_tx(q_full, NSUB * SUB_BYTES);
-      for (int sb = 0; sb < NSUB; ++sb) tma_load_2d(q_s + sb * SUB_BYTES, &map, q_full, q_col + 64 * sb, q_begin + i0);
-      for (int it = 0; ok && it < n_tiles; ++it) {
+      for (int sb = 0; sb < NSUB; ++sb) tma_load_2d(q_s + sb * SUB_BYTES, &map_q, q_full, q_col + 64 * sb, q_begin + i0);
+      // keys run one tile ahead of values: a key buffer frees up earlier (after the scores)
+      auto load_k = [&](int it) -> bool {
         const int st = it & 1;
-        if (!wait_bar(&kv_empty[st], ((it >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
-        const int row = q_begin + (kt_lo + it) * BN;
-        mbar_expect_tx(&k_full[st], NSUB * SUB_BYTES);
+        if (!wait_bar(&k_empty[st], ((it >> 1) & 1) ^ 1, abort_flag)) return false;
+        mbar_expect_tx(&k_full[st], NSUB * KV_SUB_BYTES);
         for (int sb = 0; sb < NSUB; ++sb)
-          tma_load_2d(k_s + (st * NSUB + sb) * SUB_BYTES, &map, &k_full[st], k_col + 64 * sb, row);
-        mbar_expect_tx(&v_full[st], NSUB * SUB_BYTES);
+          tma_load_2d(k_s + (st * NSUB + sb) * KV_SUB_BYTES, &map_kv, &k_full[st], k_col + 64 * sb,
+                      q_begin + (kt_lo + it) * BN);
+        return true;
+      };
+      auto load_v = [&](int it) -> bool {
+        const int st = it & 1;
+        if (!wait_bar(&v_empty[st], ((it >> 1) & 1) ^ 1, abort_flag)) return false;
+        mbar_expect_tx(&v_full[st], NSUB * KV_SUB_BYTES);
         for (int sb = 0; sb < NSUB; ++sb)
-          tma_load_2d(v_s + (st * NSUB + sb) * SUB_BYTES, &map, &v_full[st], v_col + 64 * sb, row);
+          tma_load_2d(v_s + (st * NSUB + sb) * KV_SUB_BYTES, &map_kv, &v_full[st], v_col + 64 * sb,
+                      q_begin + (kt_lo + it) * BN);
+        return true;
+      };
+      ok = load_k(0);
+      if (ok && n_tiles > 1) ok = load_k(1);
+      for (int it = 0; ok && it < n_tiles; ++it) {
+        ok = load_v(it);
+        if (ok && it + 2 < n_tiles) ok = load_k(it + 2);
       }
     }
   } else if (warp == 5) {
@@ -150,10 +175,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map, PrefillTcPa
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
           const uint32_t qa = smem_addr(q_s + (ks / 4) * SUB_BYTES) + (ks % 4) * 32;
-          const uint32_t kb = smem_addr(k_s + (st * NSUB + ks / 4) * SUB_BYTES) + (ks % 4) * 32;
+          const uint32_t kb = smem_addr(k_s + (st * NSUB + ks / 4) * KV_SUB_BYTES) + (ks % 4) * 32;
           umma_bf16(tmem_base + st * BN, smem_desc_k128(qa), smem_desc_k128(kb), IDESC_S, ks > 0 ? 1u : 0u);
         }
         umma_commit(&s_full[st]);
+        umma_commit(&k_empty[st]);
         return true;
       };
       if (!wait_bar(q_full, 0, abort_flag)) ok = false;
@@ -166,13 +192,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map, PrefillTcPa
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk) {               // 16 keys per instruction
-          const uint32_t pa = smem_addr(p_s + (kk / 4) * SUB_BYTES) + (kk % 4) * 32;
-          const uint32_t vb = smem_addr(v_s + st * NSUB * SUB_BYTES) + kk * 16 * 128;
-          umma_bf16(tmem_base + O_COL, smem_desc_k128(pa), smem_desc_mn128(vb, SUB_BYTES), IDESC_O,
+          const uint32_t pa = smem_addr(p_s) + kk * 32;
+          const uint32_t vb = smem_addr(v_s + st * NSUB * KV_SUB_BYTES) + kk * 16 * 128;
+          umma_bf16(tmem_base + O_COL, smem_desc_k128(pa), smem_desc_mn128(vb, KV_SUB_BYTES), IDESC_O,
                     (it > 0 || kk > 0) ? 1u : 0u);
         }
         umma_commit(pv_done);
-        umma_commit(&kv_empty[st]);
+        umma_commit(&v_empty[st]);
       }
     }
   } else {
@@ -186,8 +212,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map, PrefillTcPa
       if (!wait_bar(&s_full[st], (it >> 1) & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
       float sc[BN];
+      {
+        uint32_t raw[BN];
 #pragma unroll
-      for (int c = 0; c < BN; c += 16) tmem_ld16(tmem_base + lane_bits + st * BN + c, sc + c);
+        for (int c = 0; c < BN; c += 16) tmem_ld16_issue(tmem_base + lane_bits + st * BN + c, raw + c);
+        tmem_ld_wait();
+#pragma unroll
+        for (int c = 0; c < BN; ++c) sc[c] = __uint_as_float(raw[c]);
+      }
       tc_fence_before();
       mbar_arrive(&s_free[st]);
       const bool need_mask = (j0 + BN - 1 > i0) || (p.window > 0 && j0 < i0 + BM - 1 - (p.window - 1)) || (j0 + BN > len);
@@ -238,8 +270,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map, PrefillTcPa
           l += pa + pb;
           pp[e] = __floats2bfloat162_rn(pa, pb);
         }
-        const int blk = q8 / 8, chunk = q8 % 8;
-        *reinterpret_cast<uint4*>(p_s + blk * SUB_BYTES + r * 128 + ((chunk ^ (r & 7)) << 4)) = pk;
+        *reinterpret_cast<uint4*>(p_s + r * 128 + ((q8 ^ (r & 7)) << 4)) = pk;
       }
       fence_proxy_async_smem();
       mbar_arrive(p_ready);
@@ -290,14 +321,16 @@ IERT_API int iert_attention_prefill_tc(const void* qkv, void* out, const IertBat
       ((uintptr_t)qkv & 15) || ((uintptr_t)out & 15))
     return IERT_BAD_ARGUMENT;
   const long long width = (long long)(heads + 2 * kv_heads) * HD;
-  CUtensorMap map;
-  if (!tma_host::tensor_map_2d(qkv, batch->n_tokens, width, width, 128, &map)) return IERT_BAD_ARGUMENT;
+  CUtensorMap map_q, map_kv;
+  if (!tma_host::tensor_map_2d(qkv, batch->n_tokens, width, width, BM, &map_q) ||
+      !tma_host::tensor_map_2d(qkv, batch->n_tokens, width, width, BN, &map_kv))
+    return IERT_BAD_ARGUMENT;
   PrefillTcParams p;
   p.out = (__nv_bfloat16*)out;
   p.heads = heads; p.kv_heads = kv_heads; p.window = window;
   p.scale_log2e = scale * 1.4426950408889634f;
   p.err = err;
-  const size_t smem = (size_t)(NSUB * 5 + 2) * SUB_BYTES + 1024 + 256;
+  const size_t smem = (size_t)NSUB * SUB_BYTES + 4 * (size_t)NSUB * KV_SUB_BYTES + SUB_BYTES + 128;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
@@ -307,7 +340,7 @@ IERT_API int iert_attention_prefill_tc(const void* qkv, void* out, const IertBat
     configured = true;
   }
   dim3 grid((max_q_len + BM - 1) / BM, heads, batch->n_seqs);
-  attention_prefill_tc_kernel<<<grid, THREADS, smem, stream>>>(map, p, *batch);
+  attention_prefill_tc_kernel<<<grid, THREADS, smem, stream>>>(map_q, map_kv, p, *batch);
   return cudaGetLastError() == cudaSuccess ? IERT_OK : IERT_CUDA_ERROR;
 }
 
