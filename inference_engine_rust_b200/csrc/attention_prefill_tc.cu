@@ -222,19 +222,23 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       }
       tc_fence_before();
       mbar_arrive(&s_free[st]);
+      // Scores stay raw; the scale (> 0) is folded into the exponent: p = 2^(s * scale - m).
+      // A tile that every row sees entirely (the common case) takes the path without masks.
       const bool need_mask = (j0 + BN - 1 > i0) || (p.window > 0 && j0 < i0 + BM - 1 - (p.window - 1)) || (j0 + BN > len);
       float mx = -INFINITY;
+      if (!need_mask) {
 #pragma unroll
-      for (int c = 0; c < BN; ++c) {
-        float v = sc[c] * p.scale_log2e;
-        if (need_mask) {
+        for (int c = 0; c < BN; ++c) mx = fmaxf(mx, sc[c]);
+      } else {
+#pragma unroll
+        for (int c = 0; c < BN; ++c) {
           const int j = j0 + c;
           const bool vis = j <= i && j < len && (p.window <= 0 || j >= i - (p.window - 1));
-          if (!vis) v = -INFINITY;
+          if (!vis) sc[c] = -INFINITY;
+          mx = fmaxf(mx, sc[c]);
         }
-        sc[c] = v;
-        mx = fmaxf(mx, v);
       }
+      mx *= p.scale_log2e;                                   // -inf stays -inf
       const bool grow = mx > m_used + 8.0f || (m_used == -INFINITY && mx != -INFINITY);
       const bool warp_grow = __any_sync(0xffffffffu, grow);
       if (it > 0 && !wait_bar(pv_done, (it - 1) & 1, abort_flag)) { ok = false; break; }
@@ -256,8 +260,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           tc_fence_before();
         }
       }
-      // P = 2^(s - m_used) as bf16 into the swizzled tile: 16-byte chunk q of row r lives at
-      // chunk (q ^ (r & 7)) of the row
+      // P as bf16 into the swizzled tile: 16-byte chunk q of row r lives at chunk (q ^ (r & 7))
+      const float neg_m = m_used == -INFINITY ? 0.f : -m_used;   // a row without a visible key: all p are 0
+      float l0 = 0.f, l1 = 0.f;
 #pragma unroll
       for (int q8 = 0; q8 < BN / 8; ++q8) {
         uint4 pk;
@@ -265,14 +270,17 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const float a = sc[q8 * 8 + 2 * e], bb = sc[q8 * 8 + 2 * e + 1];
-          const float pa = a == -INFINITY ? 0.f : ex2(a - m_used);
-          const float pb = bb == -INFINITY ? 0.f : ex2(bb - m_used);
-          l += pa + pb;
+          float pa = ex2(fmaf(a, p.scale_log2e, neg_m)), pb = ex2(fmaf(bb, p.scale_log2e, neg_m));
+          if (need_mask) { if (a == -INFINITY) pa = 0.f; if (bb == -INFINITY) pb = 0.f; }
+          l0 += pa; l1 += pb;
           pp[e] = __floats2bfloat162_rn(pa, pb);
         }
         *reinterpret_cast<uint4*>(p_s + r * 128 + ((q8 ^ (r & 7)) << 4)) = pk;
       }
+      l += l0 + l1;
+#ifndef IERT_EXP_NO_PFENCE
       fence_proxy_async_smem();
+#endif
       mbar_arrive(p_ready);
     }
     if (ok && !wait_bar(pv_done, (n_tiles - 1) & 1, abort_flag)) ok = false;

@@ -37,6 +37,8 @@ CORE_SOURCES = [
     "gemm_tc.cu", "attention_decode.cu",
 ]
 HEADERS = ["common.cuh"]
+# Extra -D definitions for experiments (space separated), e.g. IERT_EXTRA_DEFINES="FOO=1 BAR".
+EXTRA_DEFINES = os.environ.get("IERT_EXTRA_DEFINES", "").split()
 
 
 class BuildError(RuntimeError):
@@ -79,7 +81,7 @@ def _digest(sources: Sequence[str], defines: Sequence[str]) -> str:
     for name in list(sources) + HEADERS + _extra_headers(sources):
         with open(os.path.join(CSRC_DIR, name), "rb") as f:
             h.update(name.encode() + b"\0" + f.read())
-    h.update(" ".join(NVCC_FLAGS + list(defines)).encode())
+    h.update(" ".join(NVCC_FLAGS + list(defines) + EXTRA_DEFINES).encode())
     return h.hexdigest()[:12]
 
 
@@ -96,6 +98,7 @@ def library_path(name: str, sources: Sequence[str], defines: Sequence[str] = ())
 
 
 def _compile_one(nvcc: str, src: str, obj: str, defines: Sequence[str]) -> None:
+    defines = list(defines) + EXTRA_DEFINES
     cmd = [nvcc, *NVCC_FLAGS, *[f"-D{d}" for d in defines], "-I", CSRC_DIR, "-c",
            os.path.join(CSRC_DIR, src), "-o", obj]
     p = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
