@@ -1,0 +1,93 @@
+"""The engine at Mistral-7B layer sizes (hidden 4096, 32 heads / 8 kv heads of 128, feed-forward
+14336, vocabulary 32000; two layers so that it stays small): the kernels run the shapes they
+run in production (k of 4096 and 14336, split-K, 128-wide heads, four query heads per kv
+head).  The plain implementation on the CPU is out of reach at this size, so the oracle here is
+the engine's own true 32-bit path (plain FFMA kernels), which the tiny-model tests pin to the
+plain implementation:
+
+  * float32: the logits of a request do not depend on how its tokens are cut into steps or on
+    what else is in the batch;
+  * bfloat16 (tensor-core kernels) against float32 on the same bf16-rounded weights.
+"""
+import pytest
+import torch
+
+from helpers import compare
+
+pytestmark = pytest.mark.gpu
+
+CFG = {
+    "architectures": ["MistralForCausalLM"], "model_type": "mistral",
+    "num_hidden_layers": 2, "hidden_size": 4096, "num_attention_heads": 32, "num_key_value_heads": 8,
+    "head_dim": 128, "intermediate_size": 14336, "vocab_size": 32000, "rope_theta": 10000.0,
+    "sliding_window": 160, "rms_norm_eps": 1e-5, "max_position_embeddings": 4096,
+    "tie_word_embeddings": False, "hidden_act": "silu", "bos_token_id": 1, "eos_token_id": 2,
+}
+LENGTHS = [300, 37, 129]          # the window of 160 cuts the longest request; 300 > two pages
+
+
+@pytest.fixture(scope="module")
+def models():
+    from inference_engine_rust_b200 import LoadedModel
+    from inference_engine_rust_b200.weights import RandomSource
+    bf = LoadedModel.random(CFG, seed=5, dtype="bfloat16", std=0.02, on_device=True)
+    # the float32 model gets the very same (bf16-rounded) numbers, widened
+    f32 = LoadedModel._build(bf.config, "float32", "cuda:0", False)
+    src = RandomSource(f32.expected_tensors(), 5, 0.02, dtype=torch.bfloat16, device="cuda:0")
+    f32.load(src, where="random weights")
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, CFG["vocab_size"], (n,), generator=g).tolist() for n in LENGTHS]
+    return bf, LoadedModel(bf.config, f32), prompts
+
+
+def run_whole(model, prompts):
+    eng = model.session(max_tokens=64 * 12, poison_cache=True).engine
+    out = []
+    for p in prompts:
+        s = eng.open_sequence()
+        out.append(eng.step([(s, p)], want="all").clone())
+        eng.close_sequence(s)
+    eng.check_device()
+    return out
+
+
+def run_batched_with_tails(model, prompts, tails):
+    """All prompts (minus their tails) in one step, then one token each until each ends."""
+    eng = model.session(max_tokens=64 * 12, max_sequences=4, poison_cache=True).engine
+    slots = [eng.open_sequence() for _ in prompts]
+    got = [[] for _ in prompts]
+    out = eng.step([(s, p[:len(p) - t]) for s, p, t in zip(slots, prompts, tails)], want="all")
+    at = 0
+    for i, (p, t) in enumerate(zip(prompts, tails)):
+        got[i].append(out[at:at + len(p) - t].clone())
+        at += len(p) - t
+    for k in range(max(tails)):
+        live = [i for i in range(len(prompts)) if tails[i] > k]
+        out = eng.step([(slots[i], [prompts[i][len(prompts[i]) - tails[i] + k]]) for i in live], want="last")
+        for r, i in enumerate(live):
+            got[i].append(out[r:r + 1].clone())
+        for i in live:
+            if tails[i] == k + 1:
+                eng.close_sequence(slots[i])
+    eng.check_device()
+    eng.cache.check()
+    return [torch.cat(g) for g in got]
+
+
+def test_float32_does_not_depend_on_the_cutting(models):
+    bf, f32, prompts = models
+    whole = run_whole(f32, prompts)
+    cut = run_batched_with_tails(f32, prompts, tails=[32, 5, 17])
+    for i, (a, b) in enumerate(zip(cut, whole)):
+        compare(a, b, "float32", f"7B sizes, float32, request {i}: batched and decoded against whole")
+
+
+def test_bfloat16_matches_float32(models):
+    bf, f32, prompts = models
+    want = run_whole(f32, prompts)
+    whole = run_whole(bf, prompts)
+    for i, (a, b) in enumerate(zip(whole, want)):
+        compare(a, b, "bfloat16", f"7B sizes, bfloat16 whole against float32, request {i}")
+    cut = run_batched_with_tails(bf, prompts, tails=[32, 5, 17])
+    for i, (a, b) in enumerate(zip(cut, want)):
+        compare(a, b, "bfloat16", f"7B sizes, bfloat16 batched and decoded against float32, request {i}")

@@ -299,3 +299,51 @@ def test_unknown_part_kind_is_named(toy_registered):
     with pytest.raises(KeyError) as e:
         part_class("mixer", "convolution")
     assert "attention" in str(e.value) and "running_mean" in str(e.value)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_block_part_alone(dtype):
+    """The pre-norm arrangement with its four parts against the plain block, for two prompts."""
+    from inference_engine_rust_b200.cache import Cache
+    from inference_engine_rust_b200.config.specs import LayerSpec
+    from inference_engine_rust_b200.parts import part_class
+    tdt = torch.float32 if dtype == "float32" else torch.bfloat16
+    rt = runtime(tdt)
+    H, heads, kvh, hd, I, eps = 80, 5, 5, 16, 112, 2e-5
+    norm_spec = spec("rmsnorm", eps=eps)
+    mixer_spec = spec("attention", hidden_size=H, heads=heads, kv_heads=kvh, head_dim=hd, window=None,
+                      scale=1 / math.sqrt(hd), position=spec("rope", theta=1e4, rotary_dim=hd, pairing="half"))
+    ffn_spec = spec("swiglu", hidden_size=H, intermediate_size=I)
+    ls = LayerSpec(block=spec("prenorm"), norm=norm_spec, mixer=mixer_spec, ffn=ffn_spec,
+                   mixer_prefix="model.layers.0.self_attn.", ffn_prefix="model.layers.0.mlp.",
+                   mixer_norm_name="model.layers.0.input_layernorm.weight",
+                   ffn_norm_name="model.layers.0.post_attention_layernorm.weight")
+    n1 = part_class("norm", "rmsnorm")(norm_spec, H, rt)
+    n2 = part_class("norm", "rmsnorm")(norm_spec, H, rt)
+    mixer = part_class("mixer", "attention")(mixer_spec, rt)
+    ffn = part_class("ffn", "swiglu")(ffn_spec, rt)
+    block = part_class("block", "prenorm")(ls, n1, mixer, n2, ffn, rt)
+    torch.manual_seed(2)
+    w = {ls.mixer_norm_name: (1 + 0.1 * torch.randn(H)).to(tdt), ls.ffn_norm_name: (1 + 0.1 * torch.randn(H)).to(tdt)}
+    for prefix, part in ((ls.mixer_prefix, mixer), (ls.ffn_prefix, ffn)):
+        for n, s in part.tensor_specs().items():
+            w[prefix + n] = (torch.randn(s.shape) * 0.15).to(tdt)
+    n1.load({"weight": w[ls.mixer_norm_name].to(DEV)})
+    n2.load({"weight": w[ls.ffn_norm_name].to(DEV)})
+    mixer.load({n: w[ls.mixer_prefix + n].to(DEV) for n in mixer.tensor_specs()})
+    ffn.load({n: w[ls.ffn_prefix + n].to(DEV) for n in ffn.tensor_specs()})
+    cache = Cache({0: mixer.cache_request()}, max_tokens=64 * 4, max_seq_len=256, max_sequences=2,
+                  dtype=tdt, device=DEV, poison=True)
+    lens = [33, 70]
+    slots = [cache.open_sequence() for _ in lens]
+    for s_, n in zip(slots, lens):
+        cache.reserve(s_, n)
+    cache.upload()
+    xs = [torch.randn(n, H) for n in lens]
+    x = torch.cat(xs).to(DEV)
+    block.forward(x, context(rt, lens, [0, 0], slots, "prompt"), cache.layer_view(0), True)
+    cfg = {"rms_norm_eps": eps, "num_attention_heads": heads, "num_key_value_heads": kvh, "head_dim": hd,
+           "rope_theta": 1e4, "sliding_window": None}
+    rnd = P.bf16_rounding if dtype == "bfloat16" else P.no_rounding
+    ref = torch.cat([P.block(xx, cfg, {k: v.float() for k, v in w.items()}, 0, rnd) for xx in xs])
+    compare(x, ref, dtype, "pre-norm block part")
