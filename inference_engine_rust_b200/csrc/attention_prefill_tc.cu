@@ -278,9 +278,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         *reinterpret_cast<uint4*>(p_s + r * 128 + ((q8 ^ (r & 7)) << 4)) = pk;
       }
       l += l0 + l1;
-#ifndef IERT_EXP_NO_PFENCE
       fence_proxy_async_smem();
-#endif
       mbar_arrive(p_ready);
     }
     if (ok && !wait_bar(pv_done, (n_tiles - 1) & 1, abort_flag)) ok = false;

@@ -15,11 +15,13 @@
 // (a fixed order: the result does not depend on which CTA finishes last) and writes the
 // output.  No CTA ever waits for another.
 //
-// Gated variant (GATED = true): the weight matrix is [gate; up] stacked by rows, a tile holds
+// Token-major variant (GATED = true), used for prompts.  Gated: the weight matrix is [gate; up] stacked by rows, a tile holds
 // 128 gate rows and the 128 up rows that belong to them as ONE 256-row operand on the MMA's N
 // side with 128 tokens on its M side (the full-rate 128 x 256 x 16 instruction), and the
 // epilogue (one token per thread) writes silu(gate) * up: the feed-forward's activation never goes
-// to memory unfused.  It runs whole tiles only (no split-K).
+// to memory unfused.  The same kernel with 256 consecutive weight rows per tile is the plain
+// prompt projection (store or add into the residual): a thread then owns one token's 16
+// consecutive outputs per chunk, so its loads and stores are 16-byte vectors.  Whole tiles only.
 //
 // Every wait on an mbarrier is bounded; when one runs out the kernel sets
 // IERT_ERR_WAIT_EXPIRED in the error word, drains its own TMA copies, frees its TMEM and
@@ -28,7 +30,6 @@
 #include "sm100.cuh"
 
 #include <mutex>
-#include <stdlib.h>
 #include <unordered_map>
 
 using namespace iert;
@@ -51,6 +52,8 @@ struct GemmParams {
   int out_dtype;
   int mode;
   int M, N, K;        // gated: N = rows of the gate half = columns of the output
+  int n_step;         // output columns a tile covers (token-major: 128 gated, 256 plain)
+  int second_rows;    // token-major: row of the second 128-row weight box, relative to the tile's first
   int t_tiles, n_tiles, splits, kb_total, kb_per_split, stages;
   float* ws;          // [tiles][splits][BT][TILE_N] fp32 partials (splits > 1)
   int* counters;      // [tiles] tickets, zero between launches
@@ -76,9 +79,10 @@ __device__ __forceinline__ void write_out_any(const GemmParams& p, int tok, int 
   else write_out<__nv_bfloat16>(p, tok, n, v);
 }
 
+// silu(g) * u = g * u / (1 + e^-g).  One exponential and one reciprocal per element (for very
+// negative g the exponential overflows to +inf and the quotient is 0, which is the limit).
 __device__ __forceinline__ float silu_mul(float g, float u) {
-  const float sg = g >= 0.f ? 1.0f / (1.0f + __expf(-g)) : __expf(g) / (1.0f + __expf(g));
-  return g * sg * u;
+  return __fdividef(g * u, 1.0f + __expf(-g));
 }
 
 template <int BT, bool GATED>
@@ -136,7 +140,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       int pend_kb[12], pend_t0[12];
       for (int work = blockIdx.x; ok && work < total_work; work += gridDim.x) {
         const int split = work % p.splits, tile = work / p.splits;
-        const int n0 = (tile / p.t_tiles) * TILE_N, t0 = (tile % p.t_tiles) * BT;
+        const int n0 = (tile / p.t_tiles) * p.n_step, t0 = (tile % p.t_tiles) * BT;
         const int kb0 = split * p.kb_per_split, kb1 = min(p.kb_total, kb0 + p.kb_per_split);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!dep_ready && issued == stages) {
@@ -149,7 +153,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           uint8_t* ws_ = smem + (size_t)stage * STAGE_BYTES;
           mbar_expect_tx(&full[stage], STAGE_BYTES);
           tma_load_2d(ws_, &map_w, &full[stage], kb * TILE_K, n0);
-          if (GATED) tma_load_2d(ws_ + W_STAGE_BYTES, &map_w, &full[stage], kb * TILE_K, p.N + n0);   // the up rows
+          if (GATED)   // the second 128 weight rows of the tile: the up rows (gated) or the next rows (plain)
+            tma_load_2d(ws_ + W_STAGE_BYTES, &map_w, &full[stage], kb * TILE_K, n0 + p.second_rows);
           if (dep_ready) tma_load_2d(ws_ + X_OFF, &map_x, &full[stage], kb * TILE_K, t0);
           else { pend_kb[issued] = kb; pend_t0[issued] = t0; }
           ++issued;
@@ -221,14 +226,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     bool ok = true;
     for (int work = blockIdx.x; ok && work < total_work; work += gridDim.x) {
       const int split = work % p.splits, tile = work / p.splits;
-      const int n0 = (tile / p.t_tiles) * TILE_N, t0 = (tile % p.t_tiles) * BT;
+      const int n0 = (tile / p.t_tiles) * p.n_step, t0 = (tile % p.t_tiles) * BT;
       const int n = n0 + n_local;
       const int t_valid = min(BT, p.M - t0);
       if (!wait_or_abort(&acc_full[acc], acc_phase, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * ACC_STRIDE);
       float* part = p.splits > 1 ? p.ws + ((size_t)(tile * p.splits + split) * BT) * TILE_N + n_local : nullptr;
-      if (GATED) {
+      if (GATED && p.mode == MODE_GATED_SILU) {
         // lane = token, columns [0, 128) = gate rows, [128, 256) = their up rows
         const int tok = t0 + n_local;
 #pragma unroll 1
@@ -250,6 +255,53 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
               for (int j = 0; j < 16; ++j)
                 if (n0 + c + j < p.N) o[j] = __float2bfloat16_rn(silu_mul(v[j], u[j]));
+            }
+          }
+        }
+      } else if (GATED) {
+        // token-major plain product: lane = token, 256 output columns per tile; a thread's 16
+        // values of a chunk are contiguous in memory (vector loads and stores)
+        const int tok = t0 + n_local;
+#pragma unroll 1
+        for (int c = 0; c < 2 * TILE_N; c += 16) {
+          if (n0 + c >= p.N) break;                    // warp-uniform
+          float v[16];
+          tmem_ld16(taddr + c, v);
+          if (tok >= p.M) continue;
+          const bool full16 = n0 + c + 16 <= p.N;
+          if (p.out_dtype == IERT_F32) {
+            float* o = (float*)p.out + (long long)tok * p.ldo + n0 + c;
+            if (full16 && (p.ldo & 3) == 0 && ((uintptr_t)p.out & 15) == 0) {
+              float4* o4 = reinterpret_cast<float4*>(o);
+              if (p.mode == MODE_ADD_RESIDUAL) {
+                float4 r[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) r[j] = o4[j];
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                  o4[j] = make_float4(r[j].x + v[4 * j], r[j].y + v[4 * j + 1], r[j].z + v[4 * j + 2], r[j].w + v[4 * j + 3]);
+              } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) o4[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (n0 + c + j < p.N) o[j] = p.mode == MODE_ADD_RESIDUAL ? o[j] + v[j] : v[j];
+            }
+          } else {
+            __nv_bfloat16* o = (__nv_bfloat16*)p.out + (long long)tok * p.ldo + n0 + c;
+            if (full16 && (p.ldo & 7) == 0 && ((uintptr_t)p.out & 15) == 0) {
+              uint4 w2[2];
+              __nv_bfloat162* wp = reinterpret_cast<__nv_bfloat162*>(w2);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) wp[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+              reinterpret_cast<uint4*>(o)[0] = w2[0];
+              reinterpret_cast<uint4*>(o)[1] = w2[1];
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (n0 + c + j < p.N) o[j] = __float2bfloat16_rn(v[j]);
             }
           }
         }
@@ -458,17 +510,36 @@ IERT_API int iert_gemm_tc(const void* x, long long ldx, const void* w, long long
   GemmParams p;
   p.out = out; p.ldo = ldo; p.out_dtype = out_dtype; p.mode = mode;
   p.M = M; p.N = N; p.K = K;
+  p.ws = ws; p.counters = counters; p.err = err;
+  if (!force_bt && !force_splits && M >= 128 && (mode == MODE_STORE || force_stages == -1)) {
+    // many tokens, plain store: 128 tokens on the MMA's M side, 256 weight rows on its N side
+    // (whole tiles).  Measured on 2,048 tokens: better than weight rows on M for stores (vector
+    // stores of a token's row), not for the residual add, which stays on the other kernel.
+    if (force_stages == -1) force_stages = 0;
+    p.n_step = 2 * TILE_N; p.second_rows = TILE_N;
+    p.n_tiles = (N + 2 * TILE_N - 1) / (2 * TILE_N);
+    p.t_tiles = (M + 127) / 128;
+    p.kb_total = (K + TILE_K - 1) / TILE_K;
+    p.splits = 1; p.kb_per_split = p.kb_total;
+    const int stage_bytes = 2 * W_STAGE_BYTES + 128 * TILE_K * 2;
+    int stages = force_stages ? force_stages : (226 * 1024 - 2048) / stage_bytes;
+    if (stages < 2 || (size_t)stages * stage_bytes + 1280 > 227 * 1024) return IERT_BAD_ARGUMENT;
+    p.stages = stages;
+    CUtensorMap mw, mx;
+    if (!tensor_map(w, N, K, ldw, TILE_N, &mw) || !tensor_map(x, M, K, ldx, 128, &mx)) return IERT_BAD_ARGUMENT;
+    const int tiles = p.n_tiles * p.t_tiles;
+    return launch<128, true>(mw, mx, p, tiles < sm_count() ? tiles : sm_count(), stream);
+  }
+  p.n_step = TILE_N; p.second_rows = 0;
   p.n_tiles = (N + TILE_N - 1) / TILE_N;
   p.t_tiles = (M + bt - 1) / bt;
   p.kb_total = (K + TILE_K - 1) / TILE_K;
-  p.ws = ws; p.counters = counters; p.err = err;
   const int tiles = p.n_tiles * p.t_tiles;
   const int stage_bytes = W_STAGE_BYTES + bt * TILE_K * 2;
   const int ctas_per_sm = bt <= 64 ? 2 : 1;
   const int slots = sm_count() * ctas_per_sm;
   const int smem_budget = (ctas_per_sm == 2 ? 113 : 226) * 1024 - 2048;
-  static const int env_stages = getenv("IERT_GEMM_STAGES") ? atoi(getenv("IERT_GEMM_STAGES")) : 0;
-  int stages = force_stages ? force_stages : (env_stages && bt <= 64 ? env_stages : smem_budget / stage_bytes);
+  int stages = force_stages ? force_stages : smem_budget / stage_bytes;
   if (stages > 12) stages = 12;
   if (stages < 2 || (size_t)stages * stage_bytes + 1280 > 227 * 1024) return IERT_BAD_ARGUMENT;
   p.stages = stages;
@@ -524,6 +595,7 @@ IERT_API int iert_gemm_tc_gated(const void* x, long long ldx, const void* w, lon
   GemmParams p;
   p.out = act; p.ldo = ldo; p.out_dtype = IERT_BF16; p.mode = MODE_GATED_SILU;
   p.M = M; p.N = inter; p.K = K;
+  p.n_step = TILE_N; p.second_rows = inter;
   p.n_tiles = (inter + TILE_N - 1) / TILE_N;
   p.t_tiles = (M + bt - 1) / bt;
   p.kb_total = (K + TILE_K - 1) / TILE_K;

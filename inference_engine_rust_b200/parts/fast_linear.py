@@ -6,9 +6,9 @@ import torch
 from ..csrc import bindings as B
 
 
-# Below this many tokens the fused kernel has too few tiles to fill the GPU (it cannot split K)
-# and the separate product + activation is faster.
-GATED_MIN_ROWS = int(__import__("os").environ.get("IERT_GATED_MIN_ROWS", "128"))
+# The fused kernel puts 128 tokens on the MMA's M side and cannot split K: below this many
+# tokens the separate product (split-K, thin token tile) + activation is faster.
+GATED_MIN_ROWS = 128
 
 
 def apply(linear, x, out, n_rows: int, mode: int, stream: int) -> bool:

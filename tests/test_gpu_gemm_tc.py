@@ -72,6 +72,16 @@ def test_many_tiles_per_cta():
     run(33, 40000, 128, B.GEMM_STORE, torch.float32)                           # 313 thin tiles
 
 
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (300, 1000, 264), (700, 640, 520), (2048, 384, 128)])
+def test_token_major_kernel_in_every_mode(M, N, K):
+    """Prompts: 128 tokens on the MMA's M side, 256 weight rows per tile; store (the default for
+    many tokens) and, forced, the residual add."""
+    from inference_engine_rust_b200.csrc import bindings as B
+    run(M, N, K, B.GEMM_STORE, torch.bfloat16)
+    run(M, N, K, B.GEMM_STORE, torch.float32)
+    run(M, N, K, B.GEMM_ADD_RESIDUAL, torch.float32, force_stages=-1)
+
+
 def test_refuses_what_tma_cannot_load():
     from inference_engine_rust_b200.csrc import bindings as B
     x = torch.randn(4, 100, device=DEV).bfloat16()
