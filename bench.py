@@ -228,7 +228,10 @@ def main() -> int:
         T = PREFILL_TOKENS
         flops = 2 * T * L * (H * qkv + qd * H + 3 * H * I) + 2 * H * V + L * 2 * T * T * qd
         prefill = {"value": round(T * 1e3 / pms, 1), "tokens": T, "ms": round(pms, 3),
-                   "frac": round(flops / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4), "unit": "tokens/s"}
+                   "frac": round(flops / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4), "unit": "tokens/s",
+                   "tflops": round(flops / (pms * 1e-3) / 1e12, 1), "peak_tflops": pk["bf16_tflops"]}
+        if "bf16_tflops_sustained" in pk:      # the step is tens of milliseconds of dense tensor work
+            prefill["frac_of_sustained"] = round(flops / (pms * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12), 4)
     clocks.stop()
 
     ms = main_stats["ms"]

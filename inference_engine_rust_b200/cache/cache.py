@@ -115,7 +115,9 @@ class KVGroup:
         if self.table.device.type == "cpu":
             self.table[rows] = torch.from_numpy(self.table_host[rows])
             return
-        if len(rows) * 4 >= self.n_slots:
+        # one copy of the whole table when it is small or many rows changed (each copy from
+        # pageable memory synchronises), else row by row
+        if self.table_host.nbytes <= (1 << 20) or len(rows) * 4 >= self.n_slots:
             self.table.copy_(torch.from_numpy(self.table_host), non_blocking=False)
         else:
             for r in rows:
