@@ -1,4 +1,4 @@
-"""Shared by the tests: the two tiny configurations (differing in every size and option),
+"""Shared by the tests: the tiny configurations (differing in every size and option),
 random model folders in temporary directories, weights for the plain implementation, and
 the comparison used for logits."""
 from __future__ import annotations
@@ -35,7 +35,16 @@ TINY_C = {
     "sliding_window": 70, "rms_norm_eps": 1e-5, "max_position_embeddings": 512,
     "tie_word_embeddings": True, "hidden_act": "silu", "bos_token_id": 1, "eos_token_id": 2,
 }
-TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+# Tiny D: sizes the tensor-core kernels do not take (widths that are no multiple of 8, head_dim
+# 24): every product and the attention fall back to the plain kernels, also in bfloat16.
+TINY_D = {
+    "architectures": ["MistralForCausalLM"], "model_type": "mistral",
+    "num_hidden_layers": 2, "hidden_size": 100, "num_attention_heads": 5, "num_key_value_heads": 1,
+    "head_dim": 24, "intermediate_size": 76, "vocab_size": 130, "rope_theta": 10000.0,
+    "sliding_window": 40, "rms_norm_eps": 1e-5, "max_position_embeddings": 512,
+    "tie_word_embeddings": False, "hidden_act": "silu", "bos_token_id": 1, "eos_token_id": 2,
+}
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
 
 WEIGHT_STD = 0.1      # larger than the customary 0.02 so that attention is not uniform
 

@@ -16,8 +16,9 @@ LENGTHS = {
     "A": [5, 11, 23, 70, 150],        # window 16, ring of 64 positions: 70 and 150 wrap it
     "B": [1, 7, 19, 40, 130],
     "C": [3, 64, 65, 129, 200],       # window 70, ring of 128 positions
+    "D": [2, 9, 41, 66, 90],          # sizes only the plain kernels take
 }
-CASES = [(c, d) for c in ("A", "B", "C") for d in ("float32", "bfloat16")]
+CASES = [(c, d) for c in ("A", "B", "C", "D") for d in ("float32", "bfloat16")]
 
 
 @functools.lru_cache(maxsize=None)
