@@ -48,12 +48,15 @@ class Attention(Mixer):
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         h = self.hidden_size
-        return {
+        specs = {
             "q_proj.weight": TensorSpec((self.q_dim, h)),
             "k_proj.weight": TensorSpec((self.kv_dim, h)),
             "v_proj.weight": TensorSpec((self.kv_dim, h)),
             "o_proj.weight": TensorSpec((h, self.q_dim)),
         }
+        # tensors of the position encoding, if it has any, live under "position."
+        specs.update({"position." + n: s for n, s in self.position.tensor_specs().items()})
+        return specs
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
         dt = self.rt.dtype
@@ -61,6 +64,7 @@ class Attention(Mixer):
                            tensors["v_proj.weight"].to(dt)], dim=0)
         self.qkv = Linear(fused, self.rt)
         self.o = Linear(tensors["o_proj.weight"], self.rt)
+        self.position.load({n[len("position."):]: t for n, t in tensors.items() if n.startswith("position.")})
 
     def cache_request(self) -> KVRequest:
         return KVRequest(self.kv_heads, self.head_dim, self.window)
@@ -73,9 +77,7 @@ class Attention(Mixer):
         kv = cache_view.struct
         qkv = ws.take("attn.qkv", (T, self.q_dim + 2 * self.kv_dim), rt.dtype)
         self.qkv.apply(xn, qkv, T, ctx.stream)
-        B.rope_kv_store(qkv, ctx.batch, kv, self.position.inv_freq, self.heads,
-                        self.position.rotary_dim, self.position.pairing, writes_cache,
-                        rt.err, ctx.stream)
+        self.position.encode_and_store(qkv, ctx, kv, self.heads, writes_cache)
         out = ws.take("attn.out", (T, self.q_dim), rt.dtype)
         from_cache = ctx.kind == "decode" or not writes_cache
         if from_cache and ctx.kind == "prompt":

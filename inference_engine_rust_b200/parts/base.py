@@ -6,7 +6,7 @@ learns which model it belongs to.  Adding a part means registering a class under
 kind; the configuration then names that kind for the layers that use it.
 
     norm      Norm(spec, hidden_size, rt)        .forward(x_f32, out, ctx, rows_idx=None, rows=None)
-    position  PositionEncoding(spec, head_dim, rt)
+    position  PositionEncoding(spec, head_dim, rt)   .encode_and_store(qkv, ctx, kv, heads, writes_cache)
     mixer     Mixer(spec, rt)                    .forward(xn, residual, ctx, cache_view, writes_cache)
     ffn       FeedForward(spec, rt)              .forward(xn, residual, ctx)
     block     Block(layer_spec, norm1, mixer, norm2, ffn, rt)   .forward(x, ctx, cache_view, writes_cache)
@@ -149,7 +149,12 @@ class Norm(Part):
 
 
 class PositionEncoding(Part):
-    pass
+    def encode_and_store(self, qkv, ctx: StepContext, kv, heads: int, writes_cache: bool) -> None:
+        """Give the step's queries and keys their positions, in place in `qkv`
+        ([tokens, (heads + 2 kv_heads) * head_dim], a token's absolute position being
+        ctx.batch.pos0[sequence] + its index in the sequence), then, if `writes_cache`, store
+        the keys and values in the cache `kv` (a csrc.bindings.KvView)."""
+        raise NotImplementedError
 
 
 class Mixer(Part):

@@ -1,7 +1,8 @@
 """Each part of a layer alone against the plain implementation, and the generality of the
 assembly: a toy mixer with state of its own, defined here, is registered, built and stepped
 without a change to the package; a layer is run twice; a layer reads another layer's
-cache; layers of one model use different mixers."""
+cache; layers of one model use different mixers, feed-forwards (one with routing) and position
+encodings."""
 import math
 from dataclasses import dataclass
 
@@ -347,3 +348,194 @@ def test_block_part_alone(dtype):
     rnd = P.bf16_rounding if dtype == "bfloat16" else P.no_rounding
     ref = torch.cat([P.block(xx, cfg, {k: v.float() for k, v in w.items()}, 0, rnd) for xx in xs])
     compare(x, ref, dtype, "pre-norm block part")
+
+
+# ---------------------------------------------------------------------------------------
+# two more toy parts, defined here: a feed-forward that routes each token to one of a few
+# experts, and a position encoding that is no rotation
+
+
+class TopOneExperts:
+    """y = p_e * W2_e . relu(W1_e . x) for the expert e with the largest router logit, p being the
+    softmax of the router logits (computed in 32-bit)."""
+
+    def __init__(self, part_spec, rt):
+        from inference_engine_rust_b200.parts.linear import Linear
+        self.rt, self.Linear = rt, Linear
+        self.hidden, self.inner, self.experts = (int(part_spec[k]) for k in ("hidden_size", "inner_size", "experts"))
+
+    def tensor_specs(self):
+        from inference_engine_rust_b200.weights import TensorSpec
+        specs = {"router.weight": TensorSpec((self.experts, self.hidden))}
+        for e in range(self.experts):
+            specs[f"experts.{e}.w1.weight"] = TensorSpec((self.inner, self.hidden))
+            specs[f"experts.{e}.w2.weight"] = TensorSpec((self.hidden, self.inner))
+        return specs
+
+    def load(self, tensors):
+        self.router = tensors["router.weight"].float()
+        self.w1 = [self.Linear(tensors[f"experts.{e}.w1.weight"], self.rt) for e in range(self.experts)]
+        self.w2 = [self.Linear(tensors[f"experts.{e}.w2.weight"], self.rt) for e in range(self.experts)]
+
+    def weight_bytes(self):
+        return sum(l.nbytes() for l in self.w1 + self.w2)
+
+    def forward(self, xn, residual, ctx):
+        T = ctx.n_tokens
+        p = torch.softmax(xn[:T].float() @ self.router.t(), dim=-1)
+        top = p.argmax(dim=-1)
+        for e in range(self.experts):
+            idx = torch.nonzero(top == e).flatten()
+            n = idx.numel()
+            if n == 0:
+                continue
+            h = torch.empty(n, self.inner, dtype=self.rt.dtype, device=xn.device)
+            self.w1[e].apply(xn[idx].contiguous(), h, n, ctx.stream)
+            y = torch.zeros(n, self.hidden, dtype=torch.float32, device=xn.device)
+            self.w2[e].apply(torch.relu(h), y, n, ctx.stream, add_residual=True)
+            residual.index_add_(0, idx, y * p[idx, e, None])
+
+
+class LearnedOffsets:
+    """Queries and keys get a learned vector added that depends on the position modulo `period`;
+    nothing is rotated."""
+
+    def __init__(self, part_spec, head_dim, rt):
+        self.rt, self.head_dim, self.period = rt, head_dim, int(part_spec["period"])
+
+    def tensor_specs(self):
+        from inference_engine_rust_b200.weights import TensorSpec
+        return {"offsets": TensorSpec((self.period, self.head_dim))}
+
+    def load(self, tensors):
+        self.offsets = tensors["offsets"].float()
+        self.no_freq = torch.zeros(1, dtype=torch.float32, device=self.rt.device)
+
+    def encode_and_store(self, qkv, ctx, kv, heads, writes_cache):
+        from inference_engine_rust_b200.csrc import bindings as B
+        pos = torch.cat([torch.arange(p0, p0 + q) for p0, q in zip(ctx.pos0, ctx.q_lens)]).to(qkv.device)
+        rows = qkv[:ctx.n_tokens].view(ctx.n_tokens, -1, self.head_dim)
+        n = heads + kv.kv_heads                     # queries and keys; values stay as they are
+        rows[:, :n] = (rows[:, :n].float() + self.offsets[pos % self.period][:, None, :]).to(qkv.dtype)
+        B.rope_kv_store(qkv, ctx.batch, kv, self.no_freq, heads, 0, B.PAIR_HALF, writes_cache, ctx.rt.err, ctx.stream)
+
+
+@dataclass(frozen=True)
+class RoutedToyConfig:
+    hidden_size: int
+    vocab_size: int
+    experts: int
+    period: int
+    architecture: str = "RoutedToyForCausalLM"
+
+    @classmethod
+    def from_dict(cls, raw):
+        return cls(raw["hidden_size"], raw["vocab_size"], raw["experts"], raw["period"])
+
+
+R_HEADS, R_KV, R_HD, R_INNER = 3, 1, 32, 40
+
+
+def routed_toy_spec(cfg: RoutedToyConfig):
+    from inference_engine_rust_b200.config.specs import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+    H = cfg.hidden_size
+    norm = PartSpec("rmsnorm", {"eps": 1e-5})
+
+    def attn(position):
+        return PartSpec("attention", {"hidden_size": H, "heads": R_HEADS, "kv_heads": R_KV, "head_dim": R_HD,
+                                      "window": None, "scale": R_HD ** -0.5, "position": position})
+    offsets = PartSpec("learned_offsets", {"period": cfg.period})
+    rope = PartSpec("rope", {"theta": 1e4, "rotary_dim": R_HD, "pairing": "half"})
+    routed = PartSpec("top_one_experts", {"hidden_size": H, "inner_size": R_INNER, "experts": cfg.experts})
+    dense = PartSpec("swiglu", {"hidden_size": H, "intermediate_size": 56})
+    layers = []
+    for i, (mixer, ffn) in enumerate(((attn(offsets), routed), (attn(rope), dense))):
+        p = f"toy.{i}."
+        layers.append(LayerSpec(block=PartSpec("prenorm", {}), norm=norm, mixer=mixer, ffn=ffn, mixer_prefix=p + "mix.",
+                                ffn_prefix=p + "ffn.", mixer_norm_name=p + "n1.weight", ffn_norm_name=p + "n2.weight"))
+    return ModelSpec(architecture=cfg.architecture, hidden_size=H, vocab_size=cfg.vocab_size, layers=tuple(layers),
+                     schedule=(ScheduleEntry(0, None), ScheduleEntry(1, None)), final_norm=norm,
+                     embedding_name="toy.embed.weight", final_norm_name="toy.norm.weight", lm_head_name="toy.head.weight",
+                     embedding_scale=1.0, max_position=256, bos_token_id=None, eos_token_id=None)
+
+
+def plain_routed_toy(cfg: RoutedToyConfig, w, ids):
+    T = len(ids)
+    x = P.embed(w["toy.embed.weight"], ids, 1.0)
+    # layer 0: attention whose queries and keys carry learned offsets, then the routed feed-forward
+    xn = P.rmsnorm(x, w["toy.0.n1.weight"], 1e-5)
+    off = w["toy.0.mix.position.offsets"][torch.arange(T) % cfg.period]
+    q = P.matmul(xn, w["toy.0.mix.q_proj.weight"]).view(T, R_HEADS, R_HD) + off[:, None]
+    k = P.matmul(xn, w["toy.0.mix.k_proj.weight"]).view(T, R_KV, R_HD) + off[:, None]
+    v = P.matmul(xn, w["toy.0.mix.v_proj.weight"]).view(T, R_KV, R_HD)
+    mask = torch.tril(torch.ones(T, T, dtype=torch.bool))
+    out = torch.zeros(T, R_HEADS, R_HD)
+    for h in range(R_HEADS):
+        s = (q[:, h] @ k[:, 0].t()) * R_HD ** -0.5
+        out[:, h] = P.softmax(s.masked_fill(~mask, float("-inf"))) @ v[:, 0]
+    x = x + P.matmul(out.reshape(T, -1), w["toy.0.mix.o_proj.weight"])
+    xn = P.rmsnorm(x, w["toy.0.n2.weight"], 1e-5)
+    p = P.softmax(P.matmul(xn, w["toy.0.ffn.router.weight"]))
+    y = torch.zeros_like(x)
+    chosen = []
+    for t in range(T):
+        e = int(p[t].argmax())
+        chosen.append(e)
+        hcur = torch.relu(P.matmul(xn[t:t + 1], w[f"toy.0.ffn.experts.{e}.w1.weight"]))
+        y[t] = p[t, e] * P.matmul(hcur, w[f"toy.0.ffn.experts.{e}.w2.weight"])[0]
+    x = x + y
+    # layer 1: the package's own attention with rotary positions and its dense feed-forward
+    xn = P.rmsnorm(x, w["toy.1.n1.weight"], 1e-5)
+    x = x + P.attention_layer(xn, *(w[f"toy.1.mix.{n}_proj.weight"] for n in "qkvo"), heads=R_HEADS, kv_heads=R_KV,
+                              head_dim=R_HD, rope_theta=1e4, window=None)
+    xn = P.rmsnorm(x, w["toy.1.n2.weight"], 1e-5)
+    x = x + P.ffn_layer(xn, w["toy.1.ffn.gate_proj.weight"], w["toy.1.ffn.up_proj.weight"], w["toy.1.ffn.down_proj.weight"])
+    return P.matmul(P.rmsnorm(x, w["toy.norm.weight"], 1e-5), w["toy.head.weight"]), chosen
+
+
+def test_routed_feed_forward_and_another_position_encoding():
+    """A feed-forward with routing and a position encoding that is no rotation, both defined in
+    this file, in one layer of a model whose other layer uses the package's own parts."""
+    from inference_engine_rust_b200 import LoadedModel
+    from inference_engine_rust_b200.config import registry
+    from inference_engine_rust_b200.parts import register_part, unregister_part
+    from inference_engine_rust_b200.weights import RandomSource
+    register_part("ffn", "top_one_experts", TopOneExperts)
+    register_part("position", "learned_offsets", LearnedOffsets)
+    registry.register_architecture("RoutedToyForCausalLM", RoutedToyConfig, routed_toy_spec)
+    try:
+        raw = {"architectures": ["RoutedToyForCausalLM"], "hidden_size": 72, "vocab_size": 113, "experts": 3, "period": 7}
+        model = LoadedModel.random(raw, seed=8, dtype="float32", std=0.15)
+        src = RandomSource(model.model.expected_tensors(), 8, 0.15, dtype=torch.float32)
+        w = {n: src.get(n) for n in src.names()}
+        assert "toy.0.mix.position.offsets" in w and "toy.0.ffn.experts.2.w2.weight" in w
+        assert not any(n.startswith("toy.1.mix.position") for n in w)
+        eng = model.session(max_tokens=64 * 6, poison_cache=True).engine
+        g = torch.Generator().manual_seed(1)
+        prompts = [torch.randint(0, 113, (n,), generator=g).tolist() for n in (45, 9, 66)]
+        want, chosen = zip(*(plain_routed_toy(model.config, w, p) for p in prompts))
+        assert len({e for c in chosen for e in c}) == 3, "the prompts do not reach every expert"
+        for p, ref in zip(prompts, want):
+            s = eng.open_sequence()
+            compare(eng.step([(s, p)], want="all"), ref, "float32", "routed toy, whole")
+            eng.close_sequence(s)
+        slots = [eng.open_sequence() for _ in prompts]
+        tails = [8, 3, 5]
+        got = [[] for _ in prompts]
+        out = eng.step([(s, p[:len(p) - t]) for s, p, t in zip(slots, prompts, tails)], want="all")
+        at = 0
+        for i, (p, t) in enumerate(zip(prompts, tails)):
+            got[i].append(out[at:at + len(p) - t])
+            at += len(p) - t
+        for k in range(max(tails)):
+            live = [i for i in range(3) if tails[i] > k]
+            out = eng.step([(slots[i], [prompts[i][len(prompts[i]) - tails[i] + k]]) for i in live], want="last")
+            for r, i in enumerate(live):
+                got[i].append(out[r:r + 1])
+        eng.check_device()
+        for i in range(3):
+            compare(torch.cat(got[i]), want[i], "float32", f"routed toy, request {i} batched and decoded")
+    finally:
+        unregister_part("ffn", "top_one_experts")
+        unregister_part("position", "learned_offsets")
+        registry._ARCHITECTURES.pop("RoutedToyForCausalLM", None)
