@@ -11,9 +11,14 @@
 // two accumulators in TMEM let the read-back of one tile overlap the MMAs of the next.
 //
 // Split-K (few tokens, few tiles): each split writes its fp32 partial tile to scratch memory
-// and takes a ticket; the CTA that draws the last ticket adds the partials in split order
-// (a fixed order: the result does not depend on which CTA finishes last) and writes the
-// output.  No CTA ever waits for another.
+// and counts itself in on the tile's counter.  The partials are added in split order (a fixed
+// order: the result does not depend on which CTA finishes when).  Who adds them:
+//   * every split its own share of the tile's token rows, once the counter shows that all
+//     partials are written, when the whole grid is resident at once (one work item per CTA and
+//     no more CTAs than the device holds, checked against the occupancy the driver reports):
+//     the addition is then spread over `splits` CTAs.  The wait for the counter is bounded
+//     like every other wait here;
+//   * otherwise the CTA that counts in last, alone, and no CTA waits for another.
 //
 // Token-major variant (GATED = true), used for prompts.  Gated: the weight matrix is [gate; up] stacked by rows, a tile holds
 // 128 gate rows and the 128 up rows that belong to them as ONE 256-row operand on the MMA's N
@@ -29,6 +34,7 @@
 #include "common.cuh"
 #include "sm100.cuh"
 
+#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 
@@ -57,6 +63,7 @@ struct GemmParams {
   int t_tiles, n_tiles, splits, kb_total, kb_per_split, stages;
   float* ws;          // [tiles][splits][BT][TILE_N] fp32 partials (splits > 1)
   int* counters;      // [tiles] tickets, zero between launches
+  int coop_reduce;    // splits > 1: every split adds its share of the rows (the grid is co-resident)
   int* err;
 };
 
@@ -77,6 +84,30 @@ __device__ __forceinline__ void write_out(const GemmParams& p, int tok, int n, f
 __device__ __forceinline__ void write_out_any(const GemmParams& p, int tok, int n, float v) {
   if (p.out_dtype == IERT_F32) write_out<float>(p, tok, n, v);
   else write_out<__nv_bfloat16>(p, tok, n, v);
+}
+
+// Four consecutive outputs of one token, vectorised when aligned and inside the matrix.
+__device__ __forceinline__ void write_out4(const GemmParams& p, int tok, int n, const float4& r) {
+  const bool whole = n + 4 <= p.N && (p.ldo & 3) == 0 && ((uintptr_t)p.out & 15) == 0;
+  if (whole && p.out_dtype == IERT_F32) {
+    float4* o = reinterpret_cast<float4*>((float*)p.out + (long long)tok * p.ldo + n);
+    if (p.mode == MODE_ADD_RESIDUAL) {
+      const float4 a = *o;
+      *o = make_float4(a.x + r.x, a.y + r.y, a.z + r.z, a.w + r.w);
+    } else {
+      *o = r;
+    }
+  } else if (whole && p.mode == MODE_STORE) {
+    uint2 w2;
+    *reinterpret_cast<__nv_bfloat162*>(&w2.x) = __floats2bfloat162_rn(r.x, r.y);
+    *reinterpret_cast<__nv_bfloat162*>(&w2.y) = __floats2bfloat162_rn(r.z, r.w);
+    *reinterpret_cast<uint2*>((__nv_bfloat16*)p.out + (long long)tok * p.ldo + n) = w2;
+  } else {
+    const float v[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      if (n + i < p.N) write_out_any(p, tok, n + i, v[i]);
+  }
 }
 
 // silu(g) * u = g * u / (1 + e^-g).  One exponential and one reciprocal per element (for very
@@ -341,45 +372,78 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       if (part) {
         __threadfence();
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (threadIdx.x == 64) *ticket_s = atomicAdd(&p.counters[tile], 1);
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (*ticket_s == p.splits - 1) {             // the last split of this tile: add in split order
-          __threadfence();
-          // 128 threads: 32 four-column chunks x 4 token rows per pass; all loads of a pass are
-          // issued before any is used, so a pass costs one round trip to L2
-          const int et = (int)threadIdx.x - 64, c4 = et & 31, tr = et >> 5;
-          const float* base = p.ws + ((size_t)tile * p.splits * BT) * TILE_N;
-          for (int t = tr; t < t_valid; t += 16) {      // 4 token rows x 4 splits = 16 loads in flight
-            float4 acc[4];
-#pragma unroll
-            for (int h = 0; h < 4; ++h) acc[h] = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int s0 = 0; s0 < p.splits; s0 += 4) {
-              float4 v[4][4];
-#pragma unroll
-              for (int h = 0; h < 4; ++h)
-#pragma unroll
-                for (int u = 0; u < 4; ++u)
-                  v[h][u] = (s0 + u < p.splits && t + 4 * h < t_valid)
-                                ? __ldcg(reinterpret_cast<const float4*>(base + ((size_t)(s0 + u) * BT + t + 4 * h) * TILE_N) + c4)
-                                : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-              for (int h = 0; h < 4; ++h)
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                  acc[h].x += v[h][u].x; acc[h].y += v[h][u].y; acc[h].z += v[h][u].z; acc[h].w += v[h][u].w;
-                }
+        const int et = (int)threadIdx.x - 64, c4 = et & 31, tr = et >> 5;
+        const float* base = p.ws + ((size_t)tile * p.splits * BT) * TILE_N;
+        if (p.coop_reduce) {
+          // count in, wait (bounded) until every split of the tile has, add this split's rows
+          if (threadIdx.x == 64) {
+            atomicAdd(&p.counters[tile], 1);
+            int seen = 0;
+            for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+              asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(p.counters + tile) : "memory");
+              if (seen >= p.splits) break;
+              __nanosleep(32);
             }
+            *ticket_s = seen >= p.splits ? 1 : 0;
+            if (seen < p.splits) atomicOr(p.err, IERT_ERR_WAIT_EXPIRED);
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (*ticket_s) {
+            const int rows_per = (t_valid + p.splits - 1) / p.splits;
+            const int r0 = split * rows_per, r1 = min(t_valid, r0 + rows_per);
+            for (int t = r0 + tr; t < r1; t += 4) {        // a token row per 32 threads, 8 splits in flight
+              float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+              for (int s0 = 0; s0 < p.splits; s0 += 8) {
+                float4 v[8];
 #pragma unroll
-            for (int h = 0; h < 4; ++h) {
-              if (t + 4 * h >= t_valid) break;
-              const int nn = n0 + c4 * 4, tok = t0 + t + 4 * h;
-              const float r[4] = {acc[h].x, acc[h].y, acc[h].z, acc[h].w};
+                for (int u = 0; u < 8; ++u)
+                  v[u] = s0 + u < p.splits
+                             ? __ldcg(reinterpret_cast<const float4*>(base + ((size_t)(s0 + u) * BT + t) * TILE_N) + c4)
+                             : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-              for (int i = 0; i < 4; ++i)
-                if (nn + i < p.N) write_out_any(p, tok, nn + i, r[i]);
+                for (int u = 0; u < 8; ++u) { a.x += v[u].x; a.y += v[u].y; a.z += v[u].z; a.w += v[u].w; }
+              }
+              write_out4(p, t0 + t, n0 + c4 * 4, a);
             }
           }
-          if (threadIdx.x == 64) p.counters[tile] = 0;
+          // count out; the last one out zeroes the counter for the next launch
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (threadIdx.x == 64 && atomicAdd(&p.counters[tile], 1) == 2 * p.splits - 1) p.counters[tile] = 0;
+        } else {
+          if (threadIdx.x == 64) *ticket_s = atomicAdd(&p.counters[tile], 1);
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (*ticket_s == p.splits - 1) {             // the last split of this tile: add in split order
+            __threadfence();
+            // 128 threads: 32 four-column chunks x 4 token rows per pass; all loads of a pass are
+            // issued before any is used, so a pass costs one round trip to L2
+            for (int t = tr; t < t_valid; t += 16) {      // 4 token rows x 4 splits = 16 loads in flight
+              float4 acc[4];
+#pragma unroll
+              for (int h = 0; h < 4; ++h) acc[h] = make_float4(0.f, 0.f, 0.f, 0.f);
+              for (int s0 = 0; s0 < p.splits; s0 += 4) {
+                float4 v[4][4];
+#pragma unroll
+                for (int h = 0; h < 4; ++h)
+#pragma unroll
+                  for (int u = 0; u < 4; ++u)
+                    v[h][u] = (s0 + u < p.splits && t + 4 * h < t_valid)
+                                  ? __ldcg(reinterpret_cast<const float4*>(base + ((size_t)(s0 + u) * BT + t + 4 * h) * TILE_N) + c4)
+                                  : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int h = 0; h < 4; ++h)
+#pragma unroll
+                  for (int u = 0; u < 4; ++u) {
+                    acc[h].x += v[h][u].x; acc[h].y += v[h][u].y; acc[h].z += v[h][u].z; acc[h].w += v[h][u].w;
+                  }
+              }
+#pragma unroll
+              for (int h = 0; h < 4; ++h) {
+                if (t + 4 * h >= t_valid) break;
+                write_out4(p, t0 + t + 4 * h, n0 + c4 * 4, acc[h]);
+              }
+            }
+            if (threadIdx.x == 64) p.counters[tile] = 0;
+          }
         }
       }
     }
@@ -457,6 +521,12 @@ bool tensor_map(const void* ptr, long long rows, long long cols, long long ld, i
   return true;
 }
 
+bool no_coop() {           // IERT_GEMM_COOP=0: the last split of a tile always adds alone
+  static int v = -1;
+  if (v < 0) { const char* e = getenv("IERT_GEMM_COOP"); v = (e && e[0] == '0') ? 1 : 0; }
+  return v == 1;
+}
+
 int sm_count() {
   static int n = 0;
   if (!n) {
@@ -479,6 +549,35 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, GemmParams p, int grid,
   }
   launch_dep(gemm_tc_kernel<BT, GATED>, dim3(grid), dim3(THREADS), smem, stream, mw, mx, p);
   return iert_check_launch("gemm_tc");
+}
+
+// CTAs of the weight-major kernel that one SM holds at once, as the driver reports it for the
+// kernel's registers, threads and shared memory (0 if the query fails).
+template <int BT>
+int ctas_per_sm_of(int stages) {
+  static int cached[13] = {0};
+  if (stages < 0 || stages > 12) return 0;
+  if (!cached[stages]) {
+    const size_t smem = (size_t)stages * (W_STAGE_BYTES + BT * TILE_K * 2) + 1024 + 256;
+    int n = 0;
+    if (cudaFuncSetAttribute(gemm_tc_kernel<BT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess ||
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, gemm_tc_kernel<BT, false>, THREADS, smem) != cudaSuccess) {
+      cudaGetLastError();
+      n = 0;
+    }
+    cached[stages] = n > 0 ? n : -1;
+  }
+  return cached[stages] > 0 ? cached[stages] : 0;
+}
+
+int resident_ctas_per_sm(int bt, int stages) {
+  switch (bt) {
+    case 16: return ctas_per_sm_of<16>(stages);
+    case 32: return ctas_per_sm_of<32>(stages);
+    case 64: return ctas_per_sm_of<64>(stages);
+    case 128: return ctas_per_sm_of<128>(stages);
+    default: return ctas_per_sm_of<256>(stages);
+  }
 }
 
 }  // namespace
@@ -520,7 +619,7 @@ IERT_API int iert_gemm_tc(const void* x, long long ldx, const void* w, long long
     p.n_tiles = (N + 2 * TILE_N - 1) / (2 * TILE_N);
     p.t_tiles = (M + 127) / 128;
     p.kb_total = (K + TILE_K - 1) / TILE_K;
-    p.splits = 1; p.kb_per_split = p.kb_total;
+    p.splits = 1; p.kb_per_split = p.kb_total; p.coop_reduce = 0;
     const int stage_bytes = 2 * W_STAGE_BYTES + 128 * TILE_K * 2;
     int stages = force_stages ? force_stages : (226 * 1024 - 2048) / stage_bytes;
     if (stages < 2 || (size_t)stages * stage_bytes + 1280 > 227 * 1024) return IERT_BAD_ARGUMENT;
@@ -548,7 +647,13 @@ IERT_API int iert_gemm_tc(const void* x, long long ldx, const void* w, long long
   if (force_splits) {
     splits = force_splits;
   } else if (tiles * 2 <= slots) {
-    splits = slots / tiles;
+    // Either one CTA per SM with a ring as deep as shared memory allows, or two per SM with
+    // half the ring each and twice the partial tiles to add.  Measured in whole decoding steps
+    // at 7B layer sizes: two per SM wins with 16-token tiles (partial tiles of 8 KB; two CTAs
+    // hide each other's start-up), one per SM from 32 tokens on.
+    const int one_per_sm = sm_count() / tiles, two_per_sm = slots / tiles;
+    const bool prefer_one = one_per_sm >= 1 && bt >= 32;
+    splits = prefer_one ? one_per_sm : two_per_sm;
     const int max_by_k = p.kb_total / 4 > 0 ? p.kb_total / 4 : 1;     // at least 4 k-blocks per split
     if (splits > max_by_k) splits = max_by_k;
     const int cap = bt >= 64 ? 4 : bt == 32 ? 8 : 16;   // partial tiles grow with the token tile
@@ -567,11 +672,20 @@ IERT_API int iert_gemm_tc(const void* x, long long ldx, const void* w, long long
     }
   }
   p.splits = splits;
+  const int total_work = tiles * splits;
+  if (!force_stages && ctas_per_sm == 2 && total_work <= sm_count()) {
+    // every CTA has an SM to itself: let its ring use the whole shared memory
+    stages = (226 * 1024 - 2048) / stage_bytes;
+    if (stages > 12) stages = 12;
+    p.stages = stages;
+  }
 
   CUtensorMap mw, mx;
   if (!tensor_map(w, N, K, ldw, TILE_N, &mw) || !tensor_map(x, M, K, ldx, bt, &mx)) return IERT_BAD_ARGUMENT;
-  const int total_work = tiles * splits;
   const int grid = total_work < slots ? total_work : slots;
+  // the splits of a tile may wait for one another only if every CTA of the grid is resident
+  p.coop_reduce = splits > 1 && !no_coop() && total_work <= grid &&
+                  grid <= sm_count() * resident_ctas_per_sm(bt, stages);
   switch (bt) {
     case 16: return launch<16, false>(mw, mx, p, grid, stream);
     case 32: return launch<32, false>(mw, mx, p, grid, stream);
@@ -599,7 +713,7 @@ IERT_API int iert_gemm_tc_gated(const void* x, long long ldx, const void* w, lon
   p.n_tiles = (inter + TILE_N - 1) / TILE_N;
   p.t_tiles = (M + bt - 1) / bt;
   p.kb_total = (K + TILE_K - 1) / TILE_K;
-  p.splits = 1; p.kb_per_split = p.kb_total;
+  p.splits = 1; p.kb_per_split = p.kb_total; p.coop_reduce = 0;
   p.ws = nullptr; p.counters = nullptr; p.err = err;
   const int tiles = p.n_tiles * p.t_tiles;
   const int stage_bytes = 2 * W_STAGE_BYTES + bt * TILE_K * 2;
