@@ -36,7 +36,13 @@ MISTRAL_7B = {
     "sliding_window": 4096, "rms_norm_eps": 1e-5, "max_position_embeddings": 32768,
     "tie_word_embeddings": False, "hidden_act": "silu", "bos_token_id": 1, "eos_token_id": 2,
 }
-FULL_LAYERS = 32
+# Other sizes of the same architecture, for measurements beyond the headline (--sizes).
+OTHER_SIZES = {
+    "7b-v0.3": dict(MISTRAL_7B, vocab_size=32768, rope_theta=1e6, sliding_window=None),
+    "nemo-12b": dict(MISTRAL_7B, num_hidden_layers=40, hidden_size=5120, vocab_size=131072, rope_theta=1e6,
+                     sliding_window=None, max_position_embeddings=131072),
+}
+SIZE_NAMES = {"7b-v0.1": "Mistral-7B-v0.1 sizes", "7b-v0.3": "Mistral-7B-v0.3 sizes", "nemo-12b": "Mistral-NeMo-12B sizes"}
 CONTEXT = 2048          # tokens each sequence holds when decoding starts
 MAX_CONTEXT = 4096      # the benchmark's context length: what each sequence's cache may grow to
 PREFILL_TOKENS = 2048
@@ -102,7 +108,10 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the configuration (reported)")
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (reported)")
+    ap.add_argument("--sizes", default="7b-v0.1", choices=sorted(SIZE_NAMES), help="layer sizes (default: the headline configuration)")
+    ap.add_argument("--max-context", type=int, default=MAX_CONTEXT, help="what each sequence's cache may grow to")
+    ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS)
     ap.add_argument("--points", default="1,64", help="other decode batch sizes to report, comma separated ('' = none)")
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--context", type=int, default=CONTEXT, help="tokens each sequence holds when decoding starts")
@@ -125,7 +134,11 @@ def main() -> int:
     from inference_engine_rust_b200.csrc import bindings as B
 
     pk = peaks()
-    cfg = dict(MISTRAL_7B, num_hidden_layers=a.layers)
+    base = MISTRAL_7B if a.sizes == "7b-v0.1" else OTHER_SIZES[a.sizes]
+    full_layers = base["num_hidden_layers"]
+    a.layers = a.layers or full_layers
+    a.max_context = max(a.max_context, a.context + 2 * (a.steps + a.warmup) + 8, a.prefill_tokens)
+    cfg = dict(base, num_hidden_layers=a.layers)
     t0 = time.time()
     model = LoadedModel.random(cfg, seed=0, dtype="bfloat16", std=0.02, on_device=True)
     torch.cuda.synchronize()
@@ -133,7 +146,7 @@ def main() -> int:
     batches = [a.batch] + [int(b) for b in a.points.split(",") if b.strip()]
     biggest = max(batches)
     per_seq = -(-(a.context + 2 * (a.steps + a.warmup) + 8) // 64) * 64     # the timed run and the end-to-end run
-    session = model.session(max_tokens=biggest * per_seq, max_sequences=biggest, max_seq_len=MAX_CONTEXT)
+    session = model.session(max_tokens=max(biggest * per_seq, -(-a.prefill_tokens // 64) * 64), max_sequences=biggest, max_seq_len=a.max_context)
     eng = session.engine
     sampler = Sampler(SamplingParams(temperature=0.0), eng.rt.err)
     rng = np.random.default_rng(0)
@@ -209,7 +222,7 @@ def main() -> int:
 
     prefill = None
     if not a.no_prefill:
-        prompt = rng.integers(0, vocab, PREFILL_TOKENS).tolist()
+        prompt = rng.integers(0, vocab, a.prefill_tokens).tolist()
         times = []
         for i in range(3 + 3):
             s = eng.open_sequence()
@@ -225,7 +238,7 @@ def main() -> int:
         H, I, V, L = cfg["hidden_size"], cfg["intermediate_size"], vocab, a.layers
         qkv = (cfg["num_attention_heads"] + 2 * cfg["num_key_value_heads"]) * cfg["head_dim"]
         qd = cfg["num_attention_heads"] * cfg["head_dim"]
-        T = PREFILL_TOKENS
+        T = a.prefill_tokens
         flops = 2 * T * L * (H * qkv + qd * H + 3 * H * I) + 2 * H * V + L * 2 * T * T * qd
         prefill = {"value": round(T * 1e3 / pms, 1), "tokens": T, "ms": round(pms, 3),
                    "frac": round(flops / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4), "unit": "tokens/s",
@@ -245,12 +258,12 @@ def main() -> int:
         "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic (random weights N(0, 0.02), uniform random token ids)",
         "impl": "ours",
-        "config": {"model": "Mistral-7B-v0.1 sizes", "layers": a.layers, "layers_of_config": FULL_LAYERS,
+        "config": {"model": SIZE_NAMES[a.sizes], "layers": a.layers, "layers_of_config": full_layers,
                    "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
                    "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
                    "intermediate": cfg["intermediate_size"], "vocab": vocab, "sliding_window": cfg["sliding_window"],
-                   "global_batch": a.batch, "seq_len": a.context, "max_context": MAX_CONTEXT,
-                   "prefill_tokens": PREFILL_TOKENS, "parallelism": "single GPU",
+                   "global_batch": a.batch, "seq_len": a.context, "max_context": a.max_context,
+                   "prefill_tokens": a.prefill_tokens, "parallelism": "single GPU",
                    "l2": "inputs larger than L2 (weights read per step exceed 126 MB many times)",
                    "peaks": pk["source"]},
         "e2e": {"value": round(a.batch * 1e3 / main_stats["e2e_ms"], 1), "unit": "tokens/s",
