@@ -8,6 +8,11 @@ the same option, src/bin/chat.rs:49-51).
 
     python -m inference_engine_rust_b200 -m DIR -n 32 "1 415 7 88"
     python -m inference_engine_rust_b200 random-model --config config.json --seed 0 --out DIR
+    python -m inference_engine_rust_b200 bench -m DIR [--json] [--runs 5] all --decode-tokens 128
+
+`bench` is the reference's bench_compare (src/bin/bench_compare.rs:30-87): the subcommands
+`all`, `cold-start`, `interactive-ttft` and `decode-throughput -n N`, with `-p/--prompt`,
+`--json`, `--min-decode-tps` and `--runs` (at least 5).
 """
 from __future__ import annotations
 
@@ -43,10 +48,105 @@ def _random_model(argv: List[str]) -> int:
     return 0
 
 
+def _bench(argv: List[str]) -> int:
+    from . import bench_metrics as M
+    ap = argparse.ArgumentParser(prog="inference_engine_rust_b200 bench",
+                                 description="Latency/throughput metrics of a model folder (cold TTFT, interactive TTFT, decode tok/s)")
+    ap.add_argument("-m", "--model", default="model/mistral-7b-v0.1", help="model folder")
+    ap.add_argument("-p", "--prompt", default=" ".join(str(t) for t in M.DEFAULT_BENCH_PROMPT), help="prompt as token ids")
+    ap.add_argument("--json", action="store_true", help="emit one JSON object")
+    ap.add_argument("--min-decode-tps", type=float, default=None,
+                    help="fail if measured decode tok/s is strictly below this (decode-throughput / all only)")
+    ap.add_argument("--runs", type=int, default=5, help="repetitions per command (minimum 5)")
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    ap.add_argument("--batch", type=int, default=1, help="sequences decoding together (the prompt is repeated)")
+    sub = ap.add_subparsers(dest="command", required=True)
+    p_all = sub.add_parser("all", help="cold start + interactive TTFT + decode throughput (single process)")
+    p_all.add_argument("--decode-tokens", type=int, default=128)
+    sub.add_parser("cold-start", help="from the folder on disk through the first greedy token id")
+    sub.add_parser("interactive-ttft", help="weights loaded, fresh cache: prompt evaluation + first token")
+    p_dec = sub.add_parser("decode-throughput", help="after a warm prefill, time greedy decode only")
+    p_dec.add_argument("-n", "--decode-tokens", type=int, default=128)
+    a = ap.parse_args(argv)
+    if a.runs < 5:
+        print("error: --runs must be at least 5 for stable comparisons", file=sys.stderr)   # bench_compare.rs:304-308
+        return 2
+    try:
+        prompt = parse_ids(a.prompt)
+    except ValueError as e:
+        print(f"error: {e}", file=sys.stderr)
+        return 2
+    if not prompt:
+        print("error: prompt is empty", file=sys.stderr)
+        return 2
+
+    def show(title, m):
+        print(f"=== {title} ===")
+        for k, v in m.items():
+            print(f"  {k + ':':26s}{v:.3f}" if isinstance(v, float) else f"  {k + ':':26s}{v}")
+
+    head = {"model": a.model, "prompt": prompt, "dtype": a.dtype}
+    try:
+        if a.command == "all":
+            runs = []
+            for _ in range(a.runs):
+                m = M.run_all(a.model, prompt, a.decode_tokens, dtype=a.dtype, batch=a.batch)
+                M.check_decode(m["decode"], a.min_decode_tps)
+                runs.append(m)
+            summary = {"interactive": M.summarize_interactive([r["interactive"] for r in runs]),
+                       "decode": M.summarize_decode([r["decode"] for r in runs])}
+            if a.json:
+                print(json.dumps({"suite": "all", **head,
+                                  "runs": {k: [r[k] for r in runs] for k in ("cold", "interactive", "decode")},
+                                  "summary": summary}))
+            else:
+                show("cold-start", runs[0]["cold"])
+                show("interactive-ttft (warm weights, fresh cache)", runs[0]["interactive"])
+                show("decode-throughput", runs[0]["decode"])
+                print(f"=== summary over {a.runs} runs ===")
+                print(f"  interactive: {json.dumps(summary['interactive'])}")
+                print(f"  decode:      {json.dumps(summary['decode'])}")
+        elif a.command == "cold-start":
+            if a.min_decode_tps is not None:
+                print("warning: --min-decode-tps ignored for cold-start", file=sys.stderr)
+            runs = [M.run_cold_start(a.model, prompt, dtype=a.dtype, batch=a.batch)[0] for _ in range(a.runs)]
+            if a.json:
+                print(json.dumps({"suite": "cold-start", **head, "runs": runs}))
+            else:
+                show("cold-start", runs[0])
+                print(f"  (showing run 1 of {a.runs}; use --json for all runs)")
+        else:
+            bench = M.EngineBench.load(a.model, dtype=a.dtype, batch=a.batch)
+            if a.command == "interactive-ttft":
+                runs = [bench.run_interactive_ttft(prompt) for _ in range(a.runs)]
+                summary = M.summarize_interactive(runs)
+                title = "interactive-ttft (warm weights, fresh cache)"
+            else:
+                runs = []
+                for _ in range(a.runs):
+                    m = bench.run_decode_throughput(prompt, a.decode_tokens)
+                    M.check_decode(m, a.min_decode_tps)
+                    runs.append(m)
+                summary = M.summarize_decode(runs)
+                title = "decode-throughput"
+            if a.json:
+                print(json.dumps({"suite": a.command, **head, "runs": runs, "summary": summary}))
+            else:
+                show(title, runs[0])
+                print(f"=== summary over {a.runs} runs ===")
+                print(f"  {json.dumps(summary)}")
+    except (RuntimeError, ValueError, OSError) as e:
+        print(f"error: {e}", file=sys.stderr)
+        return 1
+    return 0
+
+
 def main(argv: Optional[List[str]] = None) -> int:
     argv = list(sys.argv[1:] if argv is None else argv)
     if argv and argv[0] == "random-model":
         return _random_model(argv[1:])
+    if argv and argv[0] == "bench":
+        return _bench(argv[1:])
     ap = argparse.ArgumentParser(prog="inference_engine_rust_b200",
                                  description="Greedy or sampled generation from a model folder (token ids in, token ids out)")
     ap.add_argument("-m", "--model", default="model/mistral-7b-v0.1",

@@ -119,3 +119,25 @@ def test_request_ids_reach_the_sampler():
     generate(eng, sampler, [[1], [1]], 1, max_tokens=128, max_sequences=2, max_seq_len=64, page_tokens=64,
              request_ids=[7, 9])
     assert sampler.calls == [([7, 9], [0, 0])]
+
+
+def test_bench_summaries_and_arguments(capsys):
+    """The bench suite's statistics (src/bin/bench_compare.rs:234-300) and its argument checks."""
+    from inference_engine_rust_b200 import bench_metrics as M
+    from inference_engine_rust_b200.cli import main
+    assert M.median([3.0, 1.0, 2.0]) == 2.0 and M.median([4.0, 1.0, 2.0, 3.0]) == 2.5 and M.median([]) == 0.0
+    vals = [float(v) for v in range(1, 21)]
+    assert M.percentile(vals, 0.95) == 19.0 and M.percentile(vals, 0.0) == 1.0 and M.percentile(vals, 1.0) == 20.0
+    runs = [{"decode_tokens_per_sec": t, "decode_elapsed_ms": 1000.0 / t, "decode_tokens": 8} for t in (10.0, 30.0, 20.0)]
+    s = M.summarize_decode(runs)
+    assert s["runs"] == 3 and s["decode_tokens_per_sec"] == {"median": 20.0, "p95": 30.0, "min": 10.0, "max": 30.0}
+    with pytest.raises(ValueError):
+        M.summarize_decode([])
+    M.check_decode(runs[0], 10.0)
+    with pytest.raises(RuntimeError, match="min-decode-tps"):
+        M.check_decode(runs[0], 10.5)
+    with pytest.raises(RuntimeError, match="zero"):
+        M.check_decode(dict(runs[0], decode_tokens=0), None)
+    assert main(["bench", "--runs", "4", "cold-start"]) == 2 and "at least 5" in capsys.readouterr().err
+    assert main(["bench", "-p", "x y", "cold-start"]) == 2 and "token ids" in capsys.readouterr().err
+    assert main(["bench", "-m", "/nonexistent/folder", "cold-start"]) == 1

@@ -134,3 +134,29 @@ def test_command_line(loaded):
     assert out.returncode == 0 and out.stdout.strip().split() == [str(t) for t in want]
     bad = subprocess.run(cmd[:-1] + [""], cwd=ROOT, capture_output=True, text=True, timeout=300)
     assert bad.returncode != 0 and "prompt" in bad.stderr.lower()
+
+
+def test_bench_subcommand(loaded, capsys):
+    """The reference's bench suite (cold start, interactive TTFT, decode throughput) through the
+    command line's own entry, on a tiny model; the decode loop it times is the greedy loop."""
+    from inference_engine_rust_b200 import bench_metrics as M
+    from inference_engine_rust_b200.cli import main
+    folder, model, w = loaded["A"]
+    rc = main(["bench", "-m", folder, "--dtype", "float32", "--json", "-p", "3 9 27 81", "all", "--decode-tokens", "6"])
+    assert rc == 0
+    out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert out["suite"] == "all" and len(out["runs"]["decode"]) == 5
+    d = out["runs"]["decode"][0]
+    assert d["prompt_token_count"] == 4 and d["decode_tokens"] == 6 and d["decode_tokens_per_sec"] > 0
+    assert out["summary"]["decode"]["decode_tokens_per_sec"]["min"] <= out["summary"]["decode"]["decode_tokens_per_sec"]["median"]
+    c = out["runs"]["cold"][0]
+    assert c["cold_ttft_ms"] >= c["tensor_load_ms"] + c["prompt_eval_ms"]
+    i = out["runs"]["interactive"][0]
+    assert abs(i["ttft_infer_ms"] - i["prompt_eval_ms"] - i["lm_head_sample_ms"]) < 1e-6
+    # a floor no run can meet fails the command, as in the reference
+    rc = main(["bench", "-m", folder, "--dtype", "float32", "--min-decode-tps", "1e12", "-p", "3 9 27",
+               "decode-throughput", "-n", "3"])
+    assert rc == 1 and "--min-decode-tps" in capsys.readouterr().err
+    # a batch decodes together and counts every sequence's tokens
+    m = M.EngineBench(model, batch=3).run_decode_throughput([5, 6, 7], 4)
+    assert m["batch"] == 3 and m["decode_tokens"] == 4
