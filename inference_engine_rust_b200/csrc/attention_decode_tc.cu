@@ -88,7 +88,10 @@ attention_decode_tc_kernel(DecodeTcParams p, IertBatchView b, IertKvView c) {
   uint8_t* q_tile = smem + 2 * NSTAGE * TILE_BYTES;      // [16][ROW_BYTES]
 
   pdl_launch_dependents();     // the next kernel may start its preamble now
-  pdl_wait();                  // everything below may depend on the kernel before
+  // The kernel before this one wrote the queries and the newest key and value; the step's
+  // description, the page table and every older page are in place already.  So a CTA whose
+  // first pages are older than the newest one starts fetching them before it waits for that
+  // kernel.
   const int split = blockIdx.x, t = blockIdx.z;
   const int kvh = blockIdx.y / p.slices, slice = blockIdx.y % p.slices;
   const int group = p.heads / c.kv_heads;
@@ -102,6 +105,7 @@ attention_decode_tc_kernel(DecodeTcParams p, IertBatchView b, IertKvView c) {
   float* po = p.part_out + (((size_t)t * p.heads + head0) * p.splits + split) * HD;
   float* pml = p.part_ml + (((size_t)t * p.heads + head0) * p.splits + split) * 2;
   if (slot < 0) {
+    pdl_wait();                // the scratch may still be read by an earlier kernel's successor
     if (threadIdx.x < n_g) { pml[(size_t)threadIdx.x * p.splits * 2] = -INFINITY; pml[(size_t)threadIdx.x * p.splits * 2 + 1] = 0.f; }
     return;
   }
@@ -111,15 +115,6 @@ attention_decode_tc_kernel(DecodeTcParams p, IertBatchView b, IertKvView c) {
   const int per = (pg_hi - pg_lo + p.splits - 1) / p.splits;
   const int my_lo = pg_lo + split * per, my_hi = min(pg_hi, my_lo + per);
 
-  // queries of the group: rows 0..n_g-1 of a 16-row tile, the other rows zero
-  {
-    const __nv_bfloat16* q = p.qkv + (size_t)t * ((size_t)(p.heads + 2 * c.kv_heads) * HD) + (size_t)head0 * HD;
-    constexpr int CHUNKS = HD / 8;
-    for (int i = threadIdx.x; i < ROWS * CHUNKS; i += THREADS) {
-      const int r = i / CHUNKS, cc = i % CHUNKS;
-      cp16(q_tile + r * ROW_BYTES + cc * 16, q + (r < n_g ? r * HD + cc * 8 : 0), r < n_g);
-    }
-  }
   auto issue = [&](int pg, int buf) {
     const int page = c.page_table[(size_t)slot * c.table_width + pg % c.ring_pages];
     const bool ok = page >= 0 && page < c.n_pages;
@@ -129,11 +124,32 @@ attention_decode_tc_kernel(DecodeTcParams p, IertBatchView b, IertKvView c) {
     load_page(k_tile(buf), (const __nv_bfloat16*)c.k + off, lo, hi);
     load_page(v_tile(buf), (const __nv_bfloat16*)c.v + off, lo, hi);
   };
-  // one commit group per page, empty groups included, so that "all but the newest NSTAGE - 1
-  // groups have landed" always means "the page about to be used has landed"
+  // queries of the group: rows 0..n_g-1 of a 16-row tile, the other rows zero
+  auto load_queries = [&]() {
+    const __nv_bfloat16* q = p.qkv + (size_t)t * ((size_t)(p.heads + 2 * c.kv_heads) * HD) + (size_t)head0 * HD;
+    constexpr int CHUNKS = HD / 8;
+    for (int i = threadIdx.x; i < ROWS * CHUNKS; i += THREADS) {
+      const int r = i / CHUNKS, cc = i % CHUNKS;
+      cp16(q_tile + r * ROW_BYTES + cc * 16, q + (r < n_g ? r * HD + cc * 8 : 0), r < n_g);
+    }
+  };
+  // One commit group per page, empty groups included, in the order of use, so that "all but
+  // the newest NSTAGE - 1 groups have landed" always means "the page about to be used has
+  // landed".  The queries travel in the first group, or, with `early`, in a group of their own
+  // behind the first pages.  `early`: none of the first NSTAGE - 1
+  // pages is the newest page (whose last row the kernel before this one writes), and a page of
+  // a ring cannot be overwritten while it is read (the newest key lands in the newest page).
+  const bool early = my_lo + NSTAGE - 1 <= pos / PAGE;
+  if (!early) pdl_wait();
+  if (!early) load_queries();
 #pragma unroll
   for (int i = 0; i < NSTAGE - 1; ++i) {
     if (my_lo + i < my_hi) issue(my_lo + i, i);
+    cp_commit();
+  }
+  if (early) {
+    pdl_wait();
+    load_queries();              // a group of their own, younger than the first pages: see the first wait
     cp_commit();
   }
 
@@ -147,7 +163,8 @@ attention_decode_tc_kernel(DecodeTcParams p, IertBatchView b, IertKvView c) {
     const int buf = (pg - my_lo) % NSTAGE;
     if (pg + NSTAGE - 1 < my_hi) issue(pg + NSTAGE - 1, (pg - my_lo + NSTAGE - 1) % NSTAGE);
     cp_commit();
-    cp_wait<NSTAGE - 1>();
+    if (early && pg == my_lo) cp_wait<1>();      // the queries' group is the second youngest here
+    else cp_wait<NSTAGE - 1>();
     __syncthreads();
     if (pg == my_lo) {
 #pragma unroll

@@ -3,7 +3,9 @@
 // back.  Scores and the output accumulate in tensor memory; queries, keys, values come by TMA
 // (128-byte swizzle) straight from the step's packed projection.
 //
-//   grid (query tiles, heads, sequences); a CTA owns 128 consecutive queries of one head.
+//   grid (heads, query tiles, sequences); a CTA owns 128 consecutive queries of one head.  Blocks
+//   are handed out in index order, so all heads' longest tiles (the last queries) start first
+//   and the short ones fill the tail.
 //   Two CTAs share an SM (half of its shared memory, tensor memory and registers each), so one
 //   CTA's softmax overlaps the other's MMAs and loads.
 //   warp 4      TMA producer: the query tile once, then key and value tiles of 64 positions
@@ -92,7 +94,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   uint32_t* tmem_slot = (uint32_t*)(bars + 15);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
-  const int s = blockIdx.z, head = blockIdx.y;
+  const int s = blockIdx.z, head = blockIdx.x;
   if (b.slot_ids[s] < 0) return;
   if (smem_addr(smem) & 1023u) {                             // never expected; refuse rather than compute garbage
     if (threadIdx.x == 0) atomicOr(p.err, IERT_ERR_WAIT_EXPIRED);
@@ -100,7 +102,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   }
   const int q_begin = b.cu_q[s], len = b.cu_q[s + 1] - q_begin;
   const int n_qt = (len + BM - 1) / BM;
-  const int qt = n_qt - 1 - (int)blockIdx.x;                 // the longest tiles start first
+  const int qt = n_qt - 1 - (int)blockIdx.y;                 // the longest tiles start first
   if (qt < 0) return;
   const int i0 = qt * BM;
   const int kvh = head / (p.heads / p.kv_heads);
@@ -323,7 +325,7 @@ IERT_API int iert_attention_prefill_tc(const void* qkv, void* out, const IertBat
                                        int kv_heads, int window, float scale, int max_q_len, int* err,
                                        cudaStream_t stream) {
   if (batch->n_tokens <= 0 || max_q_len <= 0) return IERT_OK;
-  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || heads > 65535 || batch->n_seqs > 65535 ||
+  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || (max_q_len + BM - 1) / BM > 65535 || batch->n_seqs > 65535 ||
       ((uintptr_t)qkv & 15) || ((uintptr_t)out & 15))
     return IERT_BAD_ARGUMENT;
   const long long width = (long long)(heads + 2 * kv_heads) * HD;
@@ -345,7 +347,7 @@ IERT_API int iert_attention_prefill_tc(const void* qkv, void* out, const IertBat
     }
     configured = true;
   }
-  dim3 grid((max_q_len + BM - 1) / BM, heads, batch->n_seqs);
+  dim3 grid(heads, (max_q_len + BM - 1) / BM, batch->n_seqs);
   attention_prefill_tc_kernel<<<grid, THREADS, smem, stream>>>(map_q, map_kv, p, *batch);
   return cudaGetLastError() == cudaSuccess ? IERT_OK : IERT_CUDA_ERROR;
 }

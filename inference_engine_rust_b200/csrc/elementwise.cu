@@ -151,10 +151,11 @@ __global__ void rope_kv_store_kernel(T* __restrict__ qkv, IertBatchView b, IertK
   const int hd = c.head_dim, nkv = c.kv_heads;
   const int half = rotary_dim / 2;
   const int total_heads = heads + 2 * nkv;
-  pdl_wait();                  // everything below may depend on the kernel before
+  // The step's description (sequence, slot, position) and the angles do not depend on the
+  // kernel before this one, only the projection does: everything up to the first read of
+  // `qkv` runs while that kernel finishes.
   const int s = b.tok_seq[t];
-  if (s < 0) return;
-  const int slot = b.slot_ids[s];
+  const int slot = s < 0 ? -1 : b.slot_ids[s];
   if (slot < 0) return;
   const int q_begin = b.cu_q[s], q_len = b.cu_q[s + 1] - q_begin;
   const int pos = b.pos0[s] + (t - q_begin);
@@ -166,6 +167,7 @@ __global__ void rope_kv_store_kernel(T* __restrict__ qkv, IertBatchView b, IertK
     cs[half + k] = sn;
   }
   __syncthreads();
+  pdl_wait();                  // the projection is complete from here on
   const bool store = write_cache && pos >= final_len - c.ring_pages * c.page_tokens;
   T* row = qkv + (size_t)t * total_heads * hd;
   // this block's heads: [h0, h1) of [queries | keys | values]
