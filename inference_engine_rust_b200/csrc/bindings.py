@@ -156,6 +156,17 @@ def rmsnorm(x, w, out, eps: float, stream, rows_idx=None, rows: Optional[int] = 
                               n, hidden, eps, stream), "rmsnorm")
 
 
+_SM_COUNT = None
+
+
+def sm_count() -> int:
+    """Streaming multiprocessors of the current device."""
+    global _SM_COUNT
+    if _SM_COUNT is None:
+        _SM_COUNT = int(core().iert_sm_count())
+    return _SM_COUNT
+
+
 def rope_kv_store(qkv, batch: BatchView, kv: KvView, inv_freq, heads: int, rotary_dim: int,
                   pairing: int, write_cache: bool, err, stream) -> None:
     check(core().iert_rope_kv_store(qkv.data_ptr(), dtype_code(qkv.dtype), byref(batch), byref(kv),

@@ -49,6 +49,7 @@ constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;
 constexpr int W_STAGE_BYTES = TILE_N * TILE_K * 2;
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
+constexpr int XCH_BYTES = 16 * 64 * 4 + 16;   // weight-major gated tile: 16 tokens x 64 up values, aligned
 
 enum : int { MODE_STORE = 0, MODE_ADD_RESIDUAL = 1, MODE_GATED_SILU = 2 };
 
@@ -140,6 +141,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
   int* ticket_s = (int*)(tmem_slot + 2);
+  uint8_t* xch_s = (uint8_t*)(((uintptr_t)(tmem_slot + 4) + 15) & ~(uintptr_t)15);   // 4 KB, weight-major gated only
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
@@ -186,6 +188,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           tma_load_2d(ws_, &map_w, &full[stage], kb * TILE_K, n0);
           if (GATED)   // the second 128 weight rows of the tile: the up rows (gated) or the next rows (plain)
             tma_load_2d(ws_ + W_STAGE_BYTES, &map_w, &full[stage], kb * TILE_K, n0 + p.second_rows);
+          else if (p.mode == MODE_GATED_SILU)   // weight-major gated: 64 gate rows (above), then their 64 up rows
+            tma_load_2d(ws_ + W_STAGE_BYTES / 2, &map_w, &full[stage], kb * TILE_K, n0 + p.second_rows);
           if (dep_ready) tma_load_2d(ws_ + X_OFF, &map_x, &full[stage], kb * TILE_K, t0);
           else { pend_kb[issued] = kb; pend_t0[issued] = t0; }
           ++issued;
@@ -337,8 +341,36 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           }
         }
       }
+      if (!GATED && p.mode == MODE_GATED_SILU) {
+        // Weight-major gated tile: TMEM lanes 0-63 hold 64 gate rows, lanes 64-127 the up rows
+        // that belong to them.  The up warps hand their values over through shared memory, the
+        // gate warps write silu(gate) * up, 64 consecutive outputs of a token per pair of warps.
+        float* xch = reinterpret_cast<float*>(xch_s);                 // [16 tokens][64]
 #pragma unroll 1
-      for (int c = 0; !GATED && c < BT; c += 16) {
+        for (int c = 0; c < BT; c += 16) {
+          if (c >= t_valid) break;                   // uniform over the four warps
+          float v[16];
+          tmem_ld16(taddr + c, v);
+          if (q >= 2) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) xch[j * 64 + (n_local - 64)] = v[j];
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (q < 2) {
+            const int i = n0 + n_local;              // n0 counts gate rows here (64 per tile)
+            if (i < p.N) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (c + j < t_valid)
+                  ((__nv_bfloat16*)p.out)[(long long)(t0 + c + j) * p.ldo + i] =
+                      __float2bfloat16_rn(silu_mul(v[j], xch[j * 64 + n_local]));
+            }
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
+      }
+#pragma unroll 1
+      for (int c = 0; !GATED && p.mode != MODE_GATED_SILU && c < BT; c += 16) {
         if (c >= t_valid) break;                     // warp-uniform
         float v[16];
         tmem_ld16(taddr + c, v);
@@ -540,7 +572,8 @@ int sm_count() {
 template <int BT, bool GATED>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, GemmParams p, int grid, cudaStream_t stream) {
   constexpr int STAGE_BYTES = (GATED ? 2 : 1) * W_STAGE_BYTES + BT * TILE_K * 2;
-  const size_t smem = (size_t)p.stages * STAGE_BYTES + 1024 + 256;
+  // ring, alignment slack, barriers; the weight-major gated tile adds its exchange buffer
+  const size_t smem = (size_t)p.stages * STAGE_BYTES + 1024 + 256 + ((!GATED && p.mode == MODE_GATED_SILU) ? XCH_BYTES : 0);
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(gemm_tc_kernel<BT, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess)
@@ -704,11 +737,40 @@ IERT_API int iert_gemm_tc_gated(const void* x, long long ldx, const void* w, lon
   if (M <= 0 || inter <= 0) return IERT_OK;
   if (K <= 0 || (K & 7) || (ldx & 7) || (ldw & 7) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15))
     return IERT_BAD_ARGUMENT;
-  const int bt = 128;                                  // tokens per tile: the MMA's M side
-  (void)force_bt;
   GemmParams p;
   p.out = act; p.ldo = ldo; p.out_dtype = IERT_BF16; p.mode = MODE_GATED_SILU;
   p.M = M; p.N = inter; p.K = K;
+  const bool weight_major = force_bt ? (force_bt != 128 && M <= force_bt)
+                                     : (M <= 64 && (inter + TILE_N / 2 - 1) / (TILE_N / 2) >= sm_count());
+  if (force_bt && force_bt != 16 && force_bt != 32 && force_bt != 64 && force_bt != 128) return IERT_BAD_ARGUMENT;
+  if (force_bt && force_bt != 128 && M > force_bt) return IERT_BAD_ARGUMENT;
+  if (weight_major) {
+    // Few tokens (decoding): weight rows on the MMA's M side, 64 gate rows and their 64 up rows
+    // per tile, no split over k.  Chosen when its tiles alone fill the device; for smaller
+    // matrices the caller does better with the split product and a separate activation.
+    const int wbt = force_bt ? force_bt : (M <= 16 ? 16 : M <= 32 ? 32 : 64);
+    p.n_step = TILE_N / 2; p.second_rows = inter;
+    p.n_tiles = (inter + TILE_N / 2 - 1) / (TILE_N / 2);
+    p.t_tiles = 1;
+    p.kb_total = (K + TILE_K - 1) / TILE_K;
+    p.splits = 1; p.kb_per_split = p.kb_total; p.coop_reduce = 0;
+    p.ws = nullptr; p.counters = nullptr; p.err = err;
+    const int stage_bytes = W_STAGE_BYTES + wbt * TILE_K * 2;
+    int stages = force_stages ? force_stages : (113 * 1024 - 2048 - XCH_BYTES) / stage_bytes;
+    if (stages > 12) stages = 12;
+    if (stages < 2 || (size_t)stages * stage_bytes + 1280 + XCH_BYTES > 227 * 1024) return IERT_BAD_ARGUMENT;
+    p.stages = stages;
+    CUtensorMap mw, mx;
+    if (!tensor_map(w, 2ll * inter, K, ldw, TILE_N / 2, &mw) || !tensor_map(x, M, K, ldx, wbt, &mx)) return IERT_BAD_ARGUMENT;
+    const int slots = 2 * sm_count();
+    const int grid = p.n_tiles < slots ? p.n_tiles : slots;
+    switch (wbt) {
+      case 16: return launch<16, false>(mw, mx, p, grid, stream);
+      case 32: return launch<32, false>(mw, mx, p, grid, stream);
+      default: return launch<64, false>(mw, mx, p, grid, stream);
+    }
+  }
+  const int bt = 128;                                  // tokens per tile: the MMA's M side
   p.n_step = TILE_N; p.second_rows = inter;
   p.n_tiles = (inter + TILE_N - 1) / TILE_N;
   p.t_tiles = (M + bt - 1) / bt;

@@ -108,7 +108,7 @@ def test_row_results_do_not_depend_on_the_batch():
 
 
 @pytest.mark.parametrize("M,I,K", [(1, 128, 64), (8, 200, 136), (40, 160, 96), (100, 384, 512), (300, 1000, 264),
-                                   (64, 14336, 256)])
+                                   (64, 14336, 256), (8, 14336, 512), (33, 9600, 128)])
 def test_gated_product_is_silu_gate_times_up(M, I, K):
     """The fused feed-forward entry: two accumulators per tile, activation in the epilogue."""
     from inference_engine_rust_b200.csrc import bindings as B
@@ -117,7 +117,10 @@ def test_gated_product_is_silu_gate_times_up(M, I, K):
     w = (torch.randn(2 * I, K, device=DEV, generator=g) * (2.0 / K ** 0.5)).bfloat16()
     act = torch.full((M, I), float("nan"), device=DEV, dtype=torch.bfloat16)
     err = torch.zeros(1, dtype=torch.int32, device=DEV)
-    for force in ({}, {"force_stages": 2}):
+    forces = [{}, {"force_stages": 2}, {"force_bt": 128}]
+    # the decoding form (weight rows on the MMA's M side) at every token tile that holds M
+    forces += [{"force_bt": bt} for bt in (16, 32, 64) if M <= bt] + ([{"force_bt": 64, "force_stages": 2}] if M <= 64 else [])
+    for force in forces:
         act.fill_(float("nan"))
         assert B.gemm_tc_gated(x, w, act, M, err, B.stream_ptr(), **force)
         torch.cuda.synchronize()
