@@ -14,6 +14,12 @@
 //   partial result (unnormalised output, maximum, sum) goes to scratch memory.  A second
 //   kernel merges the splits in split order.
 //
+// Optionally the rotary position encoding and the cache write of the step are part of this
+// kernel (angle pos * theta^(-2k/d) in fp32, src/ops/rope.rs:40-57; rotate, then store, then
+// attend, src/layers/attention.rs:577-606): every CTA rotates its group's queries as it stages
+// them; the CTA that owns the newest page rotates the new key, puts the new key and value row
+// into that page's tile in shared memory, and (one CTA per kv head) writes both to the cache.
+//
 // Visible keys: [max(0, pos + 1 - W), pos] (src/layers/attention.rs:609-613); scale from the
 // caller; softmax in fp32 (src/ops/softmax.rs:11-25).
 #include "common.cuh"
@@ -41,6 +47,11 @@ struct DecodeTcParams {
   int heads, splits, slices, gt;
   float scale_log2e;
   int* err;
+  // Fused position encoding (rope != 0): `qkv` comes straight from the projection; the kernel
+  // rotates the queries and the new key itself and, if store != 0, writes the new key and
+  // value into the cache.  With rope == 0 the kernel before has done all of that.
+  const float* inv_freq;      // [rotary_dim / 2]
+  int rope, rotary_dim, pairing, store;
 };
 
 __device__ __forceinline__ void cp16(void* smem_dst, const void* gsrc, bool valid) {
@@ -86,6 +97,8 @@ attention_decode_tc_kernel(DecodeTcParams p, IertBatchView b, IertKvView c) {
   auto k_tile = [&](int i) { return smem + (size_t)(2 * i) * TILE_BYTES; };
   auto v_tile = [&](int i) { return smem + (size_t)(2 * i + 1) * TILE_BYTES; };
   uint8_t* q_tile = smem + 2 * NSTAGE * TILE_BYTES;      // [16][ROW_BYTES]
+  float* cs_tab = reinterpret_cast<float*>(q_tile + ROWS * ROW_BYTES);   // [HD / 2] cos, [HD / 2] sin (fused rope)
+  __nv_bfloat16* new_kv = reinterpret_cast<__nv_bfloat16*>(cs_tab + HD);  // [2][HD]: the step's own key and value
 
   pdl_launch_dependents();     // the next kernel may start its preamble now
   // The kernel before this one wrote the queries and the newest key and value; the step's
@@ -115,18 +128,54 @@ attention_decode_tc_kernel(DecodeTcParams p, IertBatchView b, IertKvView c) {
   const int per = (pg_hi - pg_lo + p.splits - 1) / p.splits;
   const int my_lo = pg_lo + split * per, my_hi = min(pg_hi, my_lo + per);
 
+  // this CTA's range holds the newest page and the kernel has to supply the newest row itself
+  const bool own_new_row = p.rope && p.store && my_lo < my_hi && my_hi == pg_hi;
+  const int half = p.rotary_dim / 2;
+  if (p.rope) {                                          // angles: no dependency on the kernel before
+    for (int k = threadIdx.x; k < half; k += THREADS) {
+      float sn, cs_;
+      sincosf((float)pos * p.inv_freq[k], &sn, &cs_);
+      cs_tab[k] = cs_;
+      cs_tab[half + k] = sn;
+    }
+  }
   auto issue = [&](int pg, int buf) {
     const int page = c.page_table[(size_t)slot * c.table_width + pg % c.ring_pages];
     const bool ok = page >= 0 && page < c.n_pages;
     if (!ok && threadIdx.x == 0) atomicOr(p.err, IERT_ERR_PAGE_RANGE);
     const size_t off = (((size_t)(ok ? page : 0) * c.kv_heads + kvh) * PAGE) * HD;
-    const int lo = ok ? max(0, j_min - pg * PAGE) : PAGE, hi = ok ? min(PAGE - 1, pos - pg * PAGE) : -1;
+    const int lo = ok ? max(0, j_min - pg * PAGE) : PAGE;
+    int hi = ok ? min(PAGE - 1, pos - pg * PAGE) : -1;
+    if (own_new_row && pg == pos / PAGE) --hi;           // the newest row comes from the projection, below
     load_page(k_tile(buf), (const __nv_bfloat16*)c.k + off, lo, hi);
     load_page(v_tile(buf), (const __nv_bfloat16*)c.v + off, lo, hi);
   };
   // queries of the group: rows 0..n_g-1 of a 16-row tile, the other rows zero
+  const __nv_bfloat16* tok_row = p.qkv + (size_t)t * ((size_t)(p.heads + 2 * c.kv_heads) * HD);
+  // v[i0], v[i1] of a head rotated by the angle of pair k, fp32 math, bf16 out
+  auto rotate_into = [&](const __nv_bfloat16* src, __nv_bfloat16* dst, int k) {
+    const int i0 = p.pairing == IERT_PAIR_HALF ? k : 2 * k;
+    const int i1 = p.pairing == IERT_PAIR_HALF ? k + half : 2 * k + 1;
+    const float a = __bfloat162float(src[i0]), bb = __bfloat162float(src[i1]);
+    dst[i0] = __float2bfloat16_rn(a * cs_tab[k] - bb * cs_tab[half + k]);
+    dst[i1] = __float2bfloat16_rn(a * cs_tab[half + k] + bb * cs_tab[k]);
+  };
   auto load_queries = [&]() {
-    const __nv_bfloat16* q = p.qkv + (size_t)t * ((size_t)(p.heads + 2 * c.kv_heads) * HD) + (size_t)head0 * HD;
+    const __nv_bfloat16* q = tok_row + (size_t)head0 * HD;
+    if (p.rope) {
+      __syncthreads();                                   // the angle table is complete
+      for (int i = threadIdx.x; i < ROWS * (HD / 2); i += THREADS) {
+        const int r = i / (HD / 2), k = i % (HD / 2);
+        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(q_tile + r * ROW_BYTES);
+        if (r >= n_g) { dst[2 * k] = __float2bfloat16_rn(0.f); dst[2 * k + 1] = __float2bfloat16_rn(0.f); }
+        else if (k < half) rotate_into(q + r * HD, dst, k);
+        else {                                           // dimensions beyond rotary_dim pass through
+          const int d = p.rotary_dim + 2 * (k - half);
+          dst[d] = q[r * HD + d]; dst[d + 1] = q[r * HD + d + 1];
+        }
+      }
+      return;
+    }
     constexpr int CHUNKS = HD / 8;
     for (int i = threadIdx.x; i < ROWS * CHUNKS; i += THREADS) {
       const int r = i / CHUNKS, cc = i % CHUNKS;
@@ -152,6 +201,31 @@ attention_decode_tc_kernel(DecodeTcParams p, IertBatchView b, IertKvView c) {
     load_queries();              // a group of their own, younger than the first pages: see the first wait
     cp_commit();
   }
+  if (own_new_row) {
+    // the new key (rotated) and value: staged for the newest page's tile and, once per kv
+    // head, written to the cache (src/layers/attention.rs:604-606)
+    const __nv_bfloat16* kn = tok_row + (size_t)(p.heads + kvh) * HD;
+    const __nv_bfloat16* vn = tok_row + (size_t)(p.heads + c.kv_heads + kvh) * HD;
+    for (int k = threadIdx.x; k < HD / 2; k += THREADS) {
+      if (k < half) rotate_into(kn, new_kv, k);
+      else { const int d = p.rotary_dim + 2 * (k - half); new_kv[d] = kn[d]; new_kv[d + 1] = kn[d + 1]; }
+      new_kv[HD + 2 * k] = vn[2 * k];
+      new_kv[HD + 2 * k + 1] = vn[2 * k + 1];
+    }
+    __syncthreads();
+    if (slice == 0) {
+      const int page = c.page_table[(size_t)slot * c.table_width + (pos / PAGE) % c.ring_pages];
+      if (page >= 0 && page < c.n_pages) {
+        const size_t off = ((((size_t)page * c.kv_heads + kvh) * PAGE) + pos % PAGE) * HD;
+        for (int d = threadIdx.x; d < HD; d += THREADS) {
+          ((__nv_bfloat16*)c.k)[off + d] = new_kv[d];
+          ((__nv_bfloat16*)c.v)[off + d] = new_kv[HD + d];
+        }
+      } else if (threadIdx.x == 0) {
+        atomicOr(p.err, IERT_ERR_PAGE_RANGE);
+      }
+    }
+  }
 
   uint32_t qf[KSTEPS][4];
   float o[KSTEPS * 2][4];
@@ -166,6 +240,14 @@ attention_decode_tc_kernel(DecodeTcParams p, IertBatchView b, IertKvView c) {
     if (early && pg == my_lo) cp_wait<1>();      // the queries' group is the second youngest here
     else cp_wait<NSTAGE - 1>();
     __syncthreads();
+    if (own_new_row && pg == pos / PAGE) {               // the newest row of the newest page
+      const int r = pos % PAGE;
+      for (int d = threadIdx.x; d < HD; d += THREADS) {
+        reinterpret_cast<__nv_bfloat16*>(k_tile(buf) + r * ROW_BYTES)[d] = new_kv[d];
+        reinterpret_cast<__nv_bfloat16*>(v_tile(buf) + r * ROW_BYTES)[d] = new_kv[HD + d];
+      }
+      __syncthreads();
+    }
     if (pg == my_lo) {
 #pragma unroll
       for (int ks = 0; ks < KSTEPS; ++ks)
@@ -278,15 +360,18 @@ IERT_API long long iert_attention_decode_tc_scratch_floats(int n_tokens, int hea
   return (long long)n_tokens * heads * splits * (HD + 2);
 }
 
-// Same contract as the core library's iert_attention_decode, for caches with head_dim ==
-// HEAD_DIM, bf16, 64-position pages.  Anything else: IERT_BAD_ARGUMENT, nothing launched.
-IERT_API int iert_attention_decode_tc(const void* qkv, void* out, const IertBatchView* batch,
-                                      const IertKvView* cache, int heads, float scale, int splits,
-                                      float* scratch, int* err, cudaStream_t stream) {
+namespace {
+
+int launch_decode(const void* qkv, void* out, const IertBatchView* batch, const IertKvView* cache, int heads,
+                  float scale, int splits, float* scratch, const float* inv_freq, int rope, int rotary_dim,
+                  int pairing, int store, int* err, cudaStream_t stream) {
   const int T = batch->n_tokens;
   if (T <= 0) return IERT_OK;
   if (cache->dtype != IERT_BF16 || cache->head_dim != HD || cache->page_tokens != PAGE || splits < 1 || heads <= 0 ||
       cache->kv_heads <= 0 || heads % cache->kv_heads != 0 || T > 65535)
+    return IERT_BAD_ARGUMENT;
+  if (rope && (!inv_freq || rotary_dim < 0 || rotary_dim > HD || (rotary_dim & 1) ||
+               (pairing != IERT_PAIR_HALF && pairing != IERT_PAIR_INTERLEAVED)))
     return IERT_BAD_ARGUMENT;
   const int group = heads / cache->kv_heads;
   DecodeTcParams p;
@@ -299,8 +384,10 @@ IERT_API int iert_attention_decode_tc(const void* qkv, void* out, const IertBatc
   p.err = err;
   p.part_out = scratch;
   p.part_ml = scratch + (size_t)T * heads * splits * HD;
+  p.inv_freq = inv_freq; p.rope = rope; p.rotary_dim = rotary_dim; p.pairing = pairing; p.store = store;
   if ((long long)cache->kv_heads * p.slices > 65535) return IERT_BAD_ARGUMENT;
-  size_t smem = 2 * NSTAGE * (size_t)TILE_BYTES + ROWS * ROW_BYTES;
+  // page ring, query tile, angle table and the step's own key/value row
+  size_t smem = 2 * NSTAGE * (size_t)TILE_BYTES + ROWS * ROW_BYTES + 8 * (size_t)HD;
   const size_t merge = (size_t)(WARPS * 8 * HD + WARPS * 8 * 2) * sizeof(float);
   if (merge > smem) smem = merge;
   static bool configured = false;
@@ -316,4 +403,27 @@ IERT_API int iert_attention_decode_tc(const void* qkv, void* out, const IertBatc
   if (cudaGetLastError() != cudaSuccess) return IERT_CUDA_ERROR;
   launch_dep(attention_decode_tc_combine_kernel, dim3(T, heads), dim3(HD >= 128 ? 128 : 64), 0, stream, p);
   return cudaGetLastError() == cudaSuccess ? IERT_OK : IERT_CUDA_ERROR;
+}
+
+}  // namespace
+
+// Same contract as the core library's iert_attention_decode, for caches with head_dim ==
+// HEAD_DIM, bf16, 64-position pages.  Anything else: IERT_BAD_ARGUMENT, nothing launched.
+IERT_API int iert_attention_decode_tc(const void* qkv, void* out, const IertBatchView* batch,
+                                      const IertKvView* cache, int heads, float scale, int splits,
+                                      float* scratch, int* err, cudaStream_t stream) {
+  return launch_decode(qkv, out, batch, cache, heads, scale, splits, scratch, nullptr, 0, 0, 0, 0, err, stream);
+}
+
+// The same with the rotary encoding and the cache write of the step inside the kernel: `qkv` is
+// the raw projection of one token per sequence and is left as it is; queries and the new key
+// are rotated on the way (angles pos * inv_freq[k], pairs by `pairing`, the first `rotary_dim`
+// dimensions of a head); with store != 0 the new key and value are written to the cache.
+IERT_API int iert_attention_decode_tc_rope(const void* qkv, void* out, const IertBatchView* batch,
+                                           const IertKvView* cache, int heads, float scale, int splits,
+                                           float* scratch, const float* inv_freq, int rotary_dim, int pairing,
+                                           int store, int* err, cudaStream_t stream) {
+  if (batch->n_tokens != batch->n_seqs) return IERT_BAD_ARGUMENT;     // one token per sequence
+  return launch_decode(qkv, out, batch, cache, heads, scale, splits, scratch, inv_freq, 1, rotary_dim, pairing,
+                       store, err, stream);
 }

@@ -293,6 +293,10 @@ def _attention_lib(head_dim: int):
         lib.iert_attention_decode_tc.argtypes = [c_void_p, c_void_p, POINTER(BatchView), POINTER(KvView), c_int,
                                                  c_float, c_int, c_void_p, c_void_p, c_void_p]
         lib.iert_attention_decode_tc.restype = c_int
+        lib.iert_attention_decode_tc_rope.argtypes = [c_void_p, c_void_p, POINTER(BatchView), POINTER(KvView), c_int,
+                                                      c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
+                                                      c_void_p, c_void_p]
+        lib.iert_attention_decode_tc_rope.restype = c_int
         lib.iert_attention_prefill_tc.argtypes = [c_void_p, c_void_p, POINTER(BatchView), c_int, c_int, c_int,
                                                   c_float, c_int, c_void_p, c_void_p]
         lib.iert_attention_prefill_tc.restype = c_int
@@ -346,6 +350,26 @@ def attention_decode_tc(qkv, out, batch: BatchView, kv: KvView, heads: int, scal
         return False
     if status != 0:
         raise KernelError("attention_decode_tc: the launch failed")
+    global launch_count
+    launch_count += 2
+    return True
+
+
+def attention_decode_tc_rope(qkv, out, batch: BatchView, kv: KvView, heads: int, scale: float, splits: int,
+                             scratch, inv_freq, rotary_dim: int, pairing: int, store: bool, err, stream) -> bool:
+    """`attention_decode_tc` with the rotary encoding and the step's cache write inside the
+    kernel: `qkv` is the raw projection (one token per sequence) and stays as it is.  Returns
+    False, having launched nothing, for anything the kernel does not take."""
+    hd = kv.head_dim
+    if hd % 16 or not 16 <= hd <= 256:
+        return False
+    status = _attention_lib(hd).iert_attention_decode_tc_rope(
+        qkv.data_ptr(), out.data_ptr(), byref(batch), byref(kv), heads, scale, splits, scratch.data_ptr(),
+        inv_freq.data_ptr(), rotary_dim, pairing, 1 if store else 0, err.data_ptr(), stream)
+    if status == 1:
+        return False
+    if status != 0:
+        raise KernelError("attention_decode_tc_rope: the launch failed")
     global launch_count
     launch_count += 2
     return True

@@ -77,8 +77,15 @@ class Attention(Mixer):
         kv = cache_view.struct
         qkv = ws.take("attn.qkv", (T, self.q_dim + 2 * self.kv_dim), rt.dtype)
         self.qkv.apply(xn, qkv, T, ctx.stream)
-        self.position.encode_and_store(qkv, ctx, kv, self.heads, writes_cache)
         out = ws.take("attn.out", (T, self.q_dim), rt.dtype)
+        if rt.fast and ctx.kind == "decode":
+            # one token per sequence: rotation, cache write and attention in one kernel, if the
+            # position encoding is a plain rotation and the kernel takes the sizes
+            from . import fast_attention
+            if fast_attention.decode_with_rotation(self, qkv, out, ctx, cache_view, writes_cache):
+                self.o.apply(out, residual, T, ctx.stream, add_residual=True)
+                return
+        self.position.encode_and_store(qkv, ctx, kv, self.heads, writes_cache)
         from_cache = ctx.kind == "decode" or not writes_cache
         if from_cache and ctx.kind == "prompt":
             cap = cache_view.group.ring_capacity

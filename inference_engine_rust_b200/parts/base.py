@@ -156,6 +156,11 @@ class PositionEncoding(Part):
         the keys and values in the cache `kv` (a csrc.bindings.KvView)."""
         raise NotImplementedError
 
+    def rotary_constants(self):
+        """(inv_freq fp32 device tensor, rotary_dim, pairing code) if the encoding is a plain
+        rotation that a mixer's kernel may apply itself, else None (the default)."""
+        return None
+
 
 class Mixer(Part):
     def cache_request(self) -> CacheRequest:

@@ -1,6 +1,8 @@
 """Dispatch of attention to the fast kernels (flash prompt attention, split-KV decode)."""
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..csrc import bindings as B
@@ -16,6 +18,22 @@ def decode_splits(n_tokens: int, kv_heads: int, group: int) -> int:
     slices = -(-group // 8)
     ctas = max(1, n_tokens * kv_heads * slices)
     return max(1, min(_MAX_SPLITS, _RESIDENT_CTAS // ctas))      # as many splits as stay one wave
+
+
+def decode_with_rotation(attn, qkv, out, ctx, cache_view, writes_cache: bool) -> bool:
+    """One-token step with the rotary encoding and the cache write inside the attention kernel.
+    False (nothing launched) if the position encoding is no plain rotation or the kernel does
+    not take this cache; the caller then encodes, stores and attends in separate kernels."""
+    rot = attn.position.rotary_constants()
+    if rot is None or qkv.dtype != torch.bfloat16 or os.environ.get("IERT_FUSED_ROPE", "1") == "0":
+        return False
+    inv_freq, rotary_dim, pairing = rot
+    rt = attn.rt
+    splits = decode_splits(ctx.n_tokens, attn.kv_heads, attn.heads // attn.kv_heads)
+    n = B.attention_decode_scratch_floats(ctx.n_tokens, attn.heads, attn.head_dim, splits)
+    scratch = rt.workspace.take("attn.decode_scratch", (n,), torch.float32)
+    return B.attention_decode_tc_rope(qkv, out, ctx.batch, cache_view.struct, attn.heads, attn.scale, splits,
+                                      scratch, inv_freq, rotary_dim, pairing, writes_cache, rt.err, ctx.stream)
 
 
 def apply(attn, qkv, out, ctx, cache_view, from_cache: bool) -> bool:

@@ -36,6 +36,9 @@ class RotaryEncoding(PositionEncoding):
             inv = inv / torch.as_tensor(factors, dtype=torch.float64)
         self.inv_freq = inv.to(torch.float32).to(rt.device)
 
+    def rotary_constants(self):
+        return self.inv_freq, self.rotary_dim, self.pairing
+
     def encode_and_store(self, qkv, ctx, kv, heads: int, writes_cache: bool) -> None:
         B.rope_kv_store(qkv, ctx.batch, kv, self.inv_freq, heads, self.rotary_dim, self.pairing,
                         writes_cache, ctx.rt.err, ctx.stream)

@@ -314,6 +314,79 @@ def test_attention_decode_batch_with_padding(heads, kvh, hd, window):
             f"tensor cores, {splits} splits: {(tc.float() - plain.float()).abs().max().item():.4g}"
 
 
+@pytest.mark.parametrize("heads,kvh,hd,window,pairing,rotary", [
+    (32, 8, 128, None, "half", 128), (12, 2, 64, 40, "interleaved", 64), (6, 1, 32, 100, "half", 16),
+    (20, 2, 48, None, "interleaved", 32)])
+def test_attention_decode_with_rotation_inside(heads, kvh, hd, window, pairing, rotary):
+    """The decode kernel that rotates queries and the new key and writes the cache itself, against
+    the separate rotate-and-store kernel followed by the same attention kernel: same output, same
+    cache afterwards; with the store switched off it reads a cache that already holds the token
+    and leaves it alone.  Lengths straddle pages and (with a window) wrap the ring; groups of
+    more than eight heads run as two slices."""
+    b = B()
+    torch.manual_seed(11)
+    dtype = torch.bfloat16
+    W = heads + 2 * kvh
+    scale = 1.0 / math.sqrt(hd)
+    code = b.PAIR_HALF if pairing == "half" else b.PAIR_INTERLEAVED
+    inv_freq = (10000.0 ** (-torch.arange(rotary // 2, dtype=torch.float64) * 2 / rotary)).float().to(DEV)
+    lens = [1, 64, 65, 300, 129]
+    fill = (torch.randn(sum(n - 1 for n in lens), W * hd, device=DEV) * 0.7).to(dtype)
+    nxt = (torch.randn(len(lens) + 1, W * hd, device=DEV) * 0.7).to(dtype)
+    err = err_word()
+    caches, views = [], []
+    for _ in range(2):                        # two caches with the same history
+        cache = make_cache(kvh, hd, window, dtype, max_tokens=64 * 24, max_seq_len=512, slots=6)
+        slots = [cache.open_sequence() for _ in lens]
+        for s_, n in zip(slots, lens):
+            cache.reserve(s_, n)
+        cache.upload()
+        keep = [(s_, n - 1) for s_, n in zip(slots, lens) if n > 1]
+        view, arrs = make_batch([n for _, n in keep], [0] * len(keep), [s_ for s_, _ in keep])
+        b.rope_kv_store(fill.clone(), view, cache.layer_view(0).struct, inv_freq, heads, rotary, code, True, err, stream())
+        caches.append(cache)
+        views.append(cache.layer_view(0))
+    order = slots[:2] + [-1] + slots[2:]      # a padding sequence in the middle
+    pos0 = [lens[0] - 1, lens[1] - 1, 0] + [n - 1 for n in lens[2:]]
+    step, arrs1 = make_batch([1] * 6, pos0, order)
+    arrs1[2][2] = -1
+    for splits in (1, 3, 8):
+        n = b.attention_decode_scratch_floats(6, heads, hd, splits)
+        scratch = torch.full((n,), float("nan"), device=DEV)
+        # separately: rotate and store, then attend
+        rotated = nxt.clone()
+        b.rope_kv_store(rotated, step, views[0].struct, inv_freq, heads, rotary, code, True, err, stream())
+        want = torch.full((6, heads * hd), float("nan"), device=DEV, dtype=dtype)
+        assert b.attention_decode_tc(rotated, want, step, views[0].struct, heads, scale, splits, scratch, err, stream())
+        # in one kernel, from the raw projection, into the second cache
+        raw = nxt.clone()
+        got = torch.full_like(want, float("nan"))
+        scratch.fill_(float("nan"))
+        assert b.attention_decode_tc_rope(raw, got, step, views[1].struct, heads, scale, splits, scratch, inv_freq,
+                                          rotary, code, True, err, stream())
+        assert err.item() == 0
+        assert torch.equal(raw, nxt), "the fused kernel must leave the projection as it is"
+        assert torch.isfinite(got).all() and float(got[2].abs().sum()) == 0
+        diff = (got.float() - want.float()).abs().max().item()
+        assert diff <= 1e-2, f"{splits} splits: output differs by {diff:.4g}"
+        live = sorted(set(p_ for s_ in slots for p_ in caches[0].kv_groups[0].pages_of(s_)))
+        for a_, b_ in ((views[0].k, views[1].k), (views[0].v, views[1].v)):
+            ka, kb = a_[live].float(), b_[live].float()
+            both = torch.isfinite(ka) & torch.isfinite(kb)
+            assert torch.equal(torch.isfinite(ka), torch.isfinite(kb)), "different rows were written"
+            assert (ka[both] - kb[both]).abs().max().item() <= 2.0 ** -6, "the caches differ"
+        # store off: the second cache holds the token already; output as before, cache untouched
+        before = (views[1].k.clone(), views[1].v.clone())
+        again = torch.full_like(want, float("nan"))
+        scratch.fill_(float("nan"))
+        assert b.attention_decode_tc_rope(raw, again, step, views[1].struct, heads, scale, splits, scratch, inv_freq,
+                                          rotary, code, False, err, stream())
+        assert err.item() == 0
+        assert (again.float() - want.float()).abs().max().item() <= 1e-2
+        assert torch.equal(before[0].view(torch.int16), views[1].k.view(torch.int16))
+        assert torch.equal(before[1].view(torch.int16), views[1].v.view(torch.int16))
+
+
 def test_sampling_greedy_and_errors():
     b = B()
     logits = torch.randn(5, 1000, device=DEV)
