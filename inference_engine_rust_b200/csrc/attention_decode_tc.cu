@@ -12,7 +12,7 @@
 //   Each of the 4 warps takes 16 of a page's 64 keys with its own running maximum and sum;
 //   the warps are merged through shared memory in warp order at the end, and the split's
 //   partial result (unnormalised output, maximum, sum) goes to scratch memory.  A second
-//   kernel merges the splits in split order.
+//   kernel merges the splits in split order; a single split writes the output itself.
 //
 // Optionally the rotary position encoding and the cache write of the step are part of this
 // kernel (angle pos * theta^(-2k/d) in fp32, src/ops/rope.rs:40-57; rotate, then store, then
@@ -119,7 +119,12 @@ attention_decode_tc_kernel(DecodeTcParams p, IertBatchView b, IertKvView c) {
   float* pml = p.part_ml + (((size_t)t * p.heads + head0) * p.splits + split) * 2;
   if (slot < 0) {
     pdl_wait();                // the scratch may still be read by an earlier kernel's successor
-    if (threadIdx.x < n_g) { pml[(size_t)threadIdx.x * p.splits * 2] = -INFINITY; pml[(size_t)threadIdx.x * p.splits * 2 + 1] = 0.f; }
+    if (p.splits == 1) {       // a padding sequence: zeros
+      for (int i = threadIdx.x; i < n_g * HD; i += THREADS)
+        p.out[((size_t)t * p.heads + head0) * HD + i] = __float2bfloat16_rn(0.f);
+    } else if (threadIdx.x < n_g) {
+      pml[(size_t)threadIdx.x * p.splits * 2] = -INFINITY; pml[(size_t)threadIdx.x * p.splits * 2 + 1] = 0.f;
+    }
     return;
   }
   const int pos = b.pos0[s] + (t - b.cu_q[s]);
@@ -315,6 +320,7 @@ attention_decode_tc_kernel(DecodeTcParams p, IertBatchView b, IertKvView c) {
   }
   if (tq == 0) { ml_s[(warp * 8 + g) * 2] = m_row; ml_s[(warp * 8 + g) * 2 + 1] = l_row; }
   __syncthreads();
+  const bool direct = p.splits == 1;                  // a single split: its result is the output
   for (int r = 0; r < n_g && r < 8; ++r) {
     float mm = -INFINITY;
     for (int w = 0; w < WARPS; ++w) mm = fmaxf(mm, ml_s[(w * 8 + r) * 2]);
@@ -324,12 +330,14 @@ attention_decode_tc_kernel(DecodeTcParams p, IertBatchView b, IertKvView c) {
       wgt[w] = mw == -INFINITY ? 0.f : exp2f(mw - mm);
       ll += wgt[w] * ml_s[(w * 8 + r) * 2 + 1];
     }
+    const float inv = ll > 0.f ? 1.0f / ll : 0.f;
     for (int d = threadIdx.x; d < HD; d += THREADS) {
       float acc = 0.f;
       for (int w = 0; w < WARPS; ++w) acc += wgt[w] * o_s[(w * 8 + r) * HD + d];
-      po[(size_t)r * p.splits * HD + d] = acc;
+      if (direct) p.out[((size_t)t * p.heads + head0 + r) * HD + d] = __float2bfloat16_rn(acc * inv);
+      else po[(size_t)r * p.splits * HD + d] = acc;
     }
-    if (threadIdx.x == 0) { pml[(size_t)r * p.splits * 2] = mm; pml[(size_t)r * p.splits * 2 + 1] = ll; }
+    if (!direct && threadIdx.x == 0) { pml[(size_t)r * p.splits * 2] = mm; pml[(size_t)r * p.splits * 2 + 1] = ll; }
   }
 }
 
@@ -401,6 +409,7 @@ int launch_decode(const void* qkv, void* out, const IertBatchView* batch, const 
   launch_dep(attention_decode_tc_kernel, dim3(splits, cache->kv_heads * p.slices, T), dim3(THREADS), smem, stream,
              p, *batch, *cache);
   if (cudaGetLastError() != cudaSuccess) return IERT_CUDA_ERROR;
+  if (splits == 1) return IERT_OK;                   // nothing to merge: the kernel wrote the output
   launch_dep(attention_decode_tc_combine_kernel, dim3(T, heads), dim3(HD >= 128 ? 128 : 64), 0, stream, p);
   return cudaGetLastError() == cudaSuccess ? IERT_OK : IERT_CUDA_ERROR;
 }

@@ -351,7 +351,7 @@ def attention_decode_tc(qkv, out, batch: BatchView, kv: KvView, heads: int, scal
     if status != 0:
         raise KernelError("attention_decode_tc: the launch failed")
     global launch_count
-    launch_count += 2
+    launch_count += 1 if splits == 1 else 2        # a single split needs no merge kernel
     return True
 
 
@@ -371,7 +371,7 @@ def attention_decode_tc_rope(qkv, out, batch: BatchView, kv: KvView, heads: int,
     if status != 0:
         raise KernelError("attention_decode_tc_rope: the launch failed")
     global launch_count
-    launch_count += 2
+    launch_count += 1 if splits == 1 else 2        # a single split needs no merge kernel
     return True
 
 
