@@ -103,15 +103,78 @@ __global__ void rmsnorm_reg_kernel(const float* __restrict__ x, const TW* __rest
   }
 }
 
+// The same again with 16-byte accesses: a thread holds V runs of four consecutive elements.
+// `hidden` a multiple of 4, all three pointers aligned for vectors of four.
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
+  uint2 raw;
+  *reinterpret_cast<__nv_bfloat162*>(&raw.x) = __floats2bfloat162_rn(v.x, v.y);
+  *reinterpret_cast<__nv_bfloat162*>(&raw.y) = __floats2bfloat162_rn(v.z, v.w);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
+template <typename TW, typename TO, int V>
+__global__ void rmsnorm_vec_kernel(const float* __restrict__ x, const TW* __restrict__ w,
+                                   TO* __restrict__ out, const int* __restrict__ rows_idx,
+                                   int hidden, float eps) {
+  __shared__ float scratch[33];
+  pdl_launch_dependents();     // the next kernel may start its preamble now
+  const int n4 = hidden >> 2;
+  float4 wv[V], xv[V];
+#pragma unroll
+  for (int k = 0; k < V; ++k) {
+    const int i4 = threadIdx.x + k * blockDim.x;
+    wv[k] = i4 < n4 ? load4(w + 4 * i4) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  pdl_wait();                  // everything below may depend on the kernel before
+  const int r = blockIdx.x;
+  const int src_row = rows_idx ? rows_idx[r] : r;
+  const float* xr = x + (size_t)src_row * hidden;
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < V; ++k) {
+    const int i4 = threadIdx.x + k * blockDim.x;
+    xv[k] = i4 < n4 ? load4(xr + 4 * i4) : make_float4(0.f, 0.f, 0.f, 0.f);
+    ss += xv[k].x * xv[k].x + xv[k].y * xv[k].y + xv[k].z * xv[k].z + xv[k].w * xv[k].w;
+  }
+  ss = block_sum(ss, scratch);
+  const float rinv = 1.0f / sqrtf(ss / (float)hidden + eps);
+  TO* o = out + (size_t)r * hidden;
+#pragma unroll
+  for (int k = 0; k < V; ++k) {
+    const int i4 = threadIdx.x + k * blockDim.x;
+    if (i4 < n4)
+      store4(o + 4 * i4, make_float4(xv[k].x * wv[k].x * rinv, xv[k].y * wv[k].y * rinv,
+                                     xv[k].z * wv[k].z * rinv, xv[k].w * wv[k].w * rinv));
+  }
+}
+
 IERT_API int iert_rmsnorm(const float* x, const void* w, int w_dtype, void* out, int out_dtype,
                           const int* rows_idx, int rows, int hidden, float eps,
                           cudaStream_t stream) {
   if (rows <= 0) return IERT_OK;
   if (hidden <= 0) return IERT_BAD_ARGUMENT;
   const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+  const bool vec = (hidden & 3) == 0 && hidden <= 16 * 512 && (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) & 15) == 0;
+  const int n4 = hidden >> 2;
 #define LAUNCH(TW, TO)                                                                                   \
   do {                                                                                                   \
-    if (hidden <= 4 * 256) launch_dep(rmsnorm_reg_kernel<TW, TO, 4>, rows, 256, 0, stream,               \
+    if (vec && n4 <= 128) launch_dep(rmsnorm_vec_kernel<TW, TO, 1>, rows, 128, 0, stream,                \
+                                     x, (const TW*)w, (TO*)out, rows_idx, hidden, eps);                  \
+    else if (vec && n4 <= 512) launch_dep(rmsnorm_vec_kernel<TW, TO, 2>, rows, 256, 0, stream,           \
+                                          x, (const TW*)w, (TO*)out, rows_idx, hidden, eps);             \
+    else if (vec && n4 <= 1024) launch_dep(rmsnorm_vec_kernel<TW, TO, 4>, rows, 256, 0, stream,          \
+                                           x, (const TW*)w, (TO*)out, rows_idx, hidden, eps);            \
+    else if (vec) launch_dep(rmsnorm_vec_kernel<TW, TO, 4>, rows, 512, 0, stream,                        \
+                             x, (const TW*)w, (TO*)out, rows_idx, hidden, eps);                          \
+    else if (hidden <= 4 * 256) launch_dep(rmsnorm_reg_kernel<TW, TO, 4>, rows, 256, 0, stream,               \
                                       x, (const TW*)w, (TO*)out, rows_idx, hidden, eps);                 \
     else if (hidden <= 8 * 512) launch_dep(rmsnorm_reg_kernel<TW, TO, 8>, rows, 512, 0, stream,          \
                                            x, (const TW*)w, (TO*)out, rows_idx, hidden, eps);            \
@@ -144,7 +207,7 @@ template <typename T>
 __global__ void rope_kv_store_kernel(T* __restrict__ qkv, IertBatchView b, IertKvView c,
                                      const float* __restrict__ inv_freq, int heads,
                                      int rotary_dim, int pairing, int write_cache,
-                                     int heads_per_block, int* __restrict__ err) {
+                                     int heads_per_block, int vec8, int* __restrict__ err) {
   extern __shared__ float cs[];                 // [rotary_dim / 2] cos, then [rotary_dim / 2] sin
   pdl_launch_dependents();     // the next kernel may start its preamble now
   const int t = blockIdx.x;
@@ -173,6 +236,57 @@ __global__ void rope_kv_store_kernel(T* __restrict__ qkv, IertBatchView b, IertK
   // this block's heads: [h0, h1) of [queries | keys | values]
   const int h0 = blockIdx.y * heads_per_block, h1 = min(total_heads, h0 + heads_per_block);
   const int rot_end = min(h1, heads + nkv);            // heads below this index are rotated
+  const int kv0 = max(h0, heads);                       // this block's key and value heads
+  if (vec8) {
+    // bf16 with 16-byte accesses: eight consecutive elements per thread and step
+    __nv_bfloat16* rowb = reinterpret_cast<__nv_bfloat16*>(row);
+    if (pairing == IERT_PAIR_HALF) {
+      const int chunks = half / 8;
+      for (int i = threadIdx.x; i < (rot_end - h0) * chunks; i += blockDim.x) {
+        const int head = h0 + i / chunks, k0 = (i % chunks) * 8;
+        __nv_bfloat16* vec = rowb + (size_t)head * hd;
+        uint4 ra = *reinterpret_cast<const uint4*>(vec + k0), rb = *reinterpret_cast<const uint4*>(vec + half + k0);
+        __nv_bfloat162* pa = reinterpret_cast<__nv_bfloat162*>(&ra);
+        __nv_bfloat162* pb = reinterpret_cast<__nv_bfloat162*>(&rb);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 a = __bfloat1622float2(pa[e]), bb = __bfloat1622float2(pb[e]);
+          const int k = k0 + 2 * e;
+          pa[e] = __floats2bfloat162_rn(a.x * cs[k] - bb.x * cs[half + k], a.y * cs[k + 1] - bb.y * cs[half + k + 1]);
+          pb[e] = __floats2bfloat162_rn(a.x * cs[half + k] + bb.x * cs[k], a.y * cs[half + k + 1] + bb.y * cs[k + 1]);
+        }
+        *reinterpret_cast<uint4*>(vec + k0) = ra;
+        *reinterpret_cast<uint4*>(vec + half + k0) = rb;
+      }
+    } else {
+      const int chunks = rotary_dim / 8;
+      for (int i = threadIdx.x; i < (rot_end - h0) * chunks; i += blockDim.x) {
+        const int head = h0 + i / chunks, c0 = (i % chunks) * 8;
+        __nv_bfloat16* vec = rowb + (size_t)head * hd;
+        uint4 rv = *reinterpret_cast<const uint4*>(vec + c0);
+        __nv_bfloat162* pv = reinterpret_cast<__nv_bfloat162*>(&rv);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 ab = __bfloat1622float2(pv[e]);
+          const int k = c0 / 2 + e;
+          pv[e] = __floats2bfloat162_rn(ab.x * cs[k] - ab.y * cs[half + k], ab.x * cs[half + k] + ab.y * cs[k]);
+        }
+        *reinterpret_cast<uint4*>(vec + c0) = rv;
+      }
+    }
+    if (!store || kv0 >= h1) return;
+    __syncthreads();                                    // the rotated keys are read back below
+    const int chunks = hd / 8;
+    for (int i = threadIdx.x; i < (h1 - kv0) * chunks; i += blockDim.x) {
+      const int hh = kv0 + i / chunks - heads, d = (i % chunks) * 8;
+      const bool is_k = hh < nkv;
+      const long long off = kv_row_offset(c, slot, pos, is_k ? hh : hh - nkv, err);
+      if (off < 0) continue;
+      *reinterpret_cast<uint4*>((__nv_bfloat16*)(is_k ? c.k : c.v) + off + d) =
+          *reinterpret_cast<const uint4*>(rowb + (size_t)(heads + hh) * hd + d);
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < (rot_end - h0) * half; i += blockDim.x) {
     const int head = h0 + i / half, k = i % half;
     const int i0 = pairing == IERT_PAIR_HALF ? k : 2 * k;
@@ -182,7 +296,6 @@ __global__ void rope_kv_store_kernel(T* __restrict__ qkv, IertBatchView b, IertK
     vec[i0] = from_f32<T>(a * cs[k] - bb * cs[half + k]);
     vec[i1] = from_f32<T>(a * cs[half + k] + bb * cs[k]);
   }
-  const int kv0 = max(h0, heads);                       // this block's key and value heads
   if (!store || kv0 >= h1) return;
   __syncthreads();                                      // the rotated keys are read back below
   for (int i = threadIdx.x; i < (h1 - kv0) * hd; i += blockDim.x) {
@@ -211,10 +324,14 @@ IERT_API int iert_rope_kv_store(void* qkv, int dtype, const IertBatchView* batch
   const size_t smem = (size_t)rotary_dim * sizeof(float);
   if (smem > 48 * 1024) return IERT_BAD_ARGUMENT;
   dim3 grid(batch->n_tokens, (total_heads + heads_per_block - 1) / heads_per_block);
+  // bf16, every head a whole number of 16-byte runs, and the rotated part too
+  const int hd = cache->head_dim;
+  const int vec8 = dtype == IERT_BF16 && hd % 8 == 0 && rotary_dim % (pairing == IERT_PAIR_HALF ? 16 : 8) == 0 &&
+                   (((uintptr_t)qkv | (uintptr_t)cache->k | (uintptr_t)cache->v) & 15) == 0;
   if (dtype == IERT_F32)
-    launch_dep(rope_kv_store_kernel<float>, grid, dim3(threads), smem, stream, (float*)qkv, *batch, *cache, inv_freq, heads, rotary_dim, pairing, write_cache, heads_per_block, err);
+    launch_dep(rope_kv_store_kernel<float>, grid, dim3(threads), smem, stream, (float*)qkv, *batch, *cache, inv_freq, heads, rotary_dim, pairing, write_cache, heads_per_block, 0, err);
   else if (dtype == IERT_BF16)
-    launch_dep(rope_kv_store_kernel<__nv_bfloat16>, grid, dim3(threads), smem, stream, (__nv_bfloat16*)qkv, *batch, *cache, inv_freq, heads, rotary_dim, pairing, write_cache, heads_per_block, err);
+    launch_dep(rope_kv_store_kernel<__nv_bfloat16>, grid, dim3(threads), smem, stream, (__nv_bfloat16*)qkv, *batch, *cache, inv_freq, heads, rotary_dim, pairing, write_cache, heads_per_block, vec8, err);
   else
     return IERT_BAD_ARGUMENT;
   return iert_check_launch("rope_kv_store");
