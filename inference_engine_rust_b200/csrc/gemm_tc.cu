@@ -584,19 +584,32 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, GemmParams p, int grid,
   return iert_check_launch("gemm_tc");
 }
 
-// CTAs of the weight-major kernel that one SM holds at once, as the driver reports it for the
-// kernel's registers, threads and shared memory (0 if the query fails).
+// CTAs of the weight-major kernel that one SM holds at once (at most 2 are ever assumed), from
+// the kernel's registers, its shared memory and its tensor-memory columns.  The runtime's
+// occupancy query is not used: for this kernel it answers 1 whatever the sizes, while two CTAs
+// are resident (measured: 256 CTAs that wait for one another finish on 148 SMs).  Should the
+// estimate ever be too high, the cooperative reduction's wait runs out and sets the error word.
 template <int BT>
 int ctas_per_sm_of(int stages) {
   static int cached[13] = {0};
   if (stages < 0 || stages > 12) return 0;
   if (!cached[stages]) {
     const size_t smem = (size_t)stages * (W_STAGE_BYTES + BT * TILE_K * 2) + 1024 + 256;
-    int n = 0;
-    if (cudaFuncSetAttribute(gemm_tc_kernel<BT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess ||
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, gemm_tc_kernel<BT, false>, THREADS, smem) != cudaSuccess) {
+    int n = 0, dev = 0, smem_sm = 0, regs_sm = 0;
+    cudaFuncAttributes a;
+    if (cudaGetDevice(&dev) == cudaSuccess && cudaFuncGetAttributes(&a, gemm_tc_kernel<BT, false>) == cudaSuccess &&
+        cudaDeviceGetAttribute(&smem_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev) == cudaSuccess &&
+        cudaDeviceGetAttribute(&regs_sm, cudaDevAttrMaxRegistersPerMultiprocessor, dev) == cudaSuccess) {
+      const int regs_per_warp = (((a.numRegs + 7) / 8 * 8) * 32 + 255) / 256 * 256;
+      const int by_regs = regs_sm / (regs_per_warp * (THREADS / 32));
+      const int by_smem = (int)(smem_sm / (smem + a.sharedSizeBytes + 1024));     // 1 KB reserved per CTA
+      const int acc_cols = 2 * BT < 32 ? 32 : 2 * BT;
+      const int by_tmem = 512 / acc_cols;
+      n = by_regs < by_smem ? by_regs : by_smem;
+      if (by_tmem < n) n = by_tmem;
+      if (n > 2) n = 2;
+    } else {
       cudaGetLastError();
-      n = 0;
     }
     cached[stages] = n > 0 ? n : -1;
   }
