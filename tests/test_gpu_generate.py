@@ -160,3 +160,46 @@ def test_bench_subcommand(loaded, capsys):
     # a batch decodes together and counts every sequence's tokens
     m = M.EngineBench(model, batch=3).run_decode_throughput([5, 6, 7], 4)
     assert m["batch"] == 3 and m["decode_tokens"] == 4
+
+
+def test_refused_steps_launch_nothing(loaded):
+    """What the host can see is wrong with a step is refused before anything runs: no kernel
+    is launched, no page is taken, no length moves."""
+    from inference_engine_rust_b200 import StepError
+    from inference_engine_rust_b200.cache import CacheFull
+    from inference_engine_rust_b200.csrc import bindings as B
+    folder, model, w = loaded["A"]
+    eng = model.session(max_tokens=128, max_sequences=3, max_seq_len=100).engine
+    a, b = eng.open_sequence(), eng.open_sequence()
+    eng.step([(a, [1, 2, 3])], want=None)                      # a holds three tokens, b none
+    torch.cuda.synchronize()
+    vocab = TINY["A"]["vocab_size"]
+    cases = [
+        ([], StepError),                                       # no sequence
+        ([(a, [])], StepError),                                # no tokens
+        ([(a, [1]), (a, [2])], StepError),                     # a slot twice
+        ([(a, [vocab])], StepError), ([(b, [-1])], StepError),  # ids outside the vocabulary
+        ([(a, [1, 2])], StepError),                            # several tokens into a sequence that has begun
+        ([(a, [1]), (b, [1, 2])], StepError),                  # one goes on, one starts
+        ([(2, [1])], StepError),                               # a slot nobody holds
+        ([(b, [1] * 101)], CacheFull),                         # longer than the cache's longest sequence
+        ([(a, [1])], StepError, [[1]]),                        # a wanted place outside the tokens
+    ]
+    launches, pages = B.launch_count, eng.cache.kv_groups[0].pages.free_count
+    for case in cases:
+        entries, exc = case[0], case[1]
+        want = case[2] if len(case) > 2 else "last"
+        with pytest.raises(exc):
+            eng.step(entries, want=want)
+        assert B.launch_count == launches and eng.graph_launches == 0
+        assert eng.cache.kv_groups[0].pages.free_count == pages
+        assert eng.length(a) == 3 and eng.length(b) == 0
+    eng.check_device()
+    # a cache without a free page: the step is refused when it asks for room, nothing has run
+    small = model.session(max_tokens=64, max_sequences=2).engine
+    s1, s2 = small.open_sequence(), small.open_sequence()
+    small.step([(s1, [1, 2])], want=None)
+    launches = B.launch_count
+    with pytest.raises(CacheFull):
+        small.step([(s2, [3])], want=None)
+    assert B.launch_count == launches
