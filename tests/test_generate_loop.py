@@ -1,4 +1,6 @@
 """Decisions of the generation loop, with a scripted engine in place of the device."""
+import os
+
 import pytest
 
 from inference_engine_rust_b200.engine.generate import generate, plan_batches, run_batch
@@ -141,3 +143,25 @@ def test_bench_summaries_and_arguments(capsys):
     assert main(["bench", "--runs", "4", "cold-start"]) == 2 and "at least 5" in capsys.readouterr().err
     assert main(["bench", "-p", "x y", "cold-start"]) == 2 and "token ids" in capsys.readouterr().err
     assert main(["bench", "-m", "/nonexistent/folder", "cold-start"]) == 1
+
+
+def test_no_device_and_no_compiler_fail_loudly(monkeypatch, tmp_path):
+    """Without a GPU the engine refuses to be built (there is no CPU path); without nvcc the
+    kernels cannot be compiled and the build says where it looked."""
+    import torch
+    from inference_engine_rust_b200 import LoadedModel
+    from inference_engine_rust_b200.csrc import build
+    from inference_engine_rust_b200.csrc.bindings import KernelError
+    if not torch.cuda.is_available():
+        cfg = {"architectures": ["MistralForCausalLM"], "num_hidden_layers": 1, "hidden_size": 32,
+               "num_attention_heads": 2, "num_key_value_heads": 1, "intermediate_size": 48, "vocab_size": 50,
+               "rms_norm_eps": 1e-5, "max_position_embeddings": 64}
+        model = LoadedModel.random(cfg, seed=0, dtype="float32", device="cpu")
+        with pytest.raises(KernelError, match="no CUDA device"):
+            model.session(max_tokens=64)
+    monkeypatch.setenv("IERT_NVCC", str(tmp_path / "missing-nvcc"))
+    monkeypatch.setenv("PATH", str(tmp_path))
+    real = os.path.isfile
+    monkeypatch.setattr(build.os.path, "isfile", lambda p: False if str(p).endswith("nvcc") else real(p))
+    with pytest.raises(build.BuildError, match="nvcc not found"):
+        build.find_nvcc()
