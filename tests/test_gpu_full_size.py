@@ -91,3 +91,17 @@ def test_bfloat16_matches_float32(models):
     cut = run_batched_with_tails(bf, prompts, tails=[32, 5, 17])
     for i, (a, b) in enumerate(zip(cut, want)):
         compare(a, b, "bfloat16", f"7B sizes, bfloat16 batched and decoded against float32, request {i}")
+
+
+def test_bfloat16_runs_are_bitwise_repeatable(models):
+    """No kernel adds in an order that depends on timing (split-K partial tiles and attention
+    splits are merged in a fixed order whichever CTA finishes last): the same requests give
+    the same bits, whole and batched with decoding, on fresh sessions."""
+    bf, f32, prompts = models
+    a = run_batched_with_tails(bf, prompts, tails=[32, 5, 17])
+    b = run_batched_with_tails(bf, prompts, tails=[32, 5, 17])
+    for i, (x, y) in enumerate(zip(a, b)):
+        assert torch.equal(x, y), f"request {i}: two identical runs differ"
+    w1, w2 = run_whole(bf, prompts), run_whole(bf, prompts)
+    for i, (x, y) in enumerate(zip(w1, w2)):
+        assert torch.equal(x, y), f"request {i}: two identical prompt runs differ"
