@@ -124,3 +124,23 @@ def test_forward_prefix_consistency():
     assert full.shape == (40, cfg["vocab_size"])
     gen = P.generate_greedy(cfg, w, ids[:6], 4)
     assert len(gen) == 4 and gen[0] == P.sample_greedy(P.forward(cfg, w, ids[:6])[-1].tolist())
+
+
+def test_plain_implementation_against_its_committed_outputs():
+    """The plain implementation still computes what it computed when tests/golden was written
+    (its own earlier output, not the reference's: see tests/golden/make_golden.py)."""
+    import importlib.util
+    import os
+    import numpy as np
+    here = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+    spec = importlib.util.spec_from_file_location("make_golden", os.path.join(here, "make_golden.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    want = np.load(os.path.join(here, "plain_tiny_logits.npz"))
+    got = mod.compute()
+    assert sorted(want.files) == sorted(got)
+    for k in want.files:
+        if k.endswith("_ids"):
+            assert np.array_equal(want[k], got[k]), k
+        else:
+            assert np.allclose(want[k], got[k], atol=1e-5, rtol=1e-5), f"{k}: max diff {np.abs(want[k] - got[k]).max()}"
