@@ -153,3 +153,42 @@ def test_long_decoding_and_first_tokens(tmp_root, name, dtype):
     got = torch.cat(rows)
     compare(got[:4], ref[:4], dtype, f"{name}: the first tokens of a sequence")
     compare(got, ref, dtype, f"{name}: 210 tokens decoded one by one")
+
+
+ODD = {
+    # head_dim beyond what the tensor-core attention kernels take (plain kernels), with a window
+    "head_dim_272": dict(num_hidden_layers=1, hidden_size=128, num_attention_heads=3, num_key_value_heads=3, head_dim=272,
+                         intermediate_size=64, vocab_size=1001, sliding_window=50),
+    # one head, a window of one position (every token sees only itself), a vocabulary of three
+    "one_head_window_1": dict(num_hidden_layers=2, hidden_size=48, num_attention_heads=1, num_key_value_heads=1, head_dim=48,
+                              intermediate_size=8, vocab_size=3, sliding_window=1),
+    # sixteen query heads per kv head: two slices of the decode kernel's 8-row tile
+    "group_of_16": dict(num_hidden_layers=1, hidden_size=256, num_attention_heads=32, num_key_value_heads=2, head_dim=16,
+                        intermediate_size=72, vocab_size=515, sliding_window=None),
+    # the smallest head there is
+    "head_dim_2": dict(num_hidden_layers=1, hidden_size=24, num_attention_heads=6, num_key_value_heads=3, head_dim=2,
+                       intermediate_size=40, vocab_size=50, sliding_window=None),
+}
+
+
+@pytest.mark.parametrize("name", sorted(ODD))
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_sizes_at_the_edges(tmp_root, name, dtype):
+    """Sizes at the edge of what the kernels take: each either runs on a kernel that takes it or
+    falls back to the plain one; never a wrong result."""
+    from inference_engine_rust_b200 import LoadedModel
+    cfg = dict(TINY["A"], **ODD[name])
+    folder = make_folder(tmp_root, cfg, seed=2, dtype=dtype)
+    model = LoadedModel.load(folder, dtype=dtype)
+    w = plain_weights(folder)
+    rnd = P.bf16_rounding if dtype == "bfloat16" else P.no_rounding
+    eng = new_engine(model, max_tokens=64 * 8)
+    for n in (1, 70, 130):
+        p = prompts_for(cfg, [n], seed=n)[0]
+        ref = P.forward(cfg, w, p, rnd)
+        s = eng.open_sequence()
+        head = max(1, n - 5)
+        rows = [eng.step([(s, p[:head])], want="all")] + [eng.step([(s, [t])], want="last") for t in p[head:]]
+        eng.check_device()
+        compare(torch.cat(rows), ref, dtype, f"{name} {dtype}, {n} tokens")
+        eng.close_sequence(s)
