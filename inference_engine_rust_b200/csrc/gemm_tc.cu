@@ -49,6 +49,7 @@ constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;
 constexpr int W_STAGE_BYTES = TILE_N * TILE_K * 2;
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
+constexpr int OUT_STAGE_BYTES = 32 * TILE_N * 4;   // residual add by TMA: 32 tokens x 128 outputs fp32, two of them
 constexpr int XCH_BYTES = 16 * 64 * 4 + 16;   // weight-major gated tile: 16 tokens x 64 up values, aligned
 
 enum : int { MODE_STORE = 0, MODE_ADD_RESIDUAL = 1, MODE_GATED_SILU = 2 };
@@ -65,6 +66,9 @@ struct GemmParams {
   float* ws;          // [tiles][splits][BT][TILE_N] fp32 partials (splits > 1)
   int* counters;      // [tiles] tickets, zero between launches
   int coop_reduce;    // splits > 1: every split adds its share of the rows (the grid is co-resident)
+  int tma_out;        // residual add through TMA reduce (map_o), weight-major tiles of >= 128 tokens
+  int tail_parts;     // > 1: the tiles from full_tiles on are cut into this many parts of k (see WorkIter)
+  int full_tiles;
   int* err;
 };
 
@@ -117,10 +121,50 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
   return __fdividef(g * u, 1.0f + __expf(-g));
 }
 
+// A CTA's list of work, the same for its three roles: items (tile, part of k) strided over the
+// grid.  Usually every tile has the same number of parts (p.splits, split-K).  For residual adds
+// over many tokens whose tiles leave the last wave part empty (p.tail_parts > 1, one CTA per SM,
+// all resident) the first p.full_tiles tiles are whole and each of the others is cut into
+// p.tail_parts equal parts of k, listed part by part (all first parts, then all second parts,
+// ...), so that the last wave's work comes in pieces a quarter (say) of a tile long and fills
+// the SMs evenly, while CTAs that run at the same time still read the same range of k.  The
+// parts of a tile add their products into the residual one after the other, in the order of the
+// parts, each waiting (bounded) until the tile's counter shows its turn: the order of the
+// additions is fixed, the result repeatable, and no scratch memory is used.
+struct WorkIter {
+  const GemmParams& p;
+  int work, total_work, n_tail;
+  __device__ WorkIter(const GemmParams& p_) : p(p_) {
+    const int tiles = p.n_tiles * p.t_tiles;
+    n_tail = p.tail_parts > 1 ? tiles - p.full_tiles : 0;
+    total_work = p.tail_parts > 1 ? p.full_tiles + n_tail * p.tail_parts : tiles * p.splits;
+    work = blockIdx.x;
+  }
+  // part / n_parts: which part of the tile's k range, out of how many
+  __device__ bool next(int& tile, int& part, int& n_parts, int& kb0, int& kb1) {
+    if (work >= total_work) return false;
+    if (p.tail_parts > 1) {
+      if (work < p.full_tiles) {
+        tile = work; part = 0; n_parts = 1; kb0 = 0; kb1 = p.kb_total;
+      } else {
+        const int r = work - p.full_tiles;
+        part = r / n_tail; tile = p.full_tiles + r % n_tail; n_parts = p.tail_parts;
+        const int per = (p.kb_total + n_parts - 1) / n_parts;
+        kb0 = part * per; kb1 = min(p.kb_total, kb0 + per);
+      }
+    } else {
+      part = work % p.splits; tile = work / p.splits; n_parts = p.splits;
+      kb0 = part * p.kb_per_split; kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+    }
+    work += gridDim.x;
+    return true;
+  }
+};
+
 template <int BT, bool GATED>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-               const GemmParams p) {
+               const __grid_constant__ CUtensorMap map_o, const GemmParams p) {
   constexpr int NW = GATED ? 2 : 1;                             // weight tiles per stage
   constexpr int X_OFF = NW * W_STAGE_BYTES;
   constexpr int STAGE_BYTES = X_OFF + BT * TILE_K * 2;
@@ -142,6 +186,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
   int* ticket_s = (int*)(tmem_slot + 2);
   uint8_t* xch_s = (uint8_t*)(((uintptr_t)(tmem_slot + 4) + 15) & ~(uintptr_t)15);   // 4 KB, weight-major gated only
+  uint8_t* out_s = (uint8_t*)(((uintptr_t)(tmem_slot + 4) + 127) & ~(uintptr_t)127);  // 2 x 16 KB, residual add by TMA only
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
@@ -159,8 +204,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const uint32_t tmem_base = *tmem_slot;
   if (threadIdx.x == 0) pdl_launch_dependents();
 
-  const int total_work = p.n_tiles * p.t_tiles * p.splits;
-
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
@@ -171,10 +214,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       uint32_t phase = 0;
       bool ok = true, dep_ready = false;
       int pend_kb[12], pend_t0[12];
-      for (int work = blockIdx.x; ok && work < total_work; work += gridDim.x) {
-        const int split = work % p.splits, tile = work / p.splits;
+      WorkIter it(p);
+      int tile, split, n_parts, kb0, kb1;
+      while (ok && it.next(tile, split, n_parts, kb0, kb1)) {
         const int n0 = (tile / p.t_tiles) * p.n_step, t0 = (tile % p.t_tiles) * BT;
-        const int kb0 = split * p.kb_per_split, kb1 = min(p.kb_total, kb0 + p.kb_per_split);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!dep_ready && issued == stages) {
             pdl_wait();
@@ -220,9 +263,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
-      for (int work = blockIdx.x; ok && work < total_work; work += gridDim.x) {
-        const int split = work % p.splits;
-        const int kb0 = split * p.kb_per_split, kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+      WorkIter it(p);
+      int tile, split, n_parts, kb0, kb1;
+      while (ok && it.next(tile, split, n_parts, kb0, kb1)) {
         if (!wait_or_abort(&acc_empty[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * ACC_STRIDE);
@@ -259,15 +302,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    for (int work = blockIdx.x; ok && work < total_work; work += gridDim.x) {
-      const int split = work % p.splits, tile = work / p.splits;
+    WorkIter it(p);
+    int tile, split, n_parts, kb0, kb1;
+    while (ok && it.next(tile, split, n_parts, kb0, kb1)) {
       const int n0 = (tile / p.t_tiles) * p.n_step, t0 = (tile % p.t_tiles) * BT;
       const int n = n0 + n_local;
       const int t_valid = min(BT, p.M - t0);
       if (!wait_or_abort(&acc_full[acc], acc_phase, abort_flag)) { ok = false; break; }
       tc_fence_after();
+      const bool chained = p.tail_parts > 1 && n_parts > 1;   // a part of a cut tile: adds in its turn
+      if (chained && split > 0) {
+        if (threadIdx.x == 64) {
+          int seen = 0;
+          for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+            asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(p.counters + tile) : "memory");
+            if (seen >= split) break;
+            __nanosleep(64);
+          }
+          if (seen < split) atomicOr(p.err, IERT_ERR_WAIT_EXPIRED);
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      }
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * ACC_STRIDE);
-      float* part = p.splits > 1 ? p.ws + ((size_t)(tile * p.splits + split) * BT) * TILE_N + n_local : nullptr;
+      float* part = (p.splits > 1 && p.tail_parts <= 1) ? p.ws + ((size_t)(tile * p.splits + split) * BT) * TILE_N + n_local : nullptr;
       if (GATED && p.mode == MODE_GATED_SILU) {
         // lane = token, columns [0, 128) = gate rows, [128, 256) = their up rows
         const int tok = t0 + n_local;
@@ -369,8 +426,66 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           asm volatile("bar.sync 1, 128;" ::: "memory");
         }
       }
+      // Many tokens, residual add, whole tile: 32 tokens per pass, so that twice as many reads of
+      // the residual are in flight per round trip (the last tile's epilogue is not hidden behind
+      // any MMA and is pure memory latency).
+      bool wide_done = false;
+      if constexpr (!GATED && BT >= 128) {
+        if (p.tma_out && !part) {                    // the same for every thread
+          // tensor memory -> registers -> shared memory (32 tokens x 128 outputs, output index
+          // fastest) -> TMA adds the box into the residual.  Nothing is read back, so no memory
+          // latency is exposed; two staging buffers, the issuing thread tracks their reads.
+          if (threadIdx.x == 64) tma_prefetch_desc(&map_o);
 #pragma unroll 1
-      for (int c = 0; !GATED && p.mode != MODE_GATED_SILU && c < BT; c += 16) {
+          for (int c = 0; c < BT; c += 32) {
+            if (c >= t_valid) break;
+            float v[32];
+            tmem_ld16_issue(taddr + c, reinterpret_cast<uint32_t*>(v));
+            tmem_ld16_issue(taddr + c + 16, reinterpret_cast<uint32_t*>(v) + 16);
+            float* buf = reinterpret_cast<float*>(out_s + ((c >> 5) & 1) * OUT_STAGE_BYTES);
+            if (threadIdx.x == 64) bulk_wait_group_read<1>();          // the buffer's last reduce has read it
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) buf[j * TILE_N + n_local] = v[j];
+            fence_proxy_async_smem();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (threadIdx.x == 64) {
+              tma_reduce_add_2d(&map_o, buf, n0, t0 + c);
+              bulk_commit_group();
+            }
+          }
+          if (threadIdx.x == 64) {
+            if (p.tail_parts > 1 && n_parts > 1) bulk_wait_group<0>();   // the next part adds after this one
+            else bulk_wait_group_read<0>();
+          }
+          wide_done = true;
+        }
+      }
+      if constexpr (!GATED && BT >= 64) {
+        if (wide_done) {
+        } else
+        if (p.mode == MODE_ADD_RESIDUAL && !part && t_valid == BT) {     // the same for every thread
+          const bool mine = n < p.N;
+#pragma unroll 1
+          for (int c = 0; c < BT; c += 32) {
+            float v[32], r[32];
+            tmem_ld16_issue(taddr + c, reinterpret_cast<uint32_t*>(v));
+            tmem_ld16_issue(taddr + c + 16, reinterpret_cast<uint32_t*>(v) + 16);
+            float* o = (float*)p.out + (long long)(t0 + c) * p.ldo + n;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = mine ? o[(long long)j * p.ldo] : 0.f;
+            tmem_ld_wait();
+            if (mine) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) o[(long long)j * p.ldo] = r[j] + v[j];
+            }
+          }
+          wide_done = true;
+        }
+      }
+#pragma unroll 1
+      for (int c = 0; !GATED && !wide_done && p.mode != MODE_GATED_SILU && c < BT; c += 16) {
         if (c >= t_valid) break;                     // warp-uniform
         float v[16];
         tmem_ld16(taddr + c, v);
@@ -400,6 +515,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       mbar_arrive(&acc_empty[acc]);
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
+      if (chained) {                                 // the next part's turn; the last part puts the counter back
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (threadIdx.x == 64) atomicExch(&p.counters[tile], split + 1 == n_parts ? 0 : split + 1);
+      }
 
       if (part) {
         __threadfence();
@@ -553,6 +673,43 @@ bool tensor_map(const void* ptr, long long rows, long long cols, long long ld, i
   return true;
 }
 
+// The fp32 output [rows, cols] with row stride ld, written in boxes of 32 rows x 128 columns.
+bool tensor_map_out(const void* ptr, long long rows, long long cols, long long ld, CUtensorMap* out) {
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  static std::mutex mu;
+  MapKey key{ptr, rows, cols, ld, 32};
+  std::lock_guard<std::mutex> g(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) { *out = it->second; return true; }
+  EncodeTiledFn fn = encode_fn();
+  if (!fn || (ld & 3) || ((uintptr_t)ptr & 15)) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 4};
+  cuuint32_t box[2] = {(cuuint32_t)TILE_N, 32};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMap m;
+  CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return false;
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, m);
+  *out = m;
+  return true;
+}
+
+bool no_tma_out() {        // IERT_GEMM_TMA_OUT=0: the epilogue reads and writes the residual itself
+  static int v = -1;
+  if (v < 0) { const char* e = getenv("IERT_GEMM_TMA_OUT"); v = (e && e[0] == '0') ? 1 : 0; }
+  return v == 1;
+}
+
+bool no_tail_parts() {     // IERT_GEMM_TAIL_PARTS=0: whole tiles only
+  static int v = -1;
+  if (v < 0) { const char* e = getenv("IERT_GEMM_TAIL_PARTS"); v = (e && e[0] == '0') ? 1 : 0; }
+  return v == 1;
+}
+
 bool no_coop() {           // IERT_GEMM_COOP=0: the last split of a tile always adds alone
   static int v = -1;
   if (v < 0) { const char* e = getenv("IERT_GEMM_COOP"); v = (e && e[0] == '0') ? 1 : 0; }
@@ -570,17 +727,20 @@ int sm_count() {
 }
 
 template <int BT, bool GATED>
-int launch(const CUtensorMap& mw, const CUtensorMap& mx, GemmParams p, int grid, cudaStream_t stream) {
+int launch(const CUtensorMap& mw, const CUtensorMap& mx, GemmParams p, int grid, cudaStream_t stream,
+           const CUtensorMap* mo = nullptr) {
   constexpr int STAGE_BYTES = (GATED ? 2 : 1) * W_STAGE_BYTES + BT * TILE_K * 2;
-  // ring, alignment slack, barriers; the weight-major gated tile adds its exchange buffer
-  const size_t smem = (size_t)p.stages * STAGE_BYTES + 1024 + 256 + ((!GATED && p.mode == MODE_GATED_SILU) ? XCH_BYTES : 0);
+  // ring, alignment slack, barriers; the weight-major gated tile adds its exchange buffer, the
+  // residual add by TMA its two staging buffers
+  const size_t smem = (size_t)p.stages * STAGE_BYTES + 1024 + 256 + ((!GATED && p.mode == MODE_GATED_SILU) ? XCH_BYTES : 0) +
+                      (p.tma_out ? 2 * OUT_STAGE_BYTES + 128 : 0);
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(gemm_tc_kernel<BT, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess)
       return iert_check_launch("gemm_tc attribute");
     configured = true;
   }
-  launch_dep(gemm_tc_kernel<BT, GATED>, dim3(grid), dim3(THREADS), smem, stream, mw, mx, p);
+  launch_dep(gemm_tc_kernel<BT, GATED>, dim3(grid), dim3(THREADS), smem, stream, mw, mx, mo ? *mo : mw, p);
   return iert_check_launch("gemm_tc");
 }
 
@@ -653,6 +813,7 @@ IERT_API int iert_gemm_tc(const void* x, long long ldx, const void* w, long long
   if (bt != 16 && bt != 32 && bt != 64 && bt != 128 && bt != 256) return IERT_BAD_ARGUMENT;
 
   GemmParams p;
+  p.tail_parts = 1; p.full_tiles = 0; p.tma_out = 0;
   p.out = out; p.ldo = ldo; p.out_dtype = out_dtype; p.mode = mode;
   p.M = M; p.N = N; p.K = K;
   p.ws = ws; p.counters = counters; p.err = err;
@@ -726,18 +887,46 @@ IERT_API int iert_gemm_tc(const void* x, long long ldx, const void* w, long long
     p.stages = stages;
   }
 
-  CUtensorMap mw, mx;
+  CUtensorMap mw, mx, mo;
   if (!tensor_map(w, N, K, ldw, TILE_N, &mw) || !tensor_map(x, M, K, ldx, bt, &mx)) return IERT_BAD_ARGUMENT;
-  const int grid = total_work < slots ? total_work : slots;
+  // Many tokens, residual add: the epilogue hands its tile to TMA, which adds it into the residual
+  // (no read of the residual by the SM).  Needs two staging buffers beside the ring.
+  if (mode == MODE_ADD_RESIDUAL && bt >= 128 && splits == 1 && !no_tma_out() && tensor_map_out(out, M, N, ldo, &mo)) {
+    int st = stages;
+    while (st >= 2 && (size_t)st * stage_bytes + 1280 + 2 * OUT_STAGE_BYTES + 128 > 227 * 1024) --st;
+    if (st >= 2 && (force_stages <= 0 || st == stages)) { p.tma_out = 1; stages = st; p.stages = st; }
+  }
+  int grid = total_work < slots ? total_work : slots;
   // the splits of a tile may wait for one another only if every CTA of the grid is resident
   p.coop_reduce = splits > 1 && !no_coop() && total_work <= grid &&
                   grid <= sm_count() * resident_ctas_per_sm(bt, stages);
+  // Residual adds over many tokens whose tiles leave the last wave part empty: the tiles of that
+  // wave are cut into parts of k (see WorkIter).  One CTA per SM; parts chosen to fill the SMs.
+  if (!force_splits && !no_tail_parts() && splits == 1 && mode == MODE_ADD_RESIDUAL && bt >= 128 && ctas_per_sm == 1 &&
+      counters && tiles <= n_counters && tiles > sm_count() && tiles % sm_count() != 0) {
+    const int sms = sm_count(), n_tail = tiles % sms;
+    int best = 1;
+    double best_cost = 1.0;                            // the last wave in units of a whole tile
+    for (int parts = 2; parts <= 8; ++parts) {
+      // A part's epilogue (a few us) has to stay short beside its MMAs, and the parts of a tile add
+      // one after the other: measured, parts pay from about 40 k-blocks each on (K of 14,336 in
+      // four parts: 189 -> 179 us), and cost time below that (K of 4,096: 59 -> 62 us).
+      if (p.kb_total / parts < 40) break;
+      const double cost = (double)((n_tail * parts + sms - 1) / sms) / parts + 0.02 * parts;
+      if (cost < best_cost) { best_cost = cost; best = parts; }
+    }
+    if (best > 1) {
+      p.tail_parts = best;
+      p.full_tiles = tiles - n_tail;
+      grid = sms;
+    }
+  }
   switch (bt) {
     case 16: return launch<16, false>(mw, mx, p, grid, stream);
     case 32: return launch<32, false>(mw, mx, p, grid, stream);
     case 64: return launch<64, false>(mw, mx, p, grid, stream);
-    case 128: return launch<128, false>(mw, mx, p, grid, stream);
-    default: return launch<256, false>(mw, mx, p, grid, stream);
+    case 128: return launch<128, false>(mw, mx, p, grid, stream, p.tma_out ? &mo : nullptr);
+    default: return launch<256, false>(mw, mx, p, grid, stream, p.tma_out ? &mo : nullptr);
   }
 }
 
@@ -751,6 +940,7 @@ IERT_API int iert_gemm_tc_gated(const void* x, long long ldx, const void* w, lon
   if (K <= 0 || (K & 7) || (ldx & 7) || (ldw & 7) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15))
     return IERT_BAD_ARGUMENT;
   GemmParams p;
+  p.tail_parts = 1; p.full_tiles = 0; p.tma_out = 0;
   p.out = act; p.ldo = ldo; p.out_dtype = IERT_BF16; p.mode = MODE_GATED_SILU;
   p.M = M; p.N = inter; p.K = K;
   const bool weight_major = force_bt ? (force_bt != 128 && M <= force_bt)

@@ -59,6 +59,26 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
       : "memory");
 }
 
+// ---- TMA reduce (shared -> global, element-wise add at the destination) -------------------
+// One thread.  The box [c1 .. c1 + box rows) x [c0 .. c0 + box cols) of the tensor gets the
+// tile at `smem_src` added to it (fp32 add performed by the memory system); parts of the box
+// outside the tensor are left out.  c0 * element size must be a multiple of 16 bytes and no
+// coordinate negative.  Completion is tracked by bulk groups (below).
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, const void* smem_src, int c0, int c1) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(smem_addr(smem_src)), "r"(c0), "r"(c1)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// At most N of this thread's bulk groups still read their shared-memory source.
+template <int N> __device__ __forceinline__ void bulk_wait_group_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+// At most N of this thread's bulk groups are not yet complete (their writes performed).
+template <int N> __device__ __forceinline__ void bulk_wait_group() {
+  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+
 // ---- tensor memory ------------------------------------------------------------------------
 // Whole warp.  `ncols`: power of two in [32, 512].  The base address lands in *slot (shared).
 __device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t ncols) {

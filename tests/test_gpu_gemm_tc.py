@@ -66,6 +66,21 @@ def test_short_pipelines_wrap():
     run(130, 1100, 2048, B.GEMM_STORE, torch.float32, force_stages=3)          # several tiles per CTA
 
 
+@pytest.mark.parametrize("M,N,K", [(2048, 4096, 192), (2000, 4096, 1024), (1500, 5120, 520), (4096, 4096, 64),
+                                   (700, 9000, 136), (2048, 4096, 2560), (1100, 4224, 5128), (300, 20000, 2568),
+                                   (2048, 4096, 14336)])
+def test_residual_add_over_many_tokens(M, N, K):
+    """Residual adds over many tokens: the epilogue hands its tile to TMA, which adds it into the
+    residual; with a long k the tiles of the last, partly empty wave are cut into parts of k whose
+    products are added in a fixed order (here K = 2,560 and more).  Repeatable to the bit."""
+    from inference_engine_rust_b200.csrc import bindings as B
+    a = run(M, N, K, B.GEMM_ADD_RESIDUAL, torch.float32)
+    b = run(M, N, K, B.GEMM_ADD_RESIDUAL, torch.float32)
+    assert torch.equal(a, b), "two identical runs differ"
+    sc = B.GemmScratch.get(a.device)
+    assert int(sc.counters.abs().sum()) == 0, "a tile's flag was left raised"
+
+
 def test_many_tiles_per_cta():
     from inference_engine_rust_b200.csrc import bindings as B
     run(1500, 4096, 256, B.GEMM_STORE, torch.bfloat16)                         # 32 x 6 tiles on 148 CTAs
