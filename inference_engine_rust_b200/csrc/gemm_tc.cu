@@ -28,6 +28,12 @@
 // prompt projection (store or add into the residual): a thread then owns one token's 16
 // consecutive outputs per chunk, so its loads and stores are 16-byte vectors.  Whole tiles only.
 //
+// Residual adds over many tokens (tiles of 128 or 256 tokens) do not read the residual back:
+// the epilogue stages 32 tokens x 128 outputs of its accumulator in shared memory and a TMA
+// reduce (cp.reduce.async.bulk.tensor, fp32 add at the destination) adds them in.  When such a
+// product's tiles leave the last wave part empty and k is long, the tiles of that wave are cut
+// into parts of k whose products are added one after the other in a fixed order (see WorkIter).
+//
 // Every wait on an mbarrier is bounded; when one runs out the kernel sets
 // IERT_ERR_WAIT_EXPIRED in the error word, drains its own TMA copies, frees its TMEM and
 // returns.
