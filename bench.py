@@ -224,7 +224,7 @@ def main() -> int:
     if not a.no_prefill:
         prompt = rng.integers(0, vocab, a.prefill_tokens).tolist()
         times = []
-        for i in range(3 + 3):
+        for i in range(3 + 5):
             s = eng.open_sequence()
             start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             start.record()
@@ -242,7 +242,8 @@ def main() -> int:
         flops = 2 * T * L * (H * qkv + qd * H + 3 * H * I) + 2 * H * V + L * 2 * T * T * qd
         prefill = {"value": round(T * 1e3 / pms, 1), "tokens": T, "ms": round(pms, 3),
                    "frac": round(flops / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4), "unit": "tokens/s",
-                   "tflops": round(flops / (pms * 1e-3) / 1e12, 1), "peak_tflops": pk["bf16_tflops"]}
+                   "tflops": round(flops / (pms * 1e-3) / 1e12, 1), "peak_tflops": pk["bf16_tflops"],
+                   "runs": len(times), "ms_min": round(min(times), 3), "ms_max": round(max(times), 3)}
         if "bf16_tflops_sustained" in pk:      # the step is tens of milliseconds of dense tensor work
             prefill["frac_of_sustained"] = round(flops / (pms * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12), 4)
     clocks.stop()
