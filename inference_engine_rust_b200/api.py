@@ -86,14 +86,15 @@ class InferenceSession:
 
     max_tokens     positions the cache holds over all live sequences (each rounded up to 64)
     max_sequences  slots; default: as many as there are pages, at most 1024
+    use_graphs     replay captured CUDA graphs for one-token steps and short prompts (default)
     """
 
     def __init__(self, model: LoadedModel, max_tokens: int = 8192,
                  max_sequences: Optional[int] = None, max_seq_len: Optional[int] = None,
-                 poison_cache: bool = False):
+                 poison_cache: bool = False, use_graphs: bool = True):
         self.loaded = model
         self.engine = Engine(model.model, max_tokens=max_tokens, max_sequences=max_sequences,
-                             max_seq_len=max_seq_len, poison_cache=poison_cache)
+                             max_seq_len=max_seq_len, poison_cache=poison_cache, use_graphs=use_graphs)
         self.max_tokens = max_tokens
         self._slots: List[int] = []
 

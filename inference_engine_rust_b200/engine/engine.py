@@ -94,6 +94,45 @@ class _DecodeGraph:
             rt.workspace = saved
 
 
+class _PromptGraph:
+    """A captured prompt step for up to `nb` sequences and `tb` tokens in all (short prompts,
+    where launching a few hundred kernels costs the host more than they cost the device).
+    Tokens beyond the step's own are padding (sequence -1) and sequences beyond its own have
+    slot -1: every kernel skips them, so padding changes no result."""
+
+    def __init__(self, engine: "Engine", nb: int, tb: int):
+        rt, model = engine.rt, engine.model
+        from ..parts.base import Workspace
+        self.nb, self.tb = nb, tb
+        _, o_slot, _, o_seq, o_tok, o_rows, total = Engine._layout(nb, tb, nb)
+        self.meta = torch.zeros(total, dtype=torch.int32, device=rt.device)
+        self.meta[o_slot:o_slot + nb] = -1            # all padding until a step fills it in
+        self.meta[o_seq:o_seq + tb] = -1
+        self.logits = torch.empty((nb, model.spec.vocab_size), dtype=torch.float32, device=rt.device)
+        self.ws = Workspace(rt.device)
+        self.graph = torch.cuda.CUDAGraph()
+        saved = rt.workspace
+        rt.workspace = self.ws
+        try:
+            def run():
+                # launches are sized for the longest prompt the bucket can hold
+                ctx = engine._context("prompt", self.meta, nb, tb, [tb] + [0] * (nb - 1), [0] * nb, [-1] * nb)
+                model.forward(ctx, self.meta[o_tok:o_tok + tb], engine.cache,
+                              self.meta[o_rows:o_rows + nb], nb, logits_out=self.logits)
+            run()                                      # eager once: lazy set-up happens outside the capture
+            torch.cuda.synchronize()
+            before = B.launch_count
+            with torch.cuda.graph(self.graph):
+                run()
+            self.launches = B.launch_count - before
+        finally:
+            rt.workspace = saved
+
+
+PROMPT_GRAPH_MAX_TOKENS = 512       # longer prompts keep the device busy enough when launched one by one
+PROMPT_GRAPH_MAX_SEQUENCES = 8
+
+
 class Engine:
     """A model, its cache, and the step function over them."""
 
@@ -123,6 +162,7 @@ class Engine:
         # forward depends on the step only through device memory
         self.use_graphs = use_graphs and model.graph_safe()
         self._graphs = {}
+        self._prompt_uses = {}
 
     # ---- sequences ------------------------------------------------------------------------
     def open_sequence(self) -> int:
@@ -199,6 +239,9 @@ class Engine:
         self.cache.upload()
         if kind == "decode" and self.use_graphs and R in (0, n) and rows == list(range(R)):
             logits = self._step_graph(slots, pos0, tokens, R)
+        elif (kind == "prompt" and self.use_graphs and T <= PROMPT_GRAPH_MAX_TOKENS and n <= PROMPT_GRAPH_MAX_SEQUENCES
+              and R in (0, n) and rows == [int(c) - 1 for c in cu[1:1 + R]] and self._prompt_bucket_is_warm(n, T)):
+            logits = self._step_prompt_graph(slots, q_lens, tokens, cu, R)
         else:
             logits = self._step_eager(kind, slots, q_lens, pos0, tokens, cu, rows)
         for slot, q in zip(slots, q_lens):
@@ -270,6 +313,50 @@ class Engine:
         h[o_tok:o_tok + nb] = 0
         h[o_tok:o_tok + n] = tokens
         h[o_rows:o_rows + nb] = np.arange(nb)
+        g.meta[:total].copy_(host[:total], non_blocking=True)
+        self._staging.sent(turn)
+        self.h2d_bytes_last_step = total * 4
+        g.graph.replay()
+        self.graph_launches += g.launches
+        return g.logits[:n].clone() if R else None
+
+    def _prompt_bucket_is_warm(self, n: int, T: int) -> bool:
+        """A bucket of prompt shapes gets its graph when it is used for the second time: a
+        session that runs one prompt and is dropped never pays for a capture."""
+        nb = 1
+        while nb < n:
+            nb *= 2
+        key = ("prompt", nb, -(-T // 64) * 64)
+        if key in self._graphs:
+            return True
+        self._prompt_uses[key] = self._prompt_uses.get(key, 0) + 1
+        return self._prompt_uses[key] >= 2
+
+    def _step_prompt_graph(self, slots, q_lens, tokens, cu, R):
+        """A short prompt step through a captured graph: sequences padded to a power of two, tokens
+        to a multiple of 64; logits at each prompt's last token (or none)."""
+        n, T = len(slots), int(cu[-1])
+        nb = 1
+        while nb < n:
+            nb *= 2
+        tb = -(-T // 64) * 64
+        g = self._graphs.get(("prompt", nb, tb))
+        if g is None:
+            g = self._graphs[("prompt", nb, tb)] = _PromptGraph(self, nb, tb)
+        o_cu, o_slot, o_pos, o_seq, o_tok, o_rows, total = self._layout(nb, tb, nb)
+        host, turn = self._staging.next(total)
+        h = host.numpy()
+        h[o_cu:o_cu + n + 1] = cu
+        h[o_cu + n + 1:o_cu + nb + 1] = T              # padding sequences are empty
+        h[o_slot:o_slot + nb] = -1
+        h[o_slot:o_slot + n] = slots
+        h[o_pos:o_pos + nb] = 0
+        h[o_seq:o_seq + tb] = -1
+        h[o_seq:o_seq + T] = np.repeat(np.arange(n, dtype=np.int32), q_lens)
+        h[o_tok:o_tok + tb] = 0
+        h[o_tok:o_tok + T] = tokens
+        h[o_rows:o_rows + nb] = 0
+        h[o_rows:o_rows + n] = cu[1:] - 1
         g.meta[:total].copy_(host[:total], non_blocking=True)
         self._staging.sent(turn)
         self.h2d_bytes_last_step = total * 4

@@ -192,3 +192,33 @@ def test_sizes_at_the_edges(tmp_root, name, dtype):
         eng.check_device()
         compare(torch.cat(rows), ref, dtype, f"{name} {dtype}, {n} tokens")
         eng.close_sequence(s)
+
+
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("A", "bfloat16"), ("C", "bfloat16"), ("B", "float32")])
+def test_short_prompts_through_captured_graphs(tmp_root, name, dtype):
+    """Short prompt steps replay a captured graph from the second use of a shape bucket on (tokens
+    padded to a multiple of 64, sequences to a power of two).  Padding changes no result: the
+    logits equal those of the same step launched kernel by kernel, and the cache holds the same."""
+    model, prompts, want = _setup(tmp_root, name, dtype)
+    cfg = TINY[name]
+    eager = new_engine(model, max_tokens=64 * 24, use_graphs=False)
+    graph = new_engine(model, max_tokens=64 * 24)
+    assert graph.use_graphs
+    sets = [prompts_for(cfg, lens, seed=40 + k) for k, lens in enumerate(
+        ([1], [63], [64], [65], [5, 11, 23], [130, 7, 60], [3, 1, 2, 9, 17], [200, 250]))]
+    for rep in range(3):                       # first use of a bucket: eager; from the second on: replay
+        for ps in sets:
+            out = {}
+            for label, eng in (("eager", eager), ("graph", graph)):
+                slots = [eng.open_sequence() for _ in ps]
+                first = eng.step(list(zip(slots, ps)), want="last")
+                nxt = eng.step([(s, [7 % cfg["vocab_size"]]) for s in slots], want="last")   # reads the cache the prompt wrote
+                eng.check_device()
+                out[label] = torch.cat([first, nxt]).clone()
+                for s in slots:
+                    eng.close_sequence(s)
+            compare(out["graph"], out["eager"], dtype, f"{name} {dtype} prompts of {[len(p) for p in ps]}, pass {rep}")
+            if dtype == "float32":
+                assert torch.equal(out["graph"], out["eager"]), "the true 32-bit path must not depend on padding at all"
+    assert any(isinstance(k, tuple) for k in graph._graphs), "no prompt graph was captured"
+    assert graph.graph_launches > 0
