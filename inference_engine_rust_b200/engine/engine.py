@@ -320,13 +320,19 @@ class Engine:
         self.graph_launches += g.launches
         return g.logits[:n].clone() if R else None
 
+    @staticmethod
+    def _token_bucket(T: int) -> int:
+        """Padded token count of a short prompt step: 16, 32, then multiples of 64 (the token tiles
+        of the projection kernel)."""
+        return 16 if T <= 16 else 32 if T <= 32 else -(-T // 64) * 64
+
     def _prompt_bucket_is_warm(self, n: int, T: int) -> bool:
         """A bucket of prompt shapes gets its graph when it is used for the second time: a
         session that runs one prompt and is dropped never pays for a capture."""
         nb = 1
         while nb < n:
             nb *= 2
-        key = ("prompt", nb, -(-T // 64) * 64)
+        key = ("prompt", nb, self._token_bucket(T))
         if key in self._graphs:
             return True
         self._prompt_uses[key] = self._prompt_uses.get(key, 0) + 1
@@ -339,7 +345,7 @@ class Engine:
         nb = 1
         while nb < n:
             nb *= 2
-        tb = -(-T // 64) * 64
+        tb = self._token_bucket(T)
         g = self._graphs.get(("prompt", nb, tb))
         if g is None:
             g = self._graphs[("prompt", nb, tb)] = _PromptGraph(self, nb, tb)

@@ -197,7 +197,7 @@ def test_sizes_at_the_edges(tmp_root, name, dtype):
 @pytest.mark.parametrize("name,dtype", [("A", "float32"), ("A", "bfloat16"), ("C", "bfloat16"), ("B", "float32")])
 def test_short_prompts_through_captured_graphs(tmp_root, name, dtype):
     """Short prompt steps replay a captured graph from the second use of a shape bucket on (tokens
-    padded to a multiple of 64, sequences to a power of two).  Padding changes no result: the
+    padded to 16, 32 or a multiple of 64, sequences to a power of two).  Padding changes no result: the
     logits equal those of the same step launched kernel by kernel, and the cache holds the same."""
     model, prompts, want = _setup(tmp_root, name, dtype)
     cfg = TINY[name]
@@ -205,7 +205,7 @@ def test_short_prompts_through_captured_graphs(tmp_root, name, dtype):
     graph = new_engine(model, max_tokens=64 * 24)
     assert graph.use_graphs
     sets = [prompts_for(cfg, lens, seed=40 + k) for k, lens in enumerate(
-        ([1], [63], [64], [65], [5, 11, 23], [130, 7, 60], [3, 1, 2, 9, 17], [200, 250]))]
+        ([1], [16], [17], [33], [63], [64], [65], [5, 11, 23], [2, 3], [130, 7, 60], [3, 1, 2, 9, 17], [200, 250]))]
     for rep in range(3):                       # first use of a bucket: eager; from the second on: replay
         for ps in sets:
             out = {}
