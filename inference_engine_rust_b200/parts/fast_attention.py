@@ -7,7 +7,7 @@ import torch
 
 from ..csrc import bindings as B
 
-_RESIDENT_CTAS = 2 * 148         # two CTAs fit an SM (three-page rings of keys and values)
+_CTAS_PER_SM = 2                 # two CTAs fit an SM (three-page rings of keys and values)
 _MAX_SPLITS = 16
 
 
@@ -17,7 +17,7 @@ def decode_splits(n_tokens: int, kv_heads: int, group: int) -> int:
     only, never on the sequences' lengths, so a captured graph stays valid."""
     slices = -(-group // 8)
     ctas = max(1, n_tokens * kv_heads * slices)
-    return max(1, min(_MAX_SPLITS, _RESIDENT_CTAS // ctas))      # as many splits as stay one wave
+    return max(1, min(_MAX_SPLITS, _CTAS_PER_SM * B.sm_count() // ctas))      # as many splits as stay one wave
 
 
 def decode_with_rotation(attn, qkv, out, ctx, cache_view, writes_cache: bool) -> bool:
