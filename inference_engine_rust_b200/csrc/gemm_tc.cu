@@ -72,6 +72,7 @@ struct GemmParams {
   float* ws;          // [tiles][splits][BT][TILE_N] fp32 partials (splits > 1)
   int* counters;      // [tiles] tickets, zero between launches
   int coop_reduce;    // splits > 1: every split adds its share of the rows (the grid is co-resident)
+  int t_group;        // token tiles per group in the order of the tiles (see tile_coords); t_tiles = one group
   int tma_out;        // residual add through TMA reduce (map_o), weight-major tiles of >= 128 tokens
   int tail_parts;     // > 1: the tiles from full_tiles on are cut into this many parts of k (see WorkIter)
   int full_tiles;
@@ -137,6 +138,20 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
 // parts of a tile add their products into the residual one after the other, in the order of the
 // parts, each waiting (bounded) until the tile's counter shows its turn: the order of the
 // additions is fixed, the result repeatable, and no scratch memory is used.
+// Tile index -> (weight-row tile, token tile).  The token tiles are walked in groups of
+// p.t_group: within a group the token tile runs fastest, then the weight-row tile, then the next
+// group.  CTAs that run at the same time work on neighbouring tiles and move through k
+// together, so a group's activations (sized by the host to stay in the L2) are read from memory
+// once and the weight matrix once per group.
+__device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& n_idx, int& t_idx) {
+  const int tg = min(p.t_group, p.t_tiles);             // any larger value means one group
+  const int per_group = tg * p.n_tiles;
+  const int group = tile / per_group, r = tile - group * per_group;
+  const int in_group = min(tg, p.t_tiles - group * tg);
+  n_idx = r / in_group;
+  t_idx = group * tg + (r - n_idx * in_group);
+}
+
 struct WorkIter {
   const GemmParams& p;
   int work, total_work, n_tail;
@@ -223,7 +238,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       WorkIter it(p);
       int tile, split, n_parts, kb0, kb1;
       while (ok && it.next(tile, split, n_parts, kb0, kb1)) {
-        const int n0 = (tile / p.t_tiles) * p.n_step, t0 = (tile % p.t_tiles) * BT;
+        int n_idx, t_idx;
+        tile_coords(p, tile, n_idx, t_idx);
+        const int n0 = n_idx * p.n_step, t0 = t_idx * BT;
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!dep_ready && issued == stages) {
             pdl_wait();
@@ -311,7 +328,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     WorkIter it(p);
     int tile, split, n_parts, kb0, kb1;
     while (ok && it.next(tile, split, n_parts, kb0, kb1)) {
-      const int n0 = (tile / p.t_tiles) * p.n_step, t0 = (tile % p.t_tiles) * BT;
+      int n_idx, t_idx;
+      tile_coords(p, tile, n_idx, t_idx);
+      const int n0 = n_idx * p.n_step, t0 = t_idx * BT;
       const int n = n0 + n_local;
       const int t_valid = min(BT, p.M - t0);
       if (!wait_or_abort(&acc_full[acc], acc_phase, abort_flag)) { ok = false; break; }
@@ -704,6 +723,25 @@ bool tensor_map_out(const void* ptr, long long rows, long long cols, long long l
   return true;
 }
 
+// How many token tiles make a group in the order of the tiles (see tile_coords).  With one group
+// (all token tiles) the whole activation matrix is read once per weight-row tile unless it stays
+// in the L2; with smaller groups the weight matrix is read once per group instead.  A group's
+// activations are kept to 32 MB so that they do stay; estimated traffic decides between the two.
+// With a prompt of 2,048 tokens the activations of most products fit anyway; with 29,000 tokens
+// one group would read them 32 to 112 times.
+int token_tiles_per_group(long long x_tile_bytes, long long w_bytes, int n_tiles, int t_tiles) {
+  const long long keep = 64ll << 20, group_bytes = 32ll << 20;
+  const long long x_bytes = x_tile_bytes * t_tiles;
+  if (x_bytes <= keep) return t_tiles;
+  long long g = group_bytes / (x_tile_bytes > 0 ? x_tile_bytes : 1);
+  if (g < 1) g = 1;
+  if (g >= t_tiles) return t_tiles;
+  const long long groups = (t_tiles + g - 1) / g;
+  const long long one_group = x_bytes * n_tiles + w_bytes;
+  const long long grouped = (w_bytes <= keep ? w_bytes : w_bytes * groups) + x_bytes;
+  return grouped < one_group ? (int)g : t_tiles;
+}
+
 bool no_tma_out() {        // IERT_GEMM_TMA_OUT=0: the epilogue reads and writes the residual itself
   static int v = -1;
   if (v < 0) { const char* e = getenv("IERT_GEMM_TMA_OUT"); v = (e && e[0] == '0') ? 1 : 0; }
@@ -819,7 +857,7 @@ IERT_API int iert_gemm_tc(const void* x, long long ldx, const void* w, long long
   if (bt != 16 && bt != 32 && bt != 64 && bt != 128 && bt != 256) return IERT_BAD_ARGUMENT;
 
   GemmParams p;
-  p.tail_parts = 1; p.full_tiles = 0; p.tma_out = 0;
+  p.tail_parts = 1; p.full_tiles = 0; p.tma_out = 0; p.t_group = 1 << 30;
   p.out = out; p.ldo = ldo; p.out_dtype = out_dtype; p.mode = mode;
   p.M = M; p.N = N; p.K = K;
   p.ws = ws; p.counters = counters; p.err = err;
@@ -833,6 +871,7 @@ IERT_API int iert_gemm_tc(const void* x, long long ldx, const void* w, long long
     p.t_tiles = (M + 127) / 128;
     p.kb_total = (K + TILE_K - 1) / TILE_K;
     p.splits = 1; p.kb_per_split = p.kb_total; p.coop_reduce = 0;
+    p.t_group = token_tiles_per_group(2ll * 128 * K, 2ll * N * K, p.n_tiles, p.t_tiles);
     const int stage_bytes = 2 * W_STAGE_BYTES + 128 * TILE_K * 2;
     int stages = force_stages ? force_stages : (226 * 1024 - 2048) / stage_bytes;
     if (stages < 2 || (size_t)stages * stage_bytes + 1280 > 227 * 1024) return IERT_BAD_ARGUMENT;
@@ -846,6 +885,7 @@ IERT_API int iert_gemm_tc(const void* x, long long ldx, const void* w, long long
   p.n_tiles = (N + TILE_N - 1) / TILE_N;
   p.t_tiles = (M + bt - 1) / bt;
   p.kb_total = (K + TILE_K - 1) / TILE_K;
+  p.t_group = token_tiles_per_group(2ll * bt * K, 2ll * N * K, p.n_tiles, p.t_tiles);
   const int tiles = p.n_tiles * p.t_tiles;
   const int stage_bytes = W_STAGE_BYTES + bt * TILE_K * 2;
   const int ctas_per_sm = bt <= 64 ? 2 : 1;
@@ -946,7 +986,7 @@ IERT_API int iert_gemm_tc_gated(const void* x, long long ldx, const void* w, lon
   if (K <= 0 || (K & 7) || (ldx & 7) || (ldw & 7) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15))
     return IERT_BAD_ARGUMENT;
   GemmParams p;
-  p.tail_parts = 1; p.full_tiles = 0; p.tma_out = 0;
+  p.tail_parts = 1; p.full_tiles = 0; p.tma_out = 0; p.t_group = 1 << 30;
   p.out = act; p.ldo = ldo; p.out_dtype = IERT_BF16; p.mode = MODE_GATED_SILU;
   p.M = M; p.N = inter; p.K = K;
   const bool weight_major = force_bt ? (force_bt != 128 && M <= force_bt)
@@ -986,6 +1026,7 @@ IERT_API int iert_gemm_tc_gated(const void* x, long long ldx, const void* w, lon
   p.kb_total = (K + TILE_K - 1) / TILE_K;
   p.splits = 1; p.kb_per_split = p.kb_total; p.coop_reduce = 0;
   p.ws = nullptr; p.counters = nullptr; p.err = err;
+  p.t_group = token_tiles_per_group(2ll * bt * K, 4ll * inter * K, p.n_tiles, p.t_tiles);
   const int tiles = p.n_tiles * p.t_tiles;
   const int stage_bytes = 2 * W_STAGE_BYTES + bt * TILE_K * 2;
   const int slots = sm_count();
