@@ -730,6 +730,9 @@ bool tensor_map_out(const void* ptr, long long rows, long long cols, long long l
 // With a prompt of 2,048 tokens the activations of most products fit anyway; with 29,000 tokens
 // one group would read them 32 to 112 times.
 int token_tiles_per_group(long long x_tile_bytes, long long w_bytes, int n_tiles, int t_tiles) {
+  static int off = -1;       // IERT_GEMM_TILE_GROUPS=0: always one group (token tiles fastest)
+  if (off < 0) { const char* e = getenv("IERT_GEMM_TILE_GROUPS"); off = (e && e[0] == '0') ? 1 : 0; }
+  if (off) return t_tiles;
   const long long keep = 64ll << 20, group_bytes = 32ll << 20;
   const long long x_bytes = x_tile_bytes * t_tiles;
   if (x_bytes <= keep) return t_tiles;
