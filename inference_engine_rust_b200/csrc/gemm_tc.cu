@@ -856,7 +856,9 @@ IERT_API int iert_gemm_tc(const void* x, long long ldx, const void* w, long long
   if (mode == MODE_ADD_RESIDUAL && out_dtype != IERT_F32) return IERT_BAD_ARGUMENT;
 
   int bt = force_bt;
-  if (!bt) bt = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+  // up to 512 tokens 128-token tiles (twice as many of them) beat 256-token tiles with split-K:
+  // 512-token prompt 9.7 -> 8.6 ms, 384 tokens 8.7 -> 7.8 ms; from 1,024 tokens on there is no difference
+  if (!bt) bt = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 512 ? 128 : 256;
   if (bt != 16 && bt != 32 && bt != 64 && bt != 128 && bt != 256) return IERT_BAD_ARGUMENT;
 
   GemmParams p;
