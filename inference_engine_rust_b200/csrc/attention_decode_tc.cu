@@ -2,7 +2,7 @@
 // split over the keys, bf16 operands (mma.sync m16n8k16), fp32 scores / softmax / output.
 // Compiled once per head size (-DHEAD_DIM, multiple of 16 up to 256), like the prompt kernel.
 //
-//   grid (splits, kv_heads * slices, sequences).  The up to 16 query heads that share one kv
+//   grid (kv_heads * slices, sequences, splits).  The up to 16 query heads that share one kv
 //   head are the 16 rows of the MMA tile, so every key and value is read once per group and
 //   the arithmetic is a handful of MMAs per page: the kernel is a stream of page loads.
 //   A CTA walks its share of the sequence's 64-position pages; each page's keys and values
@@ -45,6 +45,7 @@ struct DecodeTcParams {
   float* part_ml;             // [T, heads, splits, 2]  (maximum in base-2 units, sum)
   __nv_bfloat16* out;         // [T, heads * HD]
   int heads, splits, slices, gt;
+  int target_ctas;            // > 0: a sequence is cut into as many of the `splits` parts as its length asks for
   float scale_log2e;
   int* err;
   // Fused position encoding (rope != 0): `qkv` comes straight from the projection; the kernel
@@ -91,6 +92,35 @@ __device__ __forceinline__ void load_page(uint8_t* tile, const __nv_bfloat16* sr
   }
 }
 
+// Pages of keys a one-token step of sequence s reads (0 for a padding sequence).
+__device__ __forceinline__ int pages_of_sequence(const IertBatchView& b, const IertKvView& c, int s) {
+  if (b.slot_ids[s] < 0) return 0;
+  const int pos = b.pos0[s] + (b.cu_q[s + 1] - b.cu_q[s]) - 1;
+  const int j_min = c.window > 0 ? max(0, pos + 1 - c.window) : 0;
+  return pos / PAGE + 1 - j_min / PAGE;
+}
+
+// Into how many parts a sequence of `my_pages` pages is cut when the sequences of the step have
+// unequal lengths: every part should hold about total pages / target CTAs, so that a long sequence
+// gets many short parts and a short one a single part, and the step ends when the average CTA
+// does rather than when the longest sequence's CTAs do.  Every CTA of the step computes the same
+// numbers from the step's description (whole block; `red`: shared scratch of blockDim / 32 ints).
+__device__ int balanced_parts(const IertBatchView& b, const IertKvView& c, int my_pages, int max_parts,
+                              int target_ctas, int ctas_per_sequence_part, int* red) {
+  int tot = 0;
+  for (int s = threadIdx.x; s < b.n_seqs; s += blockDim.x) tot += pages_of_sequence(b, c, s);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = tot;
+  __syncthreads();
+  tot = 0;
+  for (int w = 0; w < (int)(blockDim.x >> 5); ++w) tot += red[w];
+  __syncthreads();
+  const long long units = (long long)tot * ctas_per_sequence_part;
+  const int per_part = (int)max(1ll, (units + target_ctas - 1) / target_ctas);
+  return max(1, min(max_parts, (my_pages + per_part - 1) / per_part));
+}
+
 __global__ void __launch_bounds__(THREADS)
 attention_decode_tc_kernel(DecodeTcParams p, IertBatchView b, IertKvView c) {
   extern __shared__ __align__(16) uint8_t smem[];
@@ -105,8 +135,8 @@ attention_decode_tc_kernel(DecodeTcParams p, IertBatchView b, IertKvView c) {
   // description, the page table and every older page are in place already.  So a CTA whose
   // first pages are older than the newest one starts fetching them before it waits for that
   // kernel.
-  const int split = blockIdx.x, t = blockIdx.z;
-  const int kvh = blockIdx.y / p.slices, slice = blockIdx.y % p.slices;
+  const int split = blockIdx.z, t = blockIdx.y;      // parts slowest: CTAs of parts a sequence does not use start last
+  const int kvh = blockIdx.x / p.slices, slice = blockIdx.x % p.slices;
   const int group = p.heads / c.kv_heads;
   const int g0 = slice * p.gt;
   const int n_g = min(p.gt, group - g0);
@@ -130,7 +160,13 @@ attention_decode_tc_kernel(DecodeTcParams p, IertBatchView b, IertKvView c) {
   const int pos = b.pos0[s] + (t - b.cu_q[s]);
   const int j_min = c.window > 0 ? max(0, pos + 1 - c.window) : 0;
   const int pg_lo = j_min / PAGE, pg_hi = pos / PAGE + 1;           // logical pages [pg_lo, pg_hi)
-  const int per = (pg_hi - pg_lo + p.splits - 1) / p.splits;
+  int n_splits = p.splits;
+  if (p.target_ctas > 0 && p.splits > 1) {
+    __shared__ int red[WARPS];
+    n_splits = balanced_parts(b, c, pg_hi - pg_lo, p.splits, p.target_ctas, gridDim.x, red);
+    if (split >= n_splits) return;                     // this sequence is cut into fewer parts
+  }
+  const int per = (pg_hi - pg_lo + n_splits - 1) / n_splits;
   const int my_lo = pg_lo + split * per, my_hi = min(pg_hi, my_lo + per);
 
   // this CTA's range holds the newest page and the kernel has to supply the newest row itself
@@ -342,21 +378,37 @@ attention_decode_tc_kernel(DecodeTcParams p, IertBatchView b, IertKvView c) {
 }
 
 // One block per (token, head): merge the splits in split order, normalise, write bf16.
-__global__ void attention_decode_tc_combine_kernel(DecodeTcParams p) {
+__global__ void attention_decode_tc_combine_kernel(DecodeTcParams p, IertBatchView b, IertKvView c) {
+  __shared__ int red[8];
   pdl_launch_dependents();     // the next kernel may start its preamble now
-  pdl_wait();                  // everything below may depend on the kernel before
   const int t = blockIdx.x, head = blockIdx.y;
+  // how many parts this token's sequence was cut into (the attention kernel computed the same)
+  int n_splits = p.splits;
+  const int s_ = b.tok_seq[t];
+  const bool live = s_ >= 0 && b.slot_ids[s_] >= 0;
+  if (p.target_ctas > 0 && p.splits > 1 && live) {
+    const int pos = b.pos0[s_] + (t - b.cu_q[s_]);
+    const int j_min = c.window > 0 ? max(0, pos + 1 - c.window) : 0;
+    const int group = p.heads / c.kv_heads;
+    n_splits = balanced_parts(b, c, pos / PAGE + 1 - j_min / PAGE, p.splits, p.target_ctas,
+                              c.kv_heads * ((group + p.gt - 1) / p.gt), red);
+  }
+  pdl_wait();                  // everything below may depend on the kernel before
+  __nv_bfloat16* o = p.out + ((size_t)t * p.heads + head) * HD;
+  if (!live) {                 // a padding sequence: zeros
+    for (int d = threadIdx.x; d < HD; d += blockDim.x) o[d] = __float2bfloat16_rn(0.f);
+    return;
+  }
   const float* po = p.part_out + ((size_t)t * p.heads + head) * p.splits * HD;
   const float* pml = p.part_ml + ((size_t)t * p.heads + head) * p.splits * 2;
   float mm = -INFINITY;
-  for (int s = 0; s < p.splits; ++s) mm = fmaxf(mm, pml[2 * s]);
+  for (int s = 0; s < n_splits; ++s) mm = fmaxf(mm, pml[2 * s]);
   float ll = 0.f;
-  for (int s = 0; s < p.splits; ++s) ll += pml[2 * s] == -INFINITY ? 0.f : exp2f(pml[2 * s] - mm) * pml[2 * s + 1];
+  for (int s = 0; s < n_splits; ++s) ll += pml[2 * s] == -INFINITY ? 0.f : exp2f(pml[2 * s] - mm) * pml[2 * s + 1];
   const float inv = ll > 0.f ? 1.0f / ll : 0.f;
-  __nv_bfloat16* o = p.out + ((size_t)t * p.heads + head) * HD;
   for (int d = threadIdx.x; d < HD; d += blockDim.x) {
     float acc = 0.f;
-    for (int s = 0; s < p.splits; ++s)
+    for (int s = 0; s < n_splits; ++s)
       if (pml[2 * s] != -INFINITY) acc += exp2f(pml[2 * s] - mm) * po[(size_t)s * HD + d];
     o[d] = __float2bfloat16_rn(acc * inv);
   }
@@ -371,7 +423,7 @@ IERT_API long long iert_attention_decode_tc_scratch_floats(int n_tokens, int hea
 namespace {
 
 int launch_decode(const void* qkv, void* out, const IertBatchView* batch, const IertKvView* cache, int heads,
-                  float scale, int splits, float* scratch, const float* inv_freq, int rope, int rotary_dim,
+                  float scale, int splits, int target_ctas, float* scratch, const float* inv_freq, int rope, int rotary_dim,
                   int pairing, int store, int* err, cudaStream_t stream) {
   const int T = batch->n_tokens;
   if (T <= 0) return IERT_OK;
@@ -385,7 +437,7 @@ int launch_decode(const void* qkv, void* out, const IertBatchView* batch, const 
   DecodeTcParams p;
   p.qkv = (const __nv_bfloat16*)qkv;
   p.out = (__nv_bfloat16*)out;
-  p.heads = heads; p.splits = splits;
+  p.heads = heads; p.splits = splits; p.target_ctas = target_ctas > 0 ? target_ctas : 0;
   p.gt = group < 8 ? group : 8;                      // heads per CTA (rows 0..7 of the MMA tile)
   p.slices = (group + p.gt - 1) / p.gt;
   p.scale_log2e = scale * 1.4426950408889634f;
@@ -393,7 +445,7 @@ int launch_decode(const void* qkv, void* out, const IertBatchView* batch, const 
   p.part_out = scratch;
   p.part_ml = scratch + (size_t)T * heads * splits * HD;
   p.inv_freq = inv_freq; p.rope = rope; p.rotary_dim = rotary_dim; p.pairing = pairing; p.store = store;
-  if ((long long)cache->kv_heads * p.slices > 65535) return IERT_BAD_ARGUMENT;
+  if (splits > 65535) return IERT_BAD_ARGUMENT;
   // page ring, query tile, angle table and the step's own key/value row
   size_t smem = 2 * NSTAGE * (size_t)TILE_BYTES + ROWS * ROW_BYTES + 8 * (size_t)HD;
   const size_t merge = (size_t)(WARPS * 8 * HD + WARPS * 8 * 2) * sizeof(float);
@@ -406,22 +458,25 @@ int launch_decode(const void* qkv, void* out, const IertBatchView* batch, const 
     }
     configured = true;
   }
-  launch_dep(attention_decode_tc_kernel, dim3(splits, cache->kv_heads * p.slices, T), dim3(THREADS), smem, stream,
+  launch_dep(attention_decode_tc_kernel, dim3(cache->kv_heads * p.slices, T, splits), dim3(THREADS), smem, stream,
              p, *batch, *cache);
   if (cudaGetLastError() != cudaSuccess) return IERT_CUDA_ERROR;
   if (splits == 1) return IERT_OK;                   // nothing to merge: the kernel wrote the output
-  launch_dep(attention_decode_tc_combine_kernel, dim3(T, heads), dim3(HD >= 128 ? 128 : 64), 0, stream, p);
+  launch_dep(attention_decode_tc_combine_kernel, dim3(T, heads), dim3(HD >= 128 ? 128 : 64), 0, stream, p, *batch, *cache);
   return cudaGetLastError() == cudaSuccess ? IERT_OK : IERT_CUDA_ERROR;
 }
 
 }  // namespace
 
+// `splits`: the most parts a sequence's keys are cut into; with target_ctas > 0 each sequence is cut
+// into as many of them as its length asks for (see balanced_parts), else every sequence into all.
 // Same contract as the core library's iert_attention_decode, for caches with head_dim ==
 // HEAD_DIM, bf16, 64-position pages.  Anything else: IERT_BAD_ARGUMENT, nothing launched.
 IERT_API int iert_attention_decode_tc(const void* qkv, void* out, const IertBatchView* batch,
                                       const IertKvView* cache, int heads, float scale, int splits,
-                                      float* scratch, int* err, cudaStream_t stream) {
-  return launch_decode(qkv, out, batch, cache, heads, scale, splits, scratch, nullptr, 0, 0, 0, 0, err, stream);
+                                      int target_ctas, float* scratch, int* err, cudaStream_t stream) {
+  return launch_decode(qkv, out, batch, cache, heads, scale, splits, target_ctas, scratch, nullptr, 0, 0, 0, 0, err,
+                       stream);
 }
 
 // The same with the rotary encoding and the cache write of the step inside the kernel: `qkv` is
@@ -430,9 +485,9 @@ IERT_API int iert_attention_decode_tc(const void* qkv, void* out, const IertBatc
 // dimensions of a head); with store != 0 the new key and value are written to the cache.
 IERT_API int iert_attention_decode_tc_rope(const void* qkv, void* out, const IertBatchView* batch,
                                            const IertKvView* cache, int heads, float scale, int splits,
-                                           float* scratch, const float* inv_freq, int rotary_dim, int pairing,
-                                           int store, int* err, cudaStream_t stream) {
+                                           int target_ctas, float* scratch, const float* inv_freq, int rotary_dim,
+                                           int pairing, int store, int* err, cudaStream_t stream) {
   if (batch->n_tokens != batch->n_seqs) return IERT_BAD_ARGUMENT;     // one token per sequence
-  return launch_decode(qkv, out, batch, cache, heads, scale, splits, scratch, inv_freq, 1, rotary_dim, pairing,
-                       store, err, stream);
+  return launch_decode(qkv, out, batch, cache, heads, scale, splits, target_ctas, scratch, inv_freq, 1, rotary_dim,
+                       pairing, store, err, stream);
 }

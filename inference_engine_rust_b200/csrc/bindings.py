@@ -291,10 +291,10 @@ def _attention_lib(head_dim: int):
                                                c_float, c_int, c_void_p]
         lib.iert_attention_prefill.restype = c_int
         lib.iert_attention_decode_tc.argtypes = [c_void_p, c_void_p, POINTER(BatchView), POINTER(KvView), c_int,
-                                                 c_float, c_int, c_void_p, c_void_p, c_void_p]
+                                                 c_float, c_int, c_int, c_void_p, c_void_p, c_void_p]
         lib.iert_attention_decode_tc.restype = c_int
         lib.iert_attention_decode_tc_rope.argtypes = [c_void_p, c_void_p, POINTER(BatchView), POINTER(KvView), c_int,
-                                                      c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
+                                                      c_float, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
                                                       c_void_p, c_void_p]
         lib.iert_attention_decode_tc_rope.restype = c_int
         lib.iert_attention_prefill_tc.argtypes = [c_void_p, c_void_p, POINTER(BatchView), c_int, c_int, c_int,
@@ -337,15 +337,15 @@ def attention_prefill(qkv, out, batch: BatchView, heads: int, kv_heads: int, hea
 
 
 def attention_decode_tc(qkv, out, batch: BatchView, kv: KvView, heads: int, scale: float, splits: int,
-                        scratch, err, stream) -> bool:
+                        scratch, err, stream, target_ctas: int = 0) -> bool:
     """Tensor-core split-KV decode attention (bf16 cache, 64-position pages, head sizes that
     are multiples of 16 up to 256).  Returns False, having launched nothing, otherwise."""
     hd = kv.head_dim
     if hd % 16 or not 16 <= hd <= 256:
         return False
     status = _attention_lib(hd).iert_attention_decode_tc(qkv.data_ptr(), out.data_ptr(), byref(batch), byref(kv),
-                                                         heads, scale, splits, scratch.data_ptr(), err.data_ptr(),
-                                                         stream)
+                                                         heads, scale, splits, target_ctas, scratch.data_ptr(),
+                                                         err.data_ptr(), stream)
     if status == 1:
         return False
     if status != 0:
@@ -356,7 +356,8 @@ def attention_decode_tc(qkv, out, batch: BatchView, kv: KvView, heads: int, scal
 
 
 def attention_decode_tc_rope(qkv, out, batch: BatchView, kv: KvView, heads: int, scale: float, splits: int,
-                             scratch, inv_freq, rotary_dim: int, pairing: int, store: bool, err, stream) -> bool:
+                             scratch, inv_freq, rotary_dim: int, pairing: int, store: bool, err, stream,
+                             target_ctas: int = 0) -> bool:
     """`attention_decode_tc` with the rotary encoding and the step's cache write inside the
     kernel: `qkv` is the raw projection (one token per sequence) and stays as it is.  Returns
     False, having launched nothing, for anything the kernel does not take."""
@@ -364,7 +365,7 @@ def attention_decode_tc_rope(qkv, out, batch: BatchView, kv: KvView, heads: int,
     if hd % 16 or not 16 <= hd <= 256:
         return False
     status = _attention_lib(hd).iert_attention_decode_tc_rope(
-        qkv.data_ptr(), out.data_ptr(), byref(batch), byref(kv), heads, scale, splits, scratch.data_ptr(),
+        qkv.data_ptr(), out.data_ptr(), byref(batch), byref(kv), heads, scale, splits, target_ctas, scratch.data_ptr(),
         inv_freq.data_ptr(), rotary_dim, pairing, 1 if store else 0, err.data_ptr(), stream)
     if status == 1:
         return False

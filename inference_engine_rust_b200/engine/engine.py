@@ -65,7 +65,7 @@ class _DecodeGraph:
     """A captured one-token step for `nb` sequences: its own metadata buffer, workspace and
     logits buffer (a graph replays fixed addresses), and the graph."""
 
-    def __init__(self, engine: "Engine", nb: int):
+    def __init__(self, engine: "Engine", nb: int, unequal: bool = False):
         rt, model = engine.rt, engine.model
         from ..parts.base import Workspace
         _, o_slot, _, o_seq, o_tok, o_rows, total = Engine._layout(nb, nb, nb)
@@ -82,6 +82,7 @@ class _DecodeGraph:
         try:
             def run():
                 ctx = engine._context("decode", self.meta, nb, nb, [1] * nb, [0] * nb, [-1] * nb)
+                ctx.unequal_lengths = unequal
                 model.forward(ctx, self.meta[o_tok:o_tok + nb], engine.cache,
                               self.meta[o_rows:o_rows + nb], nb, logits_out=self.logits)
             run()                                      # eager once: lazy set-up happens outside the capture
@@ -267,6 +268,16 @@ class Engine:
                            slot_ids_dev=meta[o_slot:o_slot + n], pos0_dev=meta[o_pos:o_pos + n],
                            cu_q_dev=meta[o_cu:o_cu + n + 1])
 
+    @staticmethod
+    def _unequal(pos0) -> bool:
+        """Do the sequences of a one-token step differ so much in length that the longest should
+        be cut into more parts than the others?  (Pages of 64 positions; the longest holds over
+        1.3 times the average.)  Steps of either kind replay a graph of their own."""
+        if len(pos0) < 2:
+            return False
+        pages = [p // 64 + 1 for p in pos0]
+        return max(pages) * len(pages) > 1.3 * sum(pages)
+
     def _step_eager(self, kind, slots, q_lens, pos0, tokens, cu, rows):
         n, T, R = len(slots), int(cu[-1]), len(rows)
         o_cu, o_slot, o_pos, o_seq, o_tok, o_rows, total = self._layout(n, T, R)
@@ -285,6 +296,7 @@ class Engine:
         self._staging.sent(turn)
         self.h2d_bytes_last_step = total * 4
         ctx = self._context(kind, meta, n, T, q_lens, pos0, slots)
+        ctx.unequal_lengths = kind == "decode" and self._unequal(pos0)
         return self.model.forward(ctx, meta[o_tok:o_tok + T], self.cache,
                                   meta[o_rows:o_rows + R] if R else None, R)
 
@@ -297,9 +309,10 @@ class Engine:
         nb = 1
         while nb < n:
             nb *= 2
-        g = self._graphs.get(nb)
+        unequal = self._unequal(pos0)
+        g = self._graphs.get((nb, unequal))
         if g is None:
-            g = self._graphs[nb] = _DecodeGraph(self, nb)
+            g = self._graphs[(nb, unequal)] = _DecodeGraph(self, nb, unequal)
         o_cu, o_slot, o_pos, o_seq, o_tok, o_rows, total = self._layout(nb, nb, nb)
         host, turn = self._staging.next(total)
         h = host.numpy()

@@ -109,6 +109,8 @@ class StepContext:
     batch         csrc.bindings.BatchView (device arrays cu_q, slot_ids, tok_seq, pos0)
     n_tokens      packed tokens, padding included;  n_seqs likewise
     q_lens, pos0, slots   host copies (lists) for sizing launches and for host-side checks
+    unequal_lengths       a hint for one-token steps: the longest sequence holds well over the
+                          average, so work should be cut by length rather than evenly
     """
     kind: str
     batch: object
@@ -119,6 +121,7 @@ class StepContext:
     slots: list
     stream: int
     rt: Runtime
+    unequal_lengths: bool = False                  # one-token step whose sequences differ much in length
     slot_ids_dev: Optional[torch.Tensor] = None   # int32 [n_seqs] view, for parts written in Python
     pos0_dev: Optional[torch.Tensor] = None
     cu_q_dev: Optional[torch.Tensor] = None

@@ -20,6 +20,20 @@ def decode_splits(n_tokens: int, kv_heads: int, group: int) -> int:
     return max(1, min(_MAX_SPLITS, _CTAS_PER_SM * B.sm_count() // ctas))      # as many splits as stay one wave
 
 
+def decode_parts(n_tokens: int, kv_heads: int, group: int, unequal: bool):
+    """(most parts a sequence is cut into, CTAs to aim for) for the tensor-core decode kernel.  With
+    sequences of unequal lengths (the engine's hint) a long sequence is cut into more parts than a
+    short one, up to four times the even split, so that all CTAs hold about the same number of
+    pages: how many parts each sequence gets is worked out on the device from the lengths, which
+    costs a few microseconds that steps of equal lengths do not spend (target 0: every sequence
+    into all parts).  Both numbers depend on the (padded) batch size and the hint only."""
+    base = decode_splits(n_tokens, kv_heads, group)
+    if not unequal or base < 2 or os.environ.get("IERT_DECODE_BALANCE", "1") == "0":
+        return base, 0
+    ctas = max(1, n_tokens * kv_heads * -(-group // 8))
+    return min(_MAX_SPLITS, 4 * base), base * ctas
+
+
 def decode_with_rotation(attn, qkv, out, ctx, cache_view, writes_cache: bool) -> bool:
     """One-token step with the rotary encoding and the cache write inside the attention kernel.
     False (nothing launched) if the position encoding is no plain rotation or the kernel does
@@ -29,11 +43,12 @@ def decode_with_rotation(attn, qkv, out, ctx, cache_view, writes_cache: bool) ->
         return False
     inv_freq, rotary_dim, pairing = rot
     rt = attn.rt
-    splits = decode_splits(ctx.n_tokens, attn.kv_heads, attn.heads // attn.kv_heads)
-    n = B.attention_decode_scratch_floats(ctx.n_tokens, attn.heads, attn.head_dim, splits)
+    parts, target = decode_parts(ctx.n_tokens, attn.kv_heads, attn.heads // attn.kv_heads, ctx.unequal_lengths)
+    n = B.attention_decode_scratch_floats(ctx.n_tokens, attn.heads, attn.head_dim, parts)
     scratch = rt.workspace.take("attn.decode_scratch", (n,), torch.float32)
-    return B.attention_decode_tc_rope(qkv, out, ctx.batch, cache_view.struct, attn.heads, attn.scale, splits,
-                                      scratch, inv_freq, rotary_dim, pairing, writes_cache, rt.err, ctx.stream)
+    return B.attention_decode_tc_rope(qkv, out, ctx.batch, cache_view.struct, attn.heads, attn.scale, parts,
+                                      scratch, inv_freq, rotary_dim, pairing, writes_cache, rt.err, ctx.stream,
+                                      target_ctas=target)
 
 
 def apply(attn, qkv, out, ctx, cache_view, from_cache: bool) -> bool:
@@ -43,10 +58,11 @@ def apply(attn, qkv, out, ctx, cache_view, from_cache: bool) -> bool:
         return False
     if ctx.kind == "decode":
         splits = decode_splits(ctx.n_tokens, attn.kv_heads, attn.heads // attn.kv_heads)
-        n = B.attention_decode_scratch_floats(ctx.n_tokens, attn.heads, attn.head_dim, splits)
+        parts, target = decode_parts(ctx.n_tokens, attn.kv_heads, attn.heads // attn.kv_heads, ctx.unequal_lengths)
+        n = B.attention_decode_scratch_floats(ctx.n_tokens, attn.heads, attn.head_dim, max(parts, splits))
         scratch = rt.workspace.take("attn.decode_scratch", (n,), torch.float32)
-        if B.attention_decode_tc(qkv, out, ctx.batch, cache_view.struct, attn.heads, attn.scale, splits,
-                                 scratch, rt.err, ctx.stream):
+        if B.attention_decode_tc(qkv, out, ctx.batch, cache_view.struct, attn.heads, attn.scale, parts,
+                                 scratch, rt.err, ctx.stream, target_ctas=target):
             return True
         return B.attention_decode(qkv, out, ctx.batch, cache_view.struct, attn.heads, attn.scale, splits,
                                   scratch, rt.err, ctx.stream)
