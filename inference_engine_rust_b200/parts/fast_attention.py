@@ -28,9 +28,13 @@ def decode_parts(n_tokens: int, kv_heads: int, group: int, unequal: bool):
     costs a few microseconds that steps of equal lengths do not spend (target 0: every sequence
     into all parts).  Both numbers depend on the (padded) batch size and the hint only."""
     base = decode_splits(n_tokens, kv_heads, group)
-    if not unequal or base < 2 or os.environ.get("IERT_DECODE_BALANCE", "1") == "0":
+    if not unequal or os.environ.get("IERT_DECODE_BALANCE", "1") == "0":
         return base, 0
     ctas = max(1, n_tokens * kv_heads * -(-group // 8))
+    if base < 2:
+        # the batch alone fills the device: a sequence of average length stays whole, one that is
+        # k times longer is cut into k parts (at most 8), or its single CTA would end the step alone
+        return 8, ctas
     return min(_MAX_SPLITS, 4 * base), base * ctas
 
 
