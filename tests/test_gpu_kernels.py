@@ -312,6 +312,16 @@ def test_attention_decode_batch_with_padding(heads, kvh, hd, window):
         assert torch.isfinite(tc).all() and float(tc[3].abs().sum()) == 0
         assert torch.allclose(tc.float(), plain.float(), atol=2e-2, rtol=2e-2), \
             f"tensor cores, {splits} splits: {(tc.float() - plain.float()).abs().max().item():.4g}"
+        # cut by length: each sequence into as many of the `splits` parts as its share of the pages asks for
+        for target in (3, 40, 1000):
+            scratch.fill_(float("nan"))
+            bal = torch.full_like(plain, float("nan"))
+            assert b.attention_decode_tc(nxt, bal, view1, kvs, heads, scale, splits, scratch, err, stream(),
+                                         target_ctas=target)
+            assert err.item() == 0
+            assert torch.isfinite(bal).all() and float(bal[3].abs().sum()) == 0
+            assert torch.allclose(bal.float(), plain.float(), atol=2e-2, rtol=2e-2), \
+                f"cut by length, {splits} parts at most, {target} CTAs aimed for"
 
 
 @pytest.mark.parametrize("heads,kvh,hd,window,pairing,rotary", [
