@@ -143,7 +143,7 @@ attention_decode_tc_kernel(DecodeTcParams p, IertBatchView b, IertKvView c) {
   const int head0 = kvh * group + g0;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
 
-  const int s = b.tok_seq[t];
+  const int s = sequence_of_token(b, t);
   const int slot = s >= 0 ? b.slot_ids[s] : -1;
   float* po = p.part_out + (((size_t)t * p.heads + head0) * p.splits + split) * HD;
   float* pml = p.part_ml + (((size_t)t * p.heads + head0) * p.splits + split) * 2;
@@ -384,7 +384,7 @@ __global__ void attention_decode_tc_combine_kernel(DecodeTcParams p, IertBatchVi
   const int t = blockIdx.x, head = blockIdx.y;
   // how many parts this token's sequence was cut into (the attention kernel computed the same)
   int n_splits = p.splits;
-  const int s_ = b.tok_seq[t];
+  const int s_ = sequence_of_token(b, t);
   const bool live = s_ >= 0 && b.slot_ids[s_] >= 0;
   if (p.target_ctas > 0 && p.splits > 1 && live) {
     const int pos = b.pos0[s_] + (t - b.cu_q[s_]);

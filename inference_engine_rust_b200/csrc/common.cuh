@@ -134,6 +134,13 @@ __device__ __forceinline__ long long kv_row_offset(const IertKvView& c, int slot
   return (((long long)page * c.kv_heads + h) * c.page_tokens + row) * c.head_dim;
 }
 
+// The sequence token t belongs to (-1: padding).  A step with as many tokens as sequences is a
+// one-token step: every sequence brings exactly one token and token t is sequence t's, so the
+// look-up (one more dependent load at the head of a kernel) is skipped.
+__device__ __forceinline__ int sequence_of_token(const IertBatchView& b, int t) {
+  return b.n_tokens == b.n_seqs ? t : b.tok_seq[t];
+}
+
 // Programmatic dependent launch: a kernel launched with `launch_dep` may start while the
 // kernel before it in the stream is still running.  It must call pdl_wait() before it reads
 // anything an earlier kernel wrote and before it writes anything an earlier kernel may

@@ -217,7 +217,7 @@ __global__ void rope_kv_store_kernel(T* __restrict__ qkv, IertBatchView b, IertK
   // The step's description (sequence, slot, position) and the angles do not depend on the
   // kernel before this one, only the projection does: everything up to the first read of
   // `qkv` runs while that kernel finishes.
-  const int s = b.tok_seq[t];
+  const int s = sequence_of_token(b, t);
   const int slot = s < 0 ? -1 : b.slot_ids[s];
   if (slot < 0) return;
   const int q_begin = b.cu_q[s], q_len = b.cu_q[s + 1] - q_begin;
