@@ -858,7 +858,9 @@ IERT_API int iert_gemm_tc(const void* x, long long ldx, const void* w, long long
   int bt = force_bt;
   // up to 512 tokens 128-token tiles (twice as many of them) beat 256-token tiles with split-K:
   // 512-token prompt 9.7 -> 8.6 ms, 384 tokens 8.7 -> 7.8 ms; from 1,024 tokens on there is no difference
-  if (!bt) bt = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 512 ? 128 : 256;
+  // (65 to 128 tokens: two 64-token tiles, measured against one 128-token tile: QKV 20 -> 18 us,
+  // O 18 -> 16 us, and far better than the token-major kernel's 30 us for the store)
+  if (!bt) bt = M <= 16 ? 16 : M <= 32 ? 32 : M <= 256 ? 64 : M <= 512 ? 128 : 256;
   if (bt != 16 && bt != 32 && bt != 64 && bt != 128 && bt != 256) return IERT_BAD_ARGUMENT;
 
   GemmParams p;
@@ -866,7 +868,7 @@ IERT_API int iert_gemm_tc(const void* x, long long ldx, const void* w, long long
   p.out = out; p.ldo = ldo; p.out_dtype = out_dtype; p.mode = mode;
   p.M = M; p.N = N; p.K = K;
   p.ws = ws; p.counters = counters; p.err = err;
-  if (!force_bt && !force_splits && M >= 128 && (mode == MODE_STORE || force_stages == -1)) {
+  if (!force_bt && !force_splits && ((M > 256 && mode == MODE_STORE) || (M >= 128 && force_stages == -1))) {
     // many tokens, plain store: 128 tokens on the MMA's M side, 256 weight rows on its N side
     // (whole tiles).  Measured on 2,048 tokens: better than weight rows on M for stores (vector
     // stores of a token's row), not for the residual add, which stays on the other kernel.
@@ -910,7 +912,7 @@ IERT_API int iert_gemm_tc(const void* x, long long ldx, const void* w, long long
     // at 7B layer sizes: two per SM wins with 16-token tiles (partial tiles of 8 KB; two CTAs
     // hide each other's start-up), one per SM from 32 tokens on.
     const int one_per_sm = sm_count() / tiles, two_per_sm = slots / tiles;
-    const bool prefer_one = one_per_sm >= 1 && bt >= 32;
+    const bool prefer_one = one_per_sm >= 1 && bt >= 32 && p.t_tiles == 1;   // (two token tiles: two per SM again)
     splits = prefer_one ? one_per_sm : two_per_sm;
     const int max_by_k = p.kb_total / 4 > 0 ? p.kb_total / 4 : 1;     // at least 4 k-blocks per split
     if (splits > max_by_k) splits = max_by_k;
