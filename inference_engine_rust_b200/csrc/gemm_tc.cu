@@ -128,6 +128,53 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
   return __fdividef(g * u, 1.0f + __expf(-g));
 }
 
+// Split-K: rows t_first, t_first + 4, ... < t_end of a tile's partial products (one [BT][TILE_N]
+// fp32 block per split at `base`) added in split order and written out; 32 threads share a row, each
+// four columns (c4).  Four rows and four splits are in flight per thread and pass, and a residual is
+// read together with the first partials, so that a pass costs one round trip to the L2: with 64
+// rows per split a row-at-a-time loop spent 30 us here.
+template <int BT>
+__device__ __forceinline__ void reduce_partial_rows(const GemmParams& p, const float* base, int t_first, int t_end,
+                                                    int t0, int n, int c4) {
+  const bool vec_res = p.mode == MODE_ADD_RESIDUAL && p.out_dtype == IERT_F32 && n + 4 <= p.N && (p.ldo & 3) == 0 &&
+                       ((uintptr_t)p.out & 15) == 0;
+  for (int t = t_first; t < t_end; t += 16) {
+    float4 acc[4], res[4];
+#pragma unroll
+    for (int h = 0; h < 4; ++h) {
+      acc[h] = make_float4(0.f, 0.f, 0.f, 0.f);
+      res[h] = (vec_res && t + 4 * h < t_end)
+                   ? *reinterpret_cast<const float4*>((const float*)p.out + (long long)(t0 + t + 4 * h) * p.ldo + n)
+                   : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    for (int s0 = 0; s0 < p.splits; s0 += 4) {
+      float4 v[4][4];
+#pragma unroll
+      for (int h = 0; h < 4; ++h)
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          v[h][u] = (s0 + u < p.splits && t + 4 * h < t_end)
+                        ? __ldcg(reinterpret_cast<const float4*>(base + ((size_t)(s0 + u) * BT + t + 4 * h) * TILE_N) + c4)
+                        : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int h = 0; h < 4; ++h)
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          acc[h].x += v[h][u].x; acc[h].y += v[h][u].y; acc[h].z += v[h][u].z; acc[h].w += v[h][u].w;
+        }
+    }
+#pragma unroll
+    for (int h = 0; h < 4; ++h) {
+      if (t + 4 * h >= t_end) break;
+      if (vec_res)
+        *reinterpret_cast<float4*>((float*)p.out + (long long)(t0 + t + 4 * h) * p.ldo + n) =
+            make_float4(res[h].x + acc[h].x, res[h].y + acc[h].y, res[h].z + acc[h].z, res[h].w + acc[h].w);
+      else
+        write_out4(p, t0 + t + 4 * h, n, acc[h]);
+    }
+  }
+}
+
 // A CTA's list of work, the same for its three roles: items (tile, part of k) strided over the
 // grid.  Usually every tile has the same number of parts (p.splits, split-K).  For residual adds
 // over many tokens whose tiles leave the last wave part empty (p.tail_parts > 1, one CTA per SM,
@@ -183,7 +230,7 @@ struct WorkIter {
 };
 
 template <int BT, bool GATED>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(THREADS, 2)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                const __grid_constant__ CUtensorMap map_o, const GemmParams p) {
   constexpr int NW = GATED ? 2 : 1;                             // weight tiles per stage
@@ -568,6 +615,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           if (*ticket_s) {
             const int rows_per = (t_valid + p.splits - 1) / p.splits;
             const int r0 = split * rows_per, r1 = min(t_valid, r0 + rows_per);
+            if constexpr (BT > 32) {
+              reduce_partial_rows<BT>(p, base, r0 + tr, r1, t0, n0 + c4 * 4, c4);
+            } else
             for (int t = r0 + tr; t < r1; t += 4) {        // a token row per 32 threads, 8 splits in flight
               float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
               for (int s0 = 0; s0 < p.splits; s0 += 8) {
@@ -591,34 +641,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           asm volatile("bar.sync 1, 128;" ::: "memory");
           if (*ticket_s == p.splits - 1) {             // the last split of this tile: add in split order
             __threadfence();
-            // 128 threads: 32 four-column chunks x 4 token rows per pass; all loads of a pass are
-            // issued before any is used, so a pass costs one round trip to L2
-            for (int t = tr; t < t_valid; t += 16) {      // 4 token rows x 4 splits = 16 loads in flight
-              float4 acc[4];
-#pragma unroll
-              for (int h = 0; h < 4; ++h) acc[h] = make_float4(0.f, 0.f, 0.f, 0.f);
-              for (int s0 = 0; s0 < p.splits; s0 += 4) {
-                float4 v[4][4];
-#pragma unroll
-                for (int h = 0; h < 4; ++h)
-#pragma unroll
-                  for (int u = 0; u < 4; ++u)
-                    v[h][u] = (s0 + u < p.splits && t + 4 * h < t_valid)
-                                  ? __ldcg(reinterpret_cast<const float4*>(base + ((size_t)(s0 + u) * BT + t + 4 * h) * TILE_N) + c4)
-                                  : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-                for (int h = 0; h < 4; ++h)
-#pragma unroll
-                  for (int u = 0; u < 4; ++u) {
-                    acc[h].x += v[h][u].x; acc[h].y += v[h][u].y; acc[h].z += v[h][u].z; acc[h].w += v[h][u].w;
-                  }
-              }
-#pragma unroll
-              for (int h = 0; h < 4; ++h) {
-                if (t + 4 * h >= t_valid) break;
-                write_out4(p, t0 + t + 4 * h, n0 + c4 * 4, acc[h]);
-              }
-            }
+            reduce_partial_rows<BT>(p, base, tr, t_valid, t0, n0 + c4 * 4, c4);
             if (threadIdx.x == 64) p.counters[tile] = 0;
           }
         }
@@ -858,9 +881,12 @@ IERT_API int iert_gemm_tc(const void* x, long long ldx, const void* w, long long
   int bt = force_bt;
   // up to 512 tokens 128-token tiles (twice as many of them) beat 256-token tiles with split-K:
   // 512-token prompt 9.7 -> 8.6 ms, 384 tokens 8.7 -> 7.8 ms; from 1,024 tokens on there is no difference
-  // (65 to 128 tokens: two 64-token tiles, measured against one 128-token tile: QKV 20 -> 18 us,
-  // O 18 -> 16 us, and far better than the token-major kernel's 30 us for the store)
-  if (!bt) bt = M <= 16 ? 16 : M <= 32 ? 32 : M <= 256 ? 64 : M <= 512 ? 128 : 256;
+  // Token tile.  65 to 128 tokens: two 64-token tiles (against one 128-token tile: QKV 20 -> 18 us,
+  // O 18 -> 16 us; the token-major kernel takes 30 us for the same store).  More tokens: 256-token
+  // tiles, split over k while the tiles alone leave SMs empty (256 tokens, K of 14,336: 39 us
+  // against 47 us with 64-token tiles); 128-token tiles only where a 256-token tile would be
+  // more than half padding.
+  if (!bt) bt = M <= 16 ? 16 : M <= 32 ? 32 : M <= 128 ? 64 : (M > 256 && M <= 384) ? 128 : 256;
   if (bt != 16 && bt != 32 && bt != 64 && bt != 128 && bt != 256) return IERT_BAD_ARGUMENT;
 
   GemmParams p;

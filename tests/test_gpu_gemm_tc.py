@@ -60,6 +60,22 @@ def test_split_k_is_exact_and_repeatable(splits):
     run(3, 4096, 1024, B.GEMM_STORE, torch.bfloat16, force_splits=splits)      # more work items than CTAs
 
 
+@pytest.mark.parametrize("bt", [64, 128, 256])
+@pytest.mark.parametrize("splits", [2, 4, 7])
+def test_split_k_with_wide_token_tiles(bt, splits):
+    """Many tokens per tile and k in parts: every split adds its share of the tile's rows (four
+    rows and four splits per pass), the residual is read with the partials; a ragged last tile,
+    a width that is no multiple of 128, a K that is no multiple of 64, and a grid with more work
+    items than resident CTAs, where the last split to finish adds the whole tile."""
+    from inference_engine_rust_b200.csrc import bindings as B
+    a = run(bt + 3, 1000, 1096, B.GEMM_ADD_RESIDUAL, torch.float32, force_bt=bt, force_splits=splits)
+    b = run(bt + 3, 1000, 1096, B.GEMM_ADD_RESIDUAL, torch.float32, force_bt=bt, force_splits=splits)
+    assert torch.equal(a, b), "the partials must be added in a fixed order"
+    run(2 * bt, 392, 1024, B.GEMM_STORE, torch.bfloat16, force_bt=bt, force_splits=splits)
+    run(bt - 5, 392, 520, B.GEMM_STORE, torch.float32, force_bt=bt, force_splits=splits)
+    run(bt, 128 * 50, 512, B.GEMM_ADD_RESIDUAL, torch.float32, force_bt=bt, force_splits=splits)
+
+
 def test_short_pipelines_wrap():
     from inference_engine_rust_b200.csrc import bindings as B
     run(24, 300, 4096, B.GEMM_STORE, torch.float32, force_stages=2)
