@@ -615,7 +615,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           if (*ticket_s) {
             const int rows_per = (t_valid + p.splits - 1) / p.splits;
             const int r0 = split * rows_per, r1 = min(t_valid, r0 + rows_per);
-            if constexpr (BT > 32) {
+            if constexpr (BT > 16) {
               reduce_partial_rows<BT>(p, base, r0 + tr, r1, t0, n0 + c4 * 4, c4);
             } else
             for (int t = r0 + tr; t < r1; t += 4) {        // a token row per 32 threads, 8 splits in flight
@@ -933,16 +933,14 @@ IERT_API int iert_gemm_tc(const void* x, long long ldx, const void* w, long long
   if (force_splits) {
     splits = force_splits;
   } else if (tiles * 2 <= slots) {
-    // Either one CTA per SM with a ring as deep as shared memory allows, or two per SM with
-    // half the ring each and twice the partial tiles to add.  Measured in whole decoding steps
-    // at 7B layer sizes: two per SM wins with 16-token tiles (partial tiles of 8 KB; two CTAs
-    // hide each other's start-up), one per SM from 32 tokens on.
-    const int one_per_sm = sm_count() / tiles, two_per_sm = slots / tiles;
-    const bool prefer_one = one_per_sm >= 1 && bt >= 32 && p.t_tiles == 1;   // (two token tiles: two per SM again)
-    splits = prefer_one ? one_per_sm : two_per_sm;
+    // As many splits as fill the CTA slots (two CTAs per SM up to 64-token tiles: they hide each
+    // other's start-up and epilogue).  Measured in whole decoding steps at 7B layer sizes against
+    // one CTA per SM with a ring as deep as shared memory allows: equal at batch 64, 2 % faster
+    // at batch 32, 5 % at batch 8.
+    splits = slots / tiles;
     const int max_by_k = p.kb_total / 4 > 0 ? p.kb_total / 4 : 1;     // at least 4 k-blocks per split
     if (splits > max_by_k) splits = max_by_k;
-    const int cap = bt >= 64 ? 4 : bt == 32 ? 8 : 16;   // partial tiles grow with the token tile
+    const int cap = bt >= 32 ? 8 : 16;                  // partial tiles grow with the token tile
     if (splits > cap) splits = cap;
   }
   if (splits < 1) splits = 1;
