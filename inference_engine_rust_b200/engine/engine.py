@@ -268,15 +268,10 @@ class Engine:
                            slot_ids_dev=meta[o_slot:o_slot + n], pos0_dev=meta[o_pos:o_pos + n],
                            cu_q_dev=meta[o_cu:o_cu + n + 1])
 
-    @staticmethod
-    def _unequal(pos0) -> bool:
-        """Do the sequences of a one-token step differ so much in length that the longest should
-        be cut into more parts than the others?  (Pages of 64 positions; the longest holds over
-        1.3 times the average.)  Steps of either kind replay a graph of their own."""
-        if len(pos0) < 2:
-            return False
-        pages = [p // 64 + 1 for p in pos0]
-        return max(pages) * len(pages) > 1.3 * sum(pages)
+    def _unequal(self, pos0) -> bool:
+        """Do the mixers want this one-token step cut by the sequences' lengths?  Steps of either
+        kind replay a graph of their own."""
+        return len(pos0) >= 2 and self.model.cut_by_length(pos0)
 
     def _step_eager(self, kind, slots, q_lens, pos0, tokens, cu, rows):
         n, T, R = len(slots), int(cu[-1]), len(rows)

@@ -123,6 +123,11 @@ class Model:
         return total
 
     # ---- forward --------------------------------------------------------------------------
+    def cut_by_length(self, pos0) -> bool:
+        """Does any mixer want this one-token step (positions of the live sequences) cut by length?"""
+        asks = (getattr(parts[1], "cut_by_length", None) for parts in self._layer_parts)     # optional for a mixer
+        return any(ask(pos0) for ask in asks if ask is not None)
+
     def forward(self, ctx: StepContext, tokens: torch.Tensor, cache, logit_rows: Optional[torch.Tensor],
                 n_logit_rows: int, logits_out: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """Run the step's tokens through the scheduled layers.

@@ -72,6 +72,12 @@ class Attention(Mixer):
     def weight_bytes(self) -> int:
         return self.qkv.nbytes() + self.o.nbytes()
 
+    def cut_by_length(self, pos0) -> bool:
+        if not self.rt.fast:
+            return False
+        from . import fast_attention
+        return fast_attention.wants_length_cut(pos0, self.kv_heads, self.heads // self.kv_heads, self.window)
+
     def forward(self, xn, residual, ctx: StepContext, cache_view, writes_cache: bool) -> None:
         rt, ws, T = self.rt, self.rt.workspace, ctx.n_tokens
         kv = cache_view.struct

@@ -109,8 +109,8 @@ class StepContext:
     batch         csrc.bindings.BatchView (device arrays cu_q, slot_ids, tok_seq, pos0)
     n_tokens      packed tokens, padding included;  n_seqs likewise
     q_lens, pos0, slots   host copies (lists) for sizing launches and for host-side checks
-    unequal_lengths       a hint for one-token steps: the longest sequence holds well over the
-                          average, so work should be cut by length rather than evenly
+    unequal_lengths       one-token steps: a mixer asked for its work to be cut by the sequences'
+                          lengths rather than evenly (`Mixer.cut_by_length`)
     """
     kind: str
     batch: object
@@ -121,7 +121,7 @@ class StepContext:
     slots: list
     stream: int
     rt: Runtime
-    unequal_lengths: bool = False                  # one-token step whose sequences differ much in length
+    unequal_lengths: bool = False                  # one-token step whose mixers want a cut by length
     slot_ids_dev: Optional[torch.Tensor] = None   # int32 [n_seqs] view, for parts written in Python
     pos0_dev: Optional[torch.Tensor] = None
     cu_q_dev: Optional[torch.Tensor] = None
@@ -168,6 +168,13 @@ class PositionEncoding(Part):
 class Mixer(Part):
     def cache_request(self) -> CacheRequest:
         return None
+
+    def cut_by_length(self, pos0) -> bool:
+        """Asked once per one-token step with the positions of the live sequences: would this
+        mixer rather cut its work by the sequences' lengths than evenly?  The engine replays a
+        captured step of its own for either answer and passes the answer on as
+        `StepContext.unequal_lengths`.  The default is no."""
+        return False
 
     def forward(self, xn, residual, ctx: StepContext, cache_view, writes_cache: bool) -> None:
         raise NotImplementedError

@@ -539,3 +539,21 @@ def test_routed_feed_forward_and_another_position_encoding():
         unregister_part("ffn", "top_one_experts")
         unregister_part("position", "learned_offsets")
         registry._ARCHITECTURES.pop("RoutedToyForCausalLM", None)
+
+
+def test_attention_asks_for_a_cut_by_length_when_it_pays():
+    """The mixer's answer to the engine's question before a one-token step: sequences of equal
+    lengths keep the even cut unless the batch's CTAs leave the last round of slots mostly empty;
+    one long sequence among short ones asks for the cut by length; a mixer without the method is
+    not asked (the toy mixers above have none)."""
+    from inference_engine_rust_b200.parts import fast_attention as FA
+    from inference_engine_rust_b200.csrc import bindings as B
+    slots = 2 * B.sm_count()
+    assert not FA.wants_length_cut([2047] * 8, 8, 4, None)
+    assert not FA.wants_length_cut([2047], 8, 4, None)
+    assert FA.wants_length_cut([8191] + [1023] * 7, 8, 4, None)
+    assert not FA.wants_length_cut([8191] + [1023] * 7, 8, 4, 1024), "a window makes them equal"
+    full = slots // 8                                   # sequences whose CTAs fill the slots exactly
+    assert not FA.wants_length_cut([2047] * full, 8, 4, None)
+    assert FA.wants_length_cut([2047] * (full + full // 3), 8, 4, None), "one and a third rounds"
+    assert not FA.wants_length_cut([2047] * (2 * full - 2), 8, 4, None), "almost two full rounds"
