@@ -85,6 +85,8 @@ class KVGroup:
     def ensure(self, slot: int, length: int) -> None:
         """Pages for positions [0, length) of `slot` (or for the ring, if shorter)."""
         have = self._pages_of[slot]
+        if length <= len(have) * self.page_tokens or len(have) >= self.ring_pages > 0:
+            return                      # the usual case of a one-token step: the last page has room
         need = self.pages_needed(length)
         if need > self.table_width:
             raise CacheFull(f"sequence of {length} tokens exceeds the cache's longest sequence "

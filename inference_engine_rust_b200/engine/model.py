@@ -26,6 +26,7 @@ class Model:
         self.rt = rt
         self.blocks = []
         self._layer_parts = []       # (norm1, mixer, norm2, ffn) per layer
+        self._cut_askers = None
         h = spec.hidden_size
         for ls in spec.layers:
             norm_cls = part_class("norm", ls.norm.kind)
@@ -125,8 +126,19 @@ class Model:
     # ---- forward --------------------------------------------------------------------------
     def cut_by_length(self, pos0) -> bool:
         """Does any mixer want this one-token step (positions of the live sequences) cut by length?"""
-        asks = (getattr(parts[1], "cut_by_length", None) for parts in self._layer_parts)     # optional for a mixer
-        return any(ask(pos0) for ask in asks if ask is not None)
+        if self._cut_askers is None:
+            # every mixer that has the (optional) method, one per `cut_by_length_key()` where mixers
+            # say that their answers are the same (layers of equal shape): asked every step
+            seen, self._cut_askers = set(), []
+            for parts in self._layer_parts:
+                ask = getattr(parts[1], "cut_by_length", None)
+                if ask is None:
+                    continue
+                key = getattr(parts[1], "cut_by_length_key", lambda m=parts[1]: id(m))()
+                if key not in seen:
+                    seen.add(key)
+                    self._cut_askers.append(ask)
+        return any(ask(pos0) for ask in self._cut_askers)
 
     def forward(self, ctx: StepContext, tokens: torch.Tensor, cache, logit_rows: Optional[torch.Tensor],
                 n_logit_rows: int, logits_out: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:

@@ -72,6 +72,9 @@ class Attention(Mixer):
     def weight_bytes(self) -> int:
         return self.qkv.nbytes() + self.o.nbytes()
 
+    def cut_by_length_key(self):
+        return ("attention", self.heads, self.kv_heads, self.window, self.rt.fast)
+
     def cut_by_length(self, pos0) -> bool:
         if not self.rt.fast:
             return False

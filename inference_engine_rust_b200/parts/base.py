@@ -173,7 +173,9 @@ class Mixer(Part):
         """Asked once per one-token step with the positions of the live sequences: would this
         mixer rather cut its work by the sequences' lengths than evenly?  The engine replays a
         captured step of its own for either answer and passes the answer on as
-        `StepContext.unequal_lengths`.  The default is no."""
+        `StepContext.unequal_lengths`.  The default is no.  Mixers whose answers are always the
+        same (layers of one shape) may say so with an equal `cut_by_length_key()`; one of them
+        is asked then."""
         return False
 
     def forward(self, xn, residual, ctx: StepContext, cache_view, writes_cache: bool) -> None:

@@ -27,18 +27,22 @@ def wants_length_cut(pos0, kv_heads: int, group: int, window) -> bool:
     fills the device and a cut by length is predicted to take at least 15 % fewer page loads
     in a row: 48 sequences of 33 pages with 8 kv heads are 384 CTAs on 296 slots, two rounds
     of 33 pages; cut in two they are 768 CTAs, three rounds of 17."""
-    pages = [p // 64 + 1 - (max(0, p + 1 - window) // 64 if window else 0) for p in pos0]
-    n = len(pages)
+    n = len(pos0)
     if n < 2:
         return False
-    if max(pages) * n > 1.3 * sum(pages):
+    if window:
+        pages = [p // 64 + 1 - max(0, p + 1 - window) // 64 for p in pos0]
+    else:
+        pages = [p // 64 + 1 for p in pos0]
+    longest, total = max(pages), sum(pages)
+    if longest * n > 1.3 * total:
         return True
     per_sequence = kv_heads * -(-group // 8)
     slots = _CTAS_PER_SM * B.sm_count()
     if n * per_sequence <= slots:
         return False
-    even = -(-n * per_sequence // slots) * max(pages)
-    per_part = max(1, -(-sum(pages) * per_sequence // (2 * slots)))          # as the kernel works it out
+    even = -(-n * per_sequence // slots) * longest
+    per_part = max(1, -(-total * per_sequence // (2 * slots)))                 # as the kernel works it out
     parts = [min(8, -(-p // per_part)) for p in pages]
     cut = -(-sum(parts) * per_sequence // slots) * max(-(-p // k) for p, k in zip(pages, parts))
     return even >= 1.15 * cut
