@@ -23,6 +23,10 @@
 // Visible keys: [max(0, pos + 1 - W), pos] (src/layers/attention.rs:609-613); scale from the
 // caller; softmax in fp32 (src/ops/softmax.rs:11-25).
 #include "common.cuh"
+#include "sm100.cuh"
+#include "tma_host.cuh"
+
+#include <cstdlib>
 
 #ifndef HEAD_DIM
 #error "compile with -DHEAD_DIM=<multiple of 16>"
@@ -377,6 +381,303 @@ attention_decode_tc_kernel(DecodeTcParams p, IertBatchView b, IertKvView c) {
   }
 }
 
+#if HEAD_DIM % 64 == 0
+// ---------------------------------------------------------------------------------------------
+// The same kernel with the pages brought in by TMA (head sizes that are multiples of 64).  A
+// fifth warp is the producer: one thread waits for a ring slot to be empty, arms its barrier and
+// asks for the page's keys and values as boxes of 64 positions x 64 dimensions, written to shared
+// memory with the 128-byte swizzle (no padding: ldmatrix is conflict-free through the swizzle).
+// The four consumer warps wait for a slot's barrier, each uses its own 16 positions of the page
+// and arrives on the slot's "empty" barrier: no block-wide barrier inside the loop over pages,
+// and no load instructions in the warps that compute.  TMA brings whole pages, so positions
+// outside [j_min, pos] hold whatever the page held before: their scores are masked as before
+// (a select, so not even NaN gets through), and each warp zeroes its own rows of the values
+// that are out of range before it multiplies by them (0 x NaN would be NaN).  Every wait on a
+// barrier is bounded; when one runs out the kernel records it and goes on to its end.
+constexpr int TMA_THREADS = THREADS + 32;
+constexpr int BOX_BYTES = PAGE * 128;                   // 64 positions x 64 dimensions of bf16
+constexpr int BOXES = HD / 64;
+constexpr int TMA_TILE_BYTES = BOXES * BOX_BYTES;       // one page's keys (or values) of one kv head
+
+// Address of the 16-byte chunk holding dimensions [col, col + 8) of position `row` in a swizzled tile.
+__device__ __forceinline__ uint8_t* swz(uint8_t* tile, int row, int col) {
+  return tile + (col >> 6) * BOX_BYTES + row * 128 + ((((col & 63) >> 3) ^ (row & 7)) << 4);
+}
+
+__global__ void __launch_bounds__(TMA_THREADS)
+attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                            DecodeTcParams p, IertBatchView b, IertKvView c) {
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  __shared__ int red[8];
+  __shared__ __align__(8) uint64_t full_bar[NSTAGE], empty_bar[NSTAGE];
+  // the swizzle pattern repeats every 1,024 bytes of shared memory: the ring starts on such a boundary
+  uint8_t* smem = smem_raw + ((1024u - (sm100::smem_addr(smem_raw) & 1023u)) & 1023u);
+  auto k_tile = [&](int i) { return smem + (size_t)(2 * i) * TMA_TILE_BYTES; };
+  auto v_tile = [&](int i) { return smem + (size_t)(2 * i + 1) * TMA_TILE_BYTES; };
+  uint8_t* q_tile = smem + 2 * NSTAGE * TMA_TILE_BYTES;                     // [16][ROW_BYTES]
+  float* cs_tab = reinterpret_cast<float*>(q_tile + ROWS * ROW_BYTES);
+  __nv_bfloat16* new_kv = reinterpret_cast<__nv_bfloat16*>(cs_tab + HD);
+
+  pdl_launch_dependents();
+  const int split = blockIdx.z, t = blockIdx.y;
+  const int kvh = blockIdx.x / p.slices, slice = blockIdx.x % p.slices;
+  const int group = p.heads / c.kv_heads;
+  const int g0 = slice * p.gt;
+  const int n_g = min(p.gt, group - g0);
+  const int head0 = kvh * group + g0;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
+  const bool consumer = warp < WARPS;
+  auto consumer_sync = [&]() { asm volatile("bar.sync 1, %0;" ::"n"(THREADS) : "memory"); };
+
+  const int s = sequence_of_token(b, t);
+  const int slot = s >= 0 ? b.slot_ids[s] : -1;
+  float* po = p.part_out + (((size_t)t * p.heads + head0) * p.splits + split) * HD;
+  float* pml = p.part_ml + (((size_t)t * p.heads + head0) * p.splits + split) * 2;
+  if (slot < 0) {
+    pdl_wait();
+    if (p.splits == 1) {
+      for (int i = threadIdx.x; i < n_g * HD; i += TMA_THREADS)
+        p.out[((size_t)t * p.heads + head0) * HD + i] = __float2bfloat16_rn(0.f);
+    } else if (threadIdx.x < n_g) {
+      pml[(size_t)threadIdx.x * p.splits * 2] = -INFINITY; pml[(size_t)threadIdx.x * p.splits * 2 + 1] = 0.f;
+    }
+    return;
+  }
+  const int pos = b.pos0[s] + (t - b.cu_q[s]);
+  const int j_min = c.window > 0 ? max(0, pos + 1 - c.window) : 0;
+  const int pg_lo = j_min / PAGE, pg_hi = pos / PAGE + 1;
+  int n_splits = p.splits;
+  if (p.target_ctas > 0 && p.splits > 1) {
+    n_splits = balanced_parts(b, c, pg_hi - pg_lo, p.splits, p.target_ctas, gridDim.x, red);
+    if (split >= n_splits) return;
+  }
+  const int per = (pg_hi - pg_lo + n_splits - 1) / n_splits;
+  const int my_lo = pg_lo + split * per, my_hi = min(pg_hi, my_lo + per);
+  const bool fused = p.rope && p.store;
+  const bool own_new_row = fused && my_lo < my_hi && my_hi == pg_hi;
+  const int half = p.rotary_dim / 2;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < NSTAGE; ++i) { sm100::mbar_init(&full_bar[i], 1); sm100::mbar_init(&empty_bar[i], WARPS); }
+    sm100::mbar_fence_init();
+  }
+  __syncthreads();
+
+  if (!consumer) {
+    // ---- the producer: page numbers of up to 32 pages at a time, one per lane, then one thread
+    // arms the barrier and asks for the boxes
+    if (lane == 0) { sm100::tma_prefetch_desc(&map_k); sm100::tma_prefetch_desc(&map_v); }
+    bool waited = false;
+    for (int base = my_lo; base < my_hi; base += 32) {
+      const int mine = base + lane;
+      int page = -1;
+      if (mine < my_hi) page = c.page_table[(size_t)slot * c.table_width + mine % c.ring_pages];
+      for (int k = 0; k < 32 && base + k < my_hi; ++k) {
+        const int pg = base + k, i = pg - my_lo, buf = i % NSTAGE;
+        const int pgid = __shfl_sync(0xffffffffu, page, k);
+        const bool ok = pgid >= 0 && pgid < c.n_pages;
+        if (lane != 0) continue;
+        if (!ok) atomicOr(p.err, IERT_ERR_PAGE_RANGE);
+        // without the fused cache write the kernel in front wrote the newest row: wait for it first
+        if (!fused && !waited && pg == pos / PAGE) { pdl_wait(); waited = true; }
+        if (i >= NSTAGE && !sm100::mbar_wait(&empty_bar[buf], ((i / NSTAGE) - 1) & 1)) {
+          atomicOr(p.err, IERT_ERR_WAIT_EXPIRED);
+        }
+        sm100::mbar_expect_tx(&full_bar[buf], 2 * TMA_TILE_BYTES);
+        const int row0 = ((ok ? pgid : 0) * c.kv_heads + kvh) * PAGE;
+#pragma unroll
+        for (int bx = 0; bx < BOXES; ++bx) {
+          sm100::tma_load_2d(k_tile(buf) + bx * BOX_BYTES, &map_k, &full_bar[buf], bx * 64, row0);
+          sm100::tma_load_2d(v_tile(buf) + bx * BOX_BYTES, &map_v, &full_bar[buf], bx * 64, row0);
+        }
+      }
+    }
+    return;
+  }
+
+  // ---- consumers
+  if (p.rope) {
+    for (int k = threadIdx.x; k < half; k += THREADS) {
+      float sn, cs_;
+      sincosf((float)pos * p.inv_freq[k], &sn, &cs_);
+      cs_tab[k] = cs_;
+      cs_tab[half + k] = sn;
+    }
+  }
+  const __nv_bfloat16* tok_row = p.qkv + (size_t)t * ((size_t)(p.heads + 2 * c.kv_heads) * HD);
+  auto rotate_into = [&](const __nv_bfloat16* src, __nv_bfloat16* dst, int k) {
+    const int i0 = p.pairing == IERT_PAIR_HALF ? k : 2 * k;
+    const int i1 = p.pairing == IERT_PAIR_HALF ? k + half : 2 * k + 1;
+    const float a = __bfloat162float(src[i0]), bb = __bfloat162float(src[i1]);
+    dst[i0] = __float2bfloat16_rn(a * cs_tab[k] - bb * cs_tab[half + k]);
+    dst[i1] = __float2bfloat16_rn(a * cs_tab[half + k] + bb * cs_tab[k]);
+  };
+  pdl_wait();
+  {
+    const __nv_bfloat16* q = tok_row + (size_t)head0 * HD;
+    if (p.rope) {
+      consumer_sync();                                   // the angle table is complete
+      for (int i = threadIdx.x; i < ROWS * (HD / 2); i += THREADS) {
+        const int r = i / (HD / 2), k = i % (HD / 2);
+        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(q_tile + r * ROW_BYTES);
+        if (r >= n_g) { dst[2 * k] = __float2bfloat16_rn(0.f); dst[2 * k + 1] = __float2bfloat16_rn(0.f); }
+        else if (k < half) rotate_into(q + r * HD, dst, k);
+        else { const int d = p.rotary_dim + 2 * (k - half); dst[d] = q[r * HD + d]; dst[d + 1] = q[r * HD + d + 1]; }
+      }
+    } else {
+      constexpr int CHUNKS = HD / 8;
+      for (int i = threadIdx.x; i < ROWS * CHUNKS; i += THREADS) {
+        const int r = i / CHUNKS, cc = i % CHUNKS;
+        const uint4 val = r < n_g ? *reinterpret_cast<const uint4*>(q + r * HD + cc * 8) : make_uint4(0u, 0u, 0u, 0u);
+        *reinterpret_cast<uint4*>(q_tile + r * ROW_BYTES + cc * 16) = val;
+      }
+    }
+  }
+  if (own_new_row) {
+    const __nv_bfloat16* kn = tok_row + (size_t)(p.heads + kvh) * HD;
+    const __nv_bfloat16* vn = tok_row + (size_t)(p.heads + c.kv_heads + kvh) * HD;
+    for (int k = threadIdx.x; k < HD / 2; k += THREADS) {
+      if (k < half) rotate_into(kn, new_kv, k);
+      else { const int d = p.rotary_dim + 2 * (k - half); new_kv[d] = kn[d]; new_kv[d + 1] = kn[d + 1]; }
+      new_kv[HD + 2 * k] = vn[2 * k];
+      new_kv[HD + 2 * k + 1] = vn[2 * k + 1];
+    }
+  }
+  consumer_sync();
+  if (own_new_row && slice == 0) {
+    const int page = c.page_table[(size_t)slot * c.table_width + (pos / PAGE) % c.ring_pages];
+    if (page >= 0 && page < c.n_pages) {
+      const size_t off = ((((size_t)page * c.kv_heads + kvh) * PAGE) + pos % PAGE) * HD;
+      for (int d = threadIdx.x; d < HD; d += THREADS) {
+        ((__nv_bfloat16*)c.k)[off + d] = new_kv[d];
+        ((__nv_bfloat16*)c.v)[off + d] = new_kv[HD + d];
+      }
+    } else if (threadIdx.x == 0) {
+      atomicOr(p.err, IERT_ERR_PAGE_RANGE);
+    }
+  }
+  uint32_t qf[KSTEPS][4];
+#pragma unroll
+  for (int ks = 0; ks < KSTEPS; ++ks)
+    ldsm4(qf[ks], q_tile + (lane & 15) * ROW_BYTES + (ks * 16 + (lane >> 4) * 8) * 2);
+  float o[KSTEPS * 2][4];
+#pragma unroll
+  for (int n = 0; n < KSTEPS * 2; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  float m_row = -INFINITY, l_row = 0.f;
+
+  for (int pg = my_lo; pg < my_hi; ++pg) {
+    const int i = pg - my_lo, buf = i % NSTAGE;
+    if (!sm100::mbar_wait(&full_bar[buf], (i / NSTAGE) & 1)) {
+      if (lane == 0) atomicOr(p.err, IERT_ERR_WAIT_EXPIRED);
+      break;
+    }
+    // this warp's 16 positions of the page: rows [16 warp, 16 warp + 16)
+    const int row_lo = max(0, j_min - pg * PAGE);
+    int row_hi = min(PAGE - 1, pos - pg * PAGE);
+    const bool patch = own_new_row && pg == pos / PAGE;
+    if (patch) --row_hi;                                      // the newest row comes from the projection
+    const int w0 = warp * 16;
+    bool wrote = false;
+    if (row_lo > w0 || row_hi < w0 + 15) {                    // rows of the values that must not count
+      for (int r = w0; r < w0 + 16; ++r) {
+        if ((r >= row_lo && r <= row_hi) || (patch && r == pos % PAGE)) continue;      // (the patched row: below)
+#pragma unroll
+        for (int bx = 0; bx < BOXES; ++bx)
+          reinterpret_cast<uint32_t*>(v_tile(buf) + bx * BOX_BYTES + r * 128)[lane] = 0u;
+      }
+      wrote = true;
+    }
+    if (patch && pos % PAGE >= w0 && pos % PAGE < w0 + 16) {
+      const int r = pos % PAGE;
+      for (int d = lane; d < HD; d += 32) {
+        reinterpret_cast<__nv_bfloat16*>(swz(k_tile(buf), r, d & ~7))[d & 7] = new_kv[d];
+        reinterpret_cast<__nv_bfloat16*>(swz(v_tile(buf), r, d & ~7))[d & 7] = new_kv[HD + d];
+      }
+      wrote = true;
+    }
+    if (wrote) __syncwarp();
+    float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ++ks) {
+      uint32_t kb[4];
+      ldsm4(kb, swz(k_tile(buf), w0 + (lane & 7) + ((lane >> 4) << 3), ks * 16 + ((lane >> 3) & 1) * 8));
+      mma16816(sc[0], qf[ks], kb[0], kb[1]);
+      mma16816(sc[1], qf[ks], kb[2], kb[3]);
+    }
+    const int jbase = pg * PAGE + w0;
+    float mx = m_row;
+    float v[2][2];
+#pragma unroll
+    for (int n = 0; n < 2; ++n)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int j = jbase + n * 8 + tq * 2 + e;
+        v[n][e] = (j >= j_min && j <= pos) ? sc[n][e] * p.scale_log2e : -INFINITY;
+        mx = fmaxf(mx, v[n][e]);
+      }
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float alpha = m_row == -INFINITY ? 0.f : exp2f(m_row - mx);
+    m_row = mx;
+    l_row *= alpha;
+    float pr[2][2];
+#pragma unroll
+    for (int n = 0; n < 2; ++n)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        pr[n][e] = (v[n][e] == -INFINITY || mx == -INFINITY) ? 0.f : exp2f(v[n][e] - mx);
+        l_row += pr[n][e];
+      }
+#pragma unroll
+    for (int n = 0; n < KSTEPS * 2; ++n) { o[n][0] *= alpha; o[n][1] *= alpha; }
+    const uint32_t pa[4] = {pack2(pr[0][0], pr[0][1]), 0u, pack2(pr[1][0], pr[1][1]), 0u};
+#pragma unroll
+    for (int dp = 0; dp < KSTEPS; ++dp) {
+      uint32_t vb[4];
+      ldsm4t(vb, swz(v_tile(buf), w0 + (lane & 7) + (((lane >> 3) & 1) << 3), dp * 16 + (lane >> 4) * 8));
+      mma16816(o[2 * dp], pa, vb[0], vb[1]);
+      mma16816(o[2 * dp + 1], pa, vb[2], vb[3]);
+    }
+    if (wrote) sm100::fence_proxy_async_smem();          // the slot's next page arrives through the async proxy
+    __syncwarp();
+    if (lane == 0) sm100::mbar_arrive(&empty_bar[buf]);
+  }
+
+  // ---- merge the four warps in warp order (every page has been used: the ring is free)
+  consumer_sync();
+  l_row += __shfl_xor_sync(0xffffffffu, l_row, 1);
+  l_row += __shfl_xor_sync(0xffffffffu, l_row, 2);
+  float* o_s = reinterpret_cast<float*>(smem);                 // [WARPS][8][HD]
+  float* ml_s = o_s + WARPS * 8 * HD;                          // [WARPS][8][2]
+#pragma unroll
+  for (int n = 0; n < KSTEPS * 2; ++n) {
+    o_s[(warp * 8 + g) * HD + n * 8 + tq * 2] = o[n][0];
+    o_s[(warp * 8 + g) * HD + n * 8 + tq * 2 + 1] = o[n][1];
+  }
+  if (tq == 0) { ml_s[(warp * 8 + g) * 2] = m_row; ml_s[(warp * 8 + g) * 2 + 1] = l_row; }
+  consumer_sync();
+  const bool direct = p.splits == 1;
+  for (int r = 0; r < n_g && r < 8; ++r) {
+    float mm = -INFINITY;
+    for (int w = 0; w < WARPS; ++w) mm = fmaxf(mm, ml_s[(w * 8 + r) * 2]);
+    float wgt[WARPS], ll = 0.f;
+    for (int w = 0; w < WARPS; ++w) {
+      const float mw = ml_s[(w * 8 + r) * 2];
+      wgt[w] = mw == -INFINITY ? 0.f : exp2f(mw - mm);
+      ll += wgt[w] * ml_s[(w * 8 + r) * 2 + 1];
+    }
+    const float inv = ll > 0.f ? 1.0f / ll : 0.f;
+    for (int d = threadIdx.x; d < HD; d += THREADS) {
+      float acc = 0.f;
+      for (int w = 0; w < WARPS; ++w) acc += wgt[w] * o_s[(w * 8 + r) * HD + d];
+      if (direct) p.out[((size_t)t * p.heads + head0 + r) * HD + d] = __float2bfloat16_rn(acc * inv);
+      else po[(size_t)r * p.splits * HD + d] = acc;
+    }
+    if (!direct && threadIdx.x == 0) { pml[(size_t)r * p.splits * 2] = mm; pml[(size_t)r * p.splits * 2 + 1] = ll; }
+  }
+}
+#endif  // HEAD_DIM % 64 == 0
+
 // One block per (token, head): merge the splits in split order, normalise, write bf16.
 __global__ void attention_decode_tc_combine_kernel(DecodeTcParams p, IertBatchView b, IertKvView c) {
   __shared__ int red[8];
@@ -458,8 +759,33 @@ int launch_decode(const void* qkv, void* out, const IertBatchView* batch, const 
     }
     configured = true;
   }
-  launch_dep(attention_decode_tc_kernel, dim3(cache->kv_heads * p.slices, T, splits), dim3(THREADS), smem, stream,
-             p, *batch, *cache);
+  bool launched = false;
+#if HEAD_DIM % 64 == 0
+  // pages by TMA where the head size allows (IERT_DECODE_TMA=0: the cp.async kernel, for comparison)
+  static const bool use_tma = [] { const char* e = getenv("IERT_DECODE_TMA"); return !(e && e[0] == '0'); }();
+  CUtensorMap map_k, map_v;
+  const long long cache_rows = (long long)cache->n_pages * cache->kv_heads * PAGE;
+  if (use_tma && tma_host::tensor_map_2d(cache->k, cache_rows, HD, HD, PAGE, &map_k) &&
+      tma_host::tensor_map_2d(cache->v, cache_rows, HD, HD, PAGE, &map_v)) {
+    const size_t ring = 2 * NSTAGE * (size_t)TMA_TILE_BYTES;
+    size_t smem_tma = ring + ROWS * ROW_BYTES + 8 * (size_t)HD + 1024;      // (+ alignment of the ring)
+    if (merge > ring) smem_tma += merge - ring;
+    static bool configured_tma = false;
+    if (!configured_tma) {
+      if (cudaFuncSetAttribute(attention_decode_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_tma) != cudaSuccess) {
+        cudaGetLastError();
+        return IERT_CUDA_ERROR;
+      }
+      configured_tma = true;
+    }
+    launch_dep(attention_decode_tma_kernel, dim3(cache->kv_heads * p.slices, T, splits), dim3(TMA_THREADS), smem_tma, stream,
+               map_k, map_v, p, *batch, *cache);
+    launched = true;
+  }
+#endif
+  if (!launched)
+    launch_dep(attention_decode_tc_kernel, dim3(cache->kv_heads * p.slices, T, splits), dim3(THREADS), smem, stream,
+               p, *batch, *cache);
   if (cudaGetLastError() != cudaSuccess) return IERT_CUDA_ERROR;
   if (splits == 1) return IERT_OK;                   // nothing to merge: the kernel wrote the output
   launch_dep(attention_decode_tc_combine_kernel, dim3(T, heads), dim3(HD >= 128 ? 128 : 64), 0, stream, p, *batch, *cache);

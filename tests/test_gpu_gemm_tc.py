@@ -113,6 +113,17 @@ def test_token_major_kernel_in_every_mode(M, N, K):
     run(M, N, K, B.GEMM_ADD_RESIDUAL, torch.float32, force_stages=-1)
 
 
+@pytest.mark.parametrize("M", [65, 96, 128, 129, 200, 256, 257, 300, 384, 385, 512, 513])
+def test_between_decoding_and_prompts_at_layer_sizes(M):
+    """65 to 513 tokens at the widths of a 7B layer, with the tile and the splits the kernel
+    chooses itself there (64-, 128- and 256-token tiles, split over k while the tiles alone leave
+    SMs empty; token-major stores from 257 tokens on)."""
+    from inference_engine_rust_b200.csrc import bindings as B
+    run(M, 6144, 4096, B.GEMM_STORE, torch.bfloat16)
+    run(M, 4096, 4096, B.GEMM_ADD_RESIDUAL, torch.float32)
+    run(M, 4096, 14336, B.GEMM_ADD_RESIDUAL, torch.float32)
+
+
 def test_refuses_what_tma_cannot_load():
     from inference_engine_rust_b200.csrc import bindings as B
     x = torch.randn(4, 100, device=DEV).bfloat16()
