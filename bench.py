@@ -263,6 +263,7 @@ def main() -> int:
                    "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
                    "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
                    "intermediate": cfg["intermediate_size"], "vocab": vocab, "sliding_window": cfg["sliding_window"],
+                   "rope_theta": cfg["rope_theta"], "rms_norm_eps": cfg["rms_norm_eps"],
                    "global_batch": a.batch, "seq_len": a.context, "max_context": a.max_context,
                    "prefill_tokens": a.prefill_tokens, "parallelism": "single GPU",
                    "l2": "inputs larger than L2 (weights read per step exceed 126 MB many times)",
