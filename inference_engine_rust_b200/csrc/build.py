@@ -36,6 +36,8 @@ CORE_SOURCES = [
     "runtime.cu", "elementwise.cu", "gemm_plain.cu", "attention_plain.cu", "sampling.cu",
     "gemm_tc.cu", "attention_decode.cu",
 ]
+# the native reader of weight files (host code), loaded by the weights package
+IO_SOURCES = ["weight_reader.cu"]
 HEADERS = ["common.cuh"]
 # Extra -D definitions for experiments (space separated), e.g. IERT_EXTRA_DEFINES="FOO=1 BAR".
 EXTRA_DEFINES = os.environ.get("IERT_EXTRA_DEFINES", "").split()
@@ -182,7 +184,8 @@ def attention_library(head_dim: int):
 def build_all(verbose: bool = True) -> List[str]:
     """Every library the package can need that does not depend on a model's sizes, plus the
     size-specialised ones for the head sizes in `PREBUILT_HEAD_DIMS`."""
-    paths = [build_library("iert_core", CORE_SOURCES, verbose=verbose)]
+    paths = [build_library("iert_core", CORE_SOURCES, verbose=verbose),
+             build_library("iert_io", IO_SOURCES, verbose=verbose)]
     for hd in PREBUILT_HEAD_DIMS:
         paths.append(build_library(*attention_library(hd), verbose=verbose))
     return paths

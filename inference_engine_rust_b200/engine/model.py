@@ -16,7 +16,7 @@ from ..config.specs import ModelSpec
 from ..csrc import bindings as B
 from ..parts.base import Runtime, StepContext, part_class
 from ..parts.linear import Linear
-from ..weights.loader import (RandomSource, TensorSpec, WeightError, check_source, fetch)
+from ..weights.loader import (RandomSource, TensorSpec, WeightError, check_source, fetch_many)
 
 
 class Model:
@@ -68,8 +68,12 @@ class Model:
         check_source(expected, source, where)
         rt, spec = self.rt, self.spec
 
+        # every tensor to the device first (files: one pass of the native reader per file), then
+        # each part takes its own; a part that fuses matrices lets go of the separate ones
+        tensors = fetch_many(source, list(expected), rt.dtype, rt.device)
+
         def get(name):
-            return fetch(source, name, rt.dtype, rt.device)
+            return tensors.pop(name)
 
         self.embedding = get(spec.embedding_name)
         self.final_norm.load({"weight": get(spec.final_norm_name)})

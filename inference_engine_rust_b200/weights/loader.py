@@ -96,6 +96,31 @@ def fetch(source, name: str, run_dtype: torch.dtype, device) -> torch.Tensor:
     return t.to(device=device, dtype=stored_dtype_policy(t, run_dtype)).contiguous()
 
 
+def fetch_many(source, names, run_dtype: torch.dtype, device) -> Dict[str, torch.Tensor]:
+    """The named tensors on `device`, each in the dtype that `stored_dtype_policy` gives it.
+
+    From files to a CUDA device, every tensor that keeps its stored dtype (bf16 weights in a
+    bfloat16 run, 32-bit tensors always) is read by the native reader straight into its device
+    tensor, all of them in one pass over each file; what needs a conversion, and every other kind
+    of source, goes tensor by tensor through `fetch`."""
+    device = torch.device(device)
+    out: Dict[str, torch.Tensor] = {}
+    direct: Dict[str, torch.Tensor] = {}
+    can_read = hasattr(source, "read_into") and device.type == "cuda"
+    for name in names:
+        if can_read:
+            stored = source.stored_dtype(name)
+            if stored_dtype_policy(torch.empty(0, dtype=stored), run_dtype) == stored:
+                _, shape = source.describe(name)
+                direct[name] = torch.empty(tuple(shape), dtype=stored, device=device)
+                continue
+        out[name] = fetch(source, name, run_dtype, device)
+    if direct:
+        source.read_into(direct)
+        out.update(direct)
+    return out
+
+
 # ---------------------------------------------------------------------------------------
 # random weights
 

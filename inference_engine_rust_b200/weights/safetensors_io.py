@@ -91,6 +91,12 @@ class SafetensorsFile:
         return flat.reshape(shape)
 
 
+    def byte_range(self, name: str) -> Tuple[int, int]:
+        """(offset in the file, size in bytes) of the tensor's data."""
+        _, _, b, e = self.entries[name]
+        return self._base + b, e - b
+
+
 class TensorSource:
     """All tensors of a model folder: `model.safetensors`, or the shards that
     `model.safetensors.index.json` names."""
@@ -132,6 +138,38 @@ class TensorSource:
 
     def get(self, name: str) -> torch.Tensor:
         return self._files[self._where[name]].get(name)
+
+    def stored_dtype(self, name: str) -> torch.dtype:
+        return _DTYPES[self.describe(name)[0]][0]
+
+    def read_into(self, targets: Mapping[str, torch.Tensor], threads: int = 0, chunk_bytes: int = 0) -> None:
+        """Fill `targets[name]` (contiguous, of the stored dtype and shape; on a CUDA device or on
+        the host) with the named tensors' data, through the native reader: one call per file,
+        every tensor straight to its destination."""
+        from .native_reader import read_file_ranges
+        by_file: Dict[str, List[str]] = {}
+        device = None
+        for name, t in targets.items():
+            dt, shape = self.describe(name)
+            if t.dtype != _DTYPES[dt][0] or tuple(t.shape) != tuple(shape) or not t.is_contiguous():
+                raise SafetensorsError(f"{name}: the destination must be contiguous {dt} of shape {list(shape)}")
+            if device is None:
+                device = t.device
+            elif t.device != device:
+                raise SafetensorsError("all destinations of one read must be on the same device")
+            by_file.setdefault(self._where[name], []).append(name)
+        if device is None:
+            return
+        if device.type == "cuda":
+            index = device.index if device.index is not None else torch.cuda.current_device()
+            torch.cuda.synchronize(device)      # memory the allocator hands out again may still be in use
+        else:
+            index = -1
+        for path, names in by_file.items():
+            f = self._files[path]
+            ranges = [f.byte_range(n) for n in names]
+            read_file_ranges(path, [r[0] for r in ranges], [r[1] for r in ranges],
+                             [targets[n].data_ptr() for n in names], index, threads, chunk_bytes)
 
 
 def write_safetensors(path: str, tensors: Mapping[str, torch.Tensor],

@@ -161,3 +161,57 @@ def test_integer_tables_and_kind_check(tmp_path):
     with pytest.raises(WeightError) as e:
         check_source({"table": TensorSpec((5,)), "w": TensorSpec((2, 2), "int_table")}, src, "x")
     assert len(e.value.wrong_kind) == 2
+
+
+# ---- the native reader (host destinations here; device destinations in the GPU tests) ----------
+
+def test_native_reader_fills_host_tensors_in_any_chunking(tmp_path):
+    """Every tensor of a file lands where it is sent, whatever the chunk size and the number of
+    threads: chunks smaller than a row, chunks that do not divide a tensor, one thread or many."""
+    torch.manual_seed(3)
+    tensors = {"a": torch.randn(37, 53).bfloat16(), "b": torch.randn(1001), "c": torch.arange(77, dtype=torch.int32),
+               "d": torch.randn(5, 3, 7).bfloat16(), "empty": torch.empty(0, 4)}
+    path = str(tmp_path / "model.safetensors")
+    write_safetensors(path, tensors)
+    src = TensorSource(str(tmp_path))
+    for threads, chunk in [(1, 0), (3, 1000), (8, 13), (2, 1 << 20)]:
+        targets = {n: torch.full_like(t, 7) for n, t in tensors.items()}
+        src.read_into(targets, threads=threads, chunk_bytes=chunk)
+        for n, t in tensors.items():
+            assert torch.equal(targets[n], t), (n, threads, chunk)
+    # a subset, in an order that is not the file's
+    targets = {"d": torch.empty_like(tensors["d"]), "a": torch.empty_like(tensors["a"])}
+    src.read_into(targets, threads=2, chunk_bytes=64)
+    assert torch.equal(targets["a"], tensors["a"]) and torch.equal(targets["d"], tensors["d"])
+
+
+def test_native_reader_refuses_wrong_destinations_and_reports_short_files(tmp_path):
+    from inference_engine_rust_b200.weights.native_reader import ReadError, read_file_ranges
+    t = torch.randn(64, 64)
+    path = str(tmp_path / "model.safetensors")
+    write_safetensors(path, {"w": t})
+    src = TensorSource(str(tmp_path))
+    with pytest.raises(SafetensorsError, match="destination"):
+        src.read_into({"w": torch.empty(64, 64, dtype=torch.bfloat16)})
+    with pytest.raises(SafetensorsError, match="destination"):
+        src.read_into({"w": torch.empty(64, 65)[:, :64]})
+    # the file loses its tail after it was opened: the reader says where it ends
+    size = os.path.getsize(path)
+    with open(path, "r+b") as f:
+        f.truncate(size - 100)
+    with pytest.raises(ReadError, match="the file ends at byte"):
+        src.read_into({"w": torch.empty(64, 64)}, threads=2, chunk_bytes=4096)
+    with pytest.raises(ReadError, match="cannot open"):
+        read_file_ranges(str(tmp_path / "nothing"), [0], [4], [torch.empty(1).data_ptr()], -1)
+    with pytest.raises(ReadError, match="negative"):
+        read_file_ranges(path, [-1], [4], [torch.empty(1).data_ptr()], -1)
+
+
+def test_fetch_many_without_a_device_goes_tensor_by_tensor(tmp_path):
+    from inference_engine_rust_b200.weights import fetch_many
+    d = make_folder(tmp_path, TINY_A, seed=2, dtype="bfloat16")
+    src = TensorSource(d)
+    names = src.names()[:5]
+    got = fetch_many(src, names, torch.float32, "cpu")
+    for n in names:
+        assert got[n].dtype == torch.float32 and torch.equal(got[n], src.get(n).float())
