@@ -7,7 +7,8 @@ Prints ONE JSON line.  A "step" is one decode step of the whole batch (default b
 2,048 tokens of context, cache sized for 4,096): `value` is decoded tokens a second over K
 steps timed with CUDA events on the launching stream (each step = metadata copy, the
 captured forward graph, the sampling kernel); `e2e` is the same through the Python entry
-point with host token ids in and out every step.  Also reported: a 2,048-token prefill
+point with host token ids in and out every step (`run_ahead_value`: with the chosen ids fed from
+device memory and read on the host one step behind, as the library's generation loop does).  Also reported: a 2,048-token prefill
 with its fraction of the bf16 tensor peak, the decode step's fraction of the HBM roofline
 (every weight once plus the live requests' keys and values, over the step time), and decode
 at batch 1 and 64.  Peaks come from MEASURED_PEAKS.json when the driver wrote it.
@@ -137,7 +138,7 @@ def main() -> int:
     base = MISTRAL_7B if a.sizes == "7b-v0.1" else OTHER_SIZES[a.sizes]
     full_layers = base["num_hidden_layers"]
     a.layers = a.layers or full_layers
-    a.max_context = max(a.max_context, a.context + 2 * (a.steps + a.warmup) + 8, a.prefill_tokens)
+    a.max_context = max(a.max_context, a.context + 3 * (a.steps + a.warmup) + 8, a.prefill_tokens)
     cfg = dict(base, num_hidden_layers=a.layers)
     t0 = time.time()
     model = LoadedModel.random(cfg, seed=0, dtype="bfloat16", std=0.02, on_device=True)
@@ -145,7 +146,7 @@ def main() -> int:
     load_s = time.time() - t0
     batches = [a.batch] + [int(b) for b in a.points.split(",") if b.strip()]
     biggest = max(batches)
-    per_seq = -(-(a.context + 2 * (a.steps + a.warmup) + 8) // 64) * 64     # the timed run and the end-to-end run
+    per_seq = -(-(a.context + 3 * (a.steps + a.warmup) + 8) // 64) * 64     # the timed run and the two end-to-end runs
     session = model.session(max_tokens=max(biggest * per_seq, -(-a.prefill_tokens // 64) * 64), max_sequences=biggest, max_seq_len=a.max_context)
     eng = session.engine
     sampler = Sampler(SamplingParams(temperature=0.0), eng.rt.err)
@@ -202,6 +203,26 @@ def main() -> int:
         dt = time.perf_counter() - t_start
         return dt * 1e3 / steps, h2d // steps, d2h // steps
 
+    def decode_e2e_run_ahead(slots, steps, warmup):
+        """As the library's generation loop runs it: the ids chosen on the device feed the next step
+        from device memory, and the host reads every step's ids while the next step runs."""
+        n = len(slots)
+        reqs = list(range(n))
+        logits = eng.step([(s, [int(t)]) for s, t in zip(slots, rng.integers(0, vocab, n))], want="last")
+        chosen = sampler.sample_device(logits, reqs, [0] * n)
+        pending = sampler.read_async(chosen)
+        for i in range(steps + warmup):
+            if i == warmup:
+                torch.cuda.synchronize()
+                t_start = time.perf_counter()
+            logits = eng.step_tokens_on_device(slots, chosen)
+            pending.wait()
+            chosen = sampler.sample_device(logits, reqs, [i + 1] * n)
+            pending = sampler.read_async(chosen)
+        pending.wait()
+        torch.cuda.synchronize()
+        return (time.perf_counter() - t_start) * 1e3 / steps
+
     result = {}
     points = {}
     main_stats = None
@@ -213,7 +234,8 @@ def main() -> int:
         if nb == a.batch and main_stats is None:
             kv_bytes = eng.cache.kv_bytes_read(slots)
             e2e_ms, h2d, d2h = decode_e2e(slots, min(a.steps, 64), a.warmup)
-            main_stats = dict(ms=ms, launches=launches, kv_bytes=kv_bytes, e2e_ms=e2e_ms, h2d=h2d, d2h=d2h,
+            ahead_ms = decode_e2e_run_ahead(slots, min(a.steps, 64), a.warmup)
+            main_stats = dict(ms=ms, launches=launches, kv_bytes=kv_bytes, e2e_ms=e2e_ms, h2d=h2d, d2h=d2h, ahead_ms=ahead_ms,
                               clocks=clocks.summary(m0, m1))
         else:
             points[f"decode_b{nb}"] = round(nb * 1e3 / ms, 1)
@@ -269,7 +291,9 @@ def main() -> int:
                    "l2": "inputs larger than L2 (weights read per step exceed 126 MB many times)",
                    "peaks": pk["source"]},
         "e2e": {"value": round(a.batch * 1e3 / main_stats["e2e_ms"], 1), "unit": "tokens/s",
-                "h2d_bytes_per_step": main_stats["h2d"], "d2h_bytes_per_step": main_stats["d2h"]},
+                "h2d_bytes_per_step": main_stats["h2d"], "d2h_bytes_per_step": main_stats["d2h"],
+                # the same loop as generate() runs it: ids fed from device memory, read on the host one step behind
+                "run_ahead_value": round(a.batch * 1e3 / main_stats["ahead_ms"], 1)},
         "gpu_launches": main_stats["launches"],
         "clocks": main_stats["clocks"],
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",

@@ -136,6 +136,14 @@ class InferenceSession:
             return None
         return self.engine.step(entries, want=want)
 
+    def decode_tokens_on_device(self, tokens: torch.Tensor, want="last") -> Optional[torch.Tensor]:
+        """One more token for every sequence of the batch, the ids taken from device memory
+        (int32 [sequences], e.g. what `Sampler.sample_device` returned): the step is launched
+        without waiting for the ids on the host."""
+        if not self._slots:
+            raise RuntimeError("no batch is running; prefill() first")
+        return self.engine.step_tokens_on_device(self._slots, tokens, want=want)
+
     def logits_last_token(self, logits: torch.Tensor) -> List[List[float]]:
         """Host copy of the logits a step returned (src/engine/session.rs:72-74)."""
         self.engine.check_device()
@@ -145,9 +153,12 @@ class InferenceSession:
     def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: int = 20,
                  temperature: float = 0.0, seed: int = 0, stop_ids: Optional[Iterable[int]] = None,
                  max_batch: Optional[int] = None, request_ids: Optional[Sequence[int]] = None,
-                 on_token=None, full: bool = False) -> Union[List[List[int]], List[GenerationResult]]:
+                 on_token=None, full: bool = False,
+                 run_ahead: bool = True) -> Union[List[List[int]], List[GenerationResult]]:
         """Generated token ids for every prompt (host lists in, host lists out).  Stop ids
-        default to the configuration's EOS; the stop token is not part of the output."""
+        default to the configuration's EOS; the stop token is not part of the output.
+        `run_ahead` (default): chosen ids feed the next step from device memory and reach the
+        host one step behind, so the device never waits for the host; results are the same."""
         if self._slots:
             raise RuntimeError("a batch started with prefill() is running; reset() first")
         spec = self.loaded.spec
@@ -158,6 +169,7 @@ class InferenceSession:
         res = _generate(self.engine, sampler, prompts, max_new_tokens, stop_ids=stop_ids,
                         max_tokens=cache.n_pages * cache.page_tokens, max_sequences=cache.n_slots,
                         max_seq_len=cache.max_seq_len, page_tokens=cache.page_tokens,
-                        max_batch=max_batch, request_ids=request_ids, on_token=on_token)
+                        max_batch=max_batch, request_ids=request_ids, on_token=on_token,
+                        run_ahead=run_ahead)
         self.engine.check_device()
         return res if full else [r.tokens for r in res]

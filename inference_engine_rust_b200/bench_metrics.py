@@ -134,9 +134,16 @@ class EngineBench:
         warm_prefill_ms = _ms(t0)
         reqs = list(range(n))
         t0 = _now()
+        # as the generation loop runs it: the chosen ids feed the next step from device memory and
+        # are read on the host, every step, while that step runs
+        chosen = sampler.sample_device(logits, reqs, [0] * n)
+        pending = sampler.read_async(chosen)
         for i in range(decode_tokens):
-            ids = sampler(logits, reqs, [i] * n)
-            logits = session.decode_tokens(ids)
+            logits = session.decode_tokens_on_device(chosen)
+            pending.wait()
+            if i + 1 < decode_tokens:
+                chosen = sampler.sample_device(logits, reqs, [i + 1] * n)
+                pending = sampler.read_async(chosen)
         _sync()
         decode_elapsed_ms = _ms(t0)
         session.engine.check_device()

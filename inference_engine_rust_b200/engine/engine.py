@@ -233,18 +233,38 @@ class Engine:
         """Run one step.  `entries` = [(slot, tokens)]; `want` = "last", "all", "none"/None, or
         for each sequence the places among its tokens whose logits are wanted.  Returns
         float32 [wanted, vocab] on the device, in the order of the entries and of `want`."""
-        kind, slots, q_lens, pos0, tokens, cu, rows = self.plan(entries, want)
+        return self._run(self.plan(entries, want), None)
+
+    def step_tokens_on_device(self, slots: Sequence[int], tokens: torch.Tensor,
+                              rows: Optional[Sequence[int]] = None, want: Want = "last") -> Optional[torch.Tensor]:
+        """A one-token step whose token ids are already on the device: sequence j brings
+        `tokens[rows[j]]` (`rows` defaults to 0, 1, ...; int32, for instance straight from the
+        sampling kernel).  Nothing waits for the ids on the host, so the step can be launched while
+        the step before it still runs; the embedding kernel reports an id outside the vocabulary
+        through the device error word."""
+        n = len(slots)
+        rows = list(range(n)) if rows is None else [int(r) for r in rows]
+        if (tokens.dim() != 1 or tokens.dtype != torch.int32 or tokens.device.type != self.rt.device.type
+                or len(rows) != n or any(not 0 <= r < tokens.shape[0] for r in rows)):
+            raise StepError("device tokens must be int32 [rows] on the model's device, one row per sequence")
+        plan = self.plan([(s, (0,)) for s in slots], want)
+        if plan[0] != "decode":
+            raise StepError("tokens on the device can only continue running sequences by one token")
+        return self._run(plan, (tokens, rows))
+
+    def _run(self, plan, device_tokens) -> Optional[torch.Tensor]:
+        kind, slots, q_lens, pos0, tokens, cu, rows = plan
         n, T, R = len(slots), int(cu[-1]), len(rows)
         for slot, p, q in zip(slots, pos0, q_lens):
             self.cache.reserve(slot, p + q)
         self.cache.upload()
         if kind == "decode" and self.use_graphs and R in (0, n) and rows == list(range(R)):
-            logits = self._step_graph(slots, pos0, tokens, R)
+            logits = self._step_graph(slots, pos0, tokens, R, device_tokens)
         elif (kind == "prompt" and self.use_graphs and T <= PROMPT_GRAPH_MAX_TOKENS and n <= PROMPT_GRAPH_MAX_SEQUENCES
               and R in (0, n) and rows == [int(c) - 1 for c in cu[1:1 + R]] and self._prompt_bucket_is_warm(n, T)):
             logits = self._step_prompt_graph(slots, q_lens, tokens, cu, R)
         else:
-            logits = self._step_eager(kind, slots, q_lens, pos0, tokens, cu, rows)
+            logits = self._step_eager(kind, slots, q_lens, pos0, tokens, cu, rows, device_tokens)
         for slot, q in zip(slots, q_lens):
             self.cache.advance(slot, q)
         self.steps_run += 1
@@ -273,7 +293,20 @@ class Engine:
         kind replay a graph of their own."""
         return len(pos0) >= 2 and self.model.cut_by_length(pos0)
 
-    def _step_eager(self, kind, slots, q_lens, pos0, tokens, cu, rows):
+    @staticmethod
+    def _place_device_tokens(dest: torch.Tensor, device_tokens) -> None:
+        """dest[j] = tokens[rows[j]] by one device-to-device copy per run of consecutive rows
+        (usually one: rows leave the batch only when a sequence ends)."""
+        tokens, rows = device_tokens
+        j = 0
+        while j < len(rows):
+            k = j + 1
+            while k < len(rows) and rows[k] == rows[k - 1] + 1:
+                k += 1
+            dest[j:k].copy_(tokens[rows[j]:rows[j] + (k - j)], non_blocking=True)
+            j = k
+
+    def _step_eager(self, kind, slots, q_lens, pos0, tokens, cu, rows, device_tokens=None):
         n, T, R = len(slots), int(cu[-1]), len(rows)
         o_cu, o_slot, o_pos, o_seq, o_tok, o_rows, total = self._layout(n, T, R)
         host, turn = self._staging.next(total)
@@ -289,6 +322,8 @@ class Engine:
         meta = self._meta_dev
         meta[:total].copy_(host[:total], non_blocking=True)
         self._staging.sent(turn)
+        if device_tokens is not None:
+            self._place_device_tokens(meta[o_tok:o_tok + T], device_tokens)
         self.h2d_bytes_last_step = total * 4
         ctx = self._context(kind, meta, n, T, q_lens, pos0, slots)
         ctx.unequal_lengths = kind == "decode" and self._unequal(pos0)
@@ -296,7 +331,7 @@ class Engine:
                                   meta[o_rows:o_rows + R] if R else None, R)
 
     # ---- one-token steps as replayed CUDA graphs ---------------------------------------------
-    def _step_graph(self, slots, pos0, tokens, R):
+    def _step_graph(self, slots, pos0, tokens, R, device_tokens=None):
         """A one-token step through a captured graph.  Batches are padded to the next power of
         two with sequences whose slot is -1: kernels skip them, so padding changes no result.
         The graph writes its logits into a buffer of its own; the caller gets a copy."""
@@ -323,6 +358,8 @@ class Engine:
         h[o_rows:o_rows + nb] = np.arange(nb)
         g.meta[:total].copy_(host[:total], non_blocking=True)
         self._staging.sent(turn)
+        if device_tokens is not None:
+            self._place_device_tokens(g.meta[o_tok:o_tok + n], device_tokens)
         self.h2d_bytes_last_step = total * 4
         g.graph.replay()
         self.graph_launches += g.launches

@@ -11,6 +11,15 @@ as in src/engine/generation.rs:5-9: `sampler` chooses, this file decides who goe
 The loop only needs an object with open_sequence(), close_sequence(slot) and
 step(entries, want="last") and a callable sampler(logits, request_ids, steps) -> token ids,
 so its decisions can be tested without a device.
+
+Where the engine can take a step's tokens from device memory (`step_tokens_on_device`) and the
+sampler can hand them back without waiting (`sample_device`, `read_async`), the loop runs one
+step ahead of the host: the ids chosen from step k's logits stay on the device and feed step
+k + 1 at once, and the host reads them, decides who has ended and calls `on_token` while step
+k + 1 runs.  Who goes on by count alone (new-token limit, context) is known beforehand; only a
+stop token is not, so a sequence that ends on one has run one step in vain, whose result nobody
+reads and whose slot is given back like any other.  Tokens, reasons and the order of `on_token`
+calls are those of the plain loop.
 """
 from __future__ import annotations
 
@@ -58,6 +67,76 @@ def plan_batches(prompt_lens: Sequence[int], max_new_tokens: int, *, max_tokens:
     return batches
 
 
+def can_run_ahead(engine, sampler) -> bool:
+    return (hasattr(engine, "step_tokens_on_device") and hasattr(sampler, "sample_device")
+            and hasattr(sampler, "read_async"))
+
+
+def _keep(res: GenerationResult, tok: int, max_new_tokens: int, stop_ids: Set[int], max_seq_len: int,
+          on_token) -> None:
+    """What the loop does with a chosen token (src/main.rs:100-108), and why a sequence ends."""
+    if tok in stop_ids:                                 # not kept: src/main.rs:104-106
+        res.finish_reason = "stop"
+        return
+    res.tokens.append(tok)
+    if on_token is not None:
+        on_token(res.request, tok)
+    if len(res.tokens) >= max_new_tokens:
+        res.finish_reason = "length"
+    elif res.prompt_len + len(res.tokens) > max_seq_len:
+        res.finish_reason = "context"                   # no room to run this token
+
+
+def run_batch_ahead(engine, sampler, prompts: Sequence[Sequence[int]], request_ids: Sequence[int],
+                    max_new_tokens: int, stop_ids: Set[int], max_seq_len: int,
+                    on_token: Optional[Callable[[int, int], None]] = None) -> List[GenerationResult]:
+    """`run_batch` with the device one step ahead of the host (see the head of this file)."""
+    results = [GenerationResult(request=r, prompt_len=len(p)) for r, p in zip(request_ids, prompts)]
+    if max_new_tokens <= 0:
+        for res in results:
+            res.finish_reason = "length"
+        return results
+    slots = [engine.open_sequence() for _ in prompts]
+
+    def goes_on_if_kept(res: GenerationResult) -> bool:
+        """Will the sequence run its next token, if that token is no stop token?"""
+        n = len(res.tokens) + 1
+        return n < max_new_tokens and res.prompt_len + n <= max_seq_len
+
+    try:
+        layout = list(range(len(prompts)))         # batch indices in the row order of `chosen_dev`
+        logits = engine.step([(slots[i], list(prompts[i])) for i in layout], want="last")
+        step_no = 0
+        chosen_dev = sampler.sample_device(logits, [request_ids[i] for i in layout], [step_no] * len(layout))
+        pending = sampler.read_async(chosen_dev)
+        while True:
+            rows = [r for r, i in enumerate(layout) if not results[i].finish_reason and goes_on_if_kept(results[i])]
+            ahead = None
+            if rows:
+                nxt = [layout[r] for r in rows]
+                logits = engine.step_tokens_on_device([slots[i] for i in nxt], chosen_dev, rows)
+                nxt_dev = sampler.sample_device(logits, [request_ids[i] for i in nxt], [step_no + 1] * len(nxt))
+                ahead = (nxt, nxt_dev, sampler.read_async(nxt_dev))
+            chosen = pending.wait()
+            for i, tok in zip(layout, chosen):
+                res = results[i]
+                if res.finish_reason:                   # ended on a stop token one step ago: its row ran in vain
+                    continue
+                _keep(res, int(tok), max_new_tokens, stop_ids, max_seq_len, on_token)
+                if res.finish_reason:
+                    engine.close_sequence(slots[i])
+                    slots[i] = None
+            if ahead is None:
+                break
+            layout, chosen_dev, pending = ahead
+            step_no += 1
+    finally:
+        for s in slots:
+            if s is not None:
+                engine.close_sequence(s)
+    return results
+
+
 def run_batch(engine, sampler: Callable, prompts: Sequence[Sequence[int]], request_ids: Sequence[int],
               max_new_tokens: int, stop_ids: Set[int], max_seq_len: int,
               on_token: Optional[Callable[[int, int], None]] = None) -> List[GenerationResult]:
@@ -77,23 +156,13 @@ def run_batch(engine, sampler: Callable, prompts: Sequence[Sequence[int]], reque
             going_on, feed = [], []
             for i, tok in zip(live, chosen):
                 res = results[i]
-                tok = int(tok)
-                if tok in stop_ids:                         # not kept: src/main.rs:104-106
-                    res.finish_reason = "stop"
-                else:
-                    res.tokens.append(tok)
-                    if on_token is not None:
-                        on_token(res.request, tok)
-                    if len(res.tokens) >= max_new_tokens:
-                        res.finish_reason = "length"
-                    elif res.prompt_len + len(res.tokens) > max_seq_len:
-                        res.finish_reason = "context"       # no room to run this token
-                    else:
-                        going_on.append(i)
-                        feed.append(tok)
+                _keep(res, int(tok), max_new_tokens, stop_ids, max_seq_len, on_token)
                 if res.finish_reason:
                     engine.close_sequence(slots[i])
                     slots[i] = None
+                else:
+                    going_on.append(i)
+                    feed.append(int(tok))
             live = going_on
             if not live:
                 break
@@ -110,8 +179,10 @@ def generate(engine, sampler: Callable, prompts: Sequence[Sequence[int]], max_ne
              stop_ids: Iterable[int] = (), max_tokens: int, max_sequences: int, max_seq_len: int,
              page_tokens: int, max_batch: Optional[int] = None,
              request_ids: Optional[Sequence[int]] = None,
-             on_token: Optional[Callable[[int, int], None]] = None) -> List[GenerationResult]:
-    """All requests, batch after batch, results in the order of `prompts`."""
+             on_token: Optional[Callable[[int, int], None]] = None,
+             run_ahead: bool = True) -> List[GenerationResult]:
+    """All requests, batch after batch, results in the order of `prompts`.  `run_ahead`: keep the
+    device one step ahead of the host where engine and sampler allow it."""
     if request_ids is None:
         request_ids = list(range(len(prompts)))
     if len(request_ids) != len(prompts):
@@ -122,8 +193,9 @@ def generate(engine, sampler: Callable, prompts: Sequence[Sequence[int]], max_ne
                            page_tokens=page_tokens, max_batch=max_batch)
     out: List[Optional[GenerationResult]] = [None] * len(prompts)
     for batch in batches:
-        res = run_batch(engine, sampler, [prompts[i] for i in batch], [request_ids[i] for i in batch],
-                        max_new_tokens, stop, max_seq_len, on_token)
+        run = run_batch_ahead if run_ahead and can_run_ahead(engine, sampler) else run_batch
+        res = run(engine, sampler, [prompts[i] for i in batch], [request_ids[i] for i in batch],
+                  max_new_tokens, stop, max_seq_len, on_token)
         for i, r in zip(batch, res):
             r.request = i
             out[i] = r

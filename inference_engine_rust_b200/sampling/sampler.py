@@ -46,6 +46,11 @@ class Sampler:
     def __init__(self, params: SamplingParams, err: torch.Tensor):
         self.params = params
         self.err = err
+        # page-locked host buffers for the ids on their way back, used in rotation (the generation
+        # loop has at most two reads in flight)
+        self._host: List[Optional[torch.Tensor]] = [None] * 4
+        self._events: list = [None] * 4
+        self._turn = 0
 
     def sample_device(self, logits: torch.Tensor, request_ids: Sequence[int],
                       steps: Sequence[int]) -> torch.Tensor:
@@ -67,12 +72,42 @@ class Sampler:
                                  ctr[0], ctr[1], out, self.err, stream)
         return out
 
+    def read_async(self, tokens: torch.Tensor) -> "PendingTokens":
+        """Start the copy of device token ids (int32 [rows], as `sample_device` returns them) and
+        of the device error word to the host, and return at once; `wait()` on the result gives
+        the ids.  The caller may launch more work in between: the generation loop starts the
+        next step from the ids on the device and reads them on the host one step behind."""
+        rows = tokens.shape[0]
+        i = self._turn
+        self._turn = (i + 1) % len(self._host)
+        buf = self._host[i]
+        if buf is None or buf.numel() < rows + 1:
+            buf = self._host[i] = torch.empty(max(rows + 1, 65), dtype=torch.int32, pin_memory=True)
+        buf[:rows].copy_(tokens, non_blocking=True)
+        buf[rows:rows + 1].copy_(self.err, non_blocking=True)
+        ev = self._events[i]
+        if ev is None:
+            ev = self._events[i] = torch.cuda.Event()
+        ev.record()
+        return PendingTokens(self, buf, rows, ev)
+
     def __call__(self, logits: torch.Tensor, request_ids: Sequence[int], steps: Sequence[int]) -> List[int]:
         """Host token ids (synchronises), after checking the device error word."""
-        out = self.sample_device(logits, request_ids, steps)
-        tokens = out.tolist()
-        bits = int(self.err.item())
+        return self.read_async(self.sample_device(logits, request_ids, steps)).wait()
+
+
+class PendingTokens:
+    """Token ids on their way to the host (one copy for the ids and the error word, one wait)."""
+
+    def __init__(self, sampler: Sampler, buf: torch.Tensor, rows: int, event):
+        self._sampler, self._buf, self._rows, self._event = sampler, buf, rows, event
+
+    def wait(self) -> List[int]:
+        """The ids, after checking the device error word as it stood when they were chosen."""
+        self._event.synchronize()
+        values = self._buf[:self._rows + 1].tolist()
+        bits = values.pop()
         if bits:
-            self.err.zero_()
+            self._sampler.err.zero_()
             raise SamplingError(B.describe_error_bits(bits))
-        return tokens
+        return values

@@ -3,7 +3,7 @@ import os
 
 import pytest
 
-from inference_engine_rust_b200.engine.generate import generate, plan_batches, run_batch
+from inference_engine_rust_b200.engine.generate import generate, plan_batches, run_batch, run_batch_ahead
 
 
 class ScriptedEngine:
@@ -46,6 +46,87 @@ def scripted_sampler(script):
         return [script[r][st] for r, st in zip(request_ids, steps)]
     sampler.calls = calls
     return sampler
+
+
+class AheadEngine(ScriptedEngine):
+    """A scripted engine that also takes a step's tokens 'from the device': here a list that the
+    scripted sampler made, of which the rows named are used."""
+
+    def step_tokens_on_device(self, slots, tokens, rows=None, want="last"):
+        rows = list(range(len(slots))) if rows is None else list(rows)
+        assert len(rows) == len(slots) and rows == sorted(set(rows))
+        return self.step([(s, [tokens[r]]) for s, r in zip(slots, rows)], want)
+
+
+class AheadSampler:
+    """The scripted sampler with the two calls of the run-ahead loop.  `wait()` hands the ids out
+    and notes how many steps the engine had run by then."""
+
+    def __init__(self, script, engine=None):
+        self.script, self.engine, self.calls, self.waits = script, engine, [], []
+
+    def __call__(self, logits, request_ids, steps):
+        return self.sample_device(logits, request_ids, steps)
+
+    def sample_device(self, logits, request_ids, steps):
+        self.calls.append((list(request_ids), list(steps)))
+        return [self.script[r][st] if st < len(self.script[r]) else 0 for r, st in zip(request_ids, steps)]
+
+    def read_async(self, tokens):
+        outer = self
+
+        class Pending:
+            def wait(self):
+                outer.waits.append(len(outer.engine.steps) if outer.engine else None)
+                return list(tokens)
+        return Pending()
+
+
+CASES = [
+    # script, prompts, max_new_tokens, stop ids, max_seq_len
+    ({0: [10, 11, 2, 99], 1: [2], 2: [20, 21, 22, 23, 24]}, [[1, 5], [1, 6, 7], [1]], 4, {2}, 100),
+    ({0: [5, 6, 7]}, [[1, 2, 3]], 3, set(), 100),
+    ({0: [5, 6, 7, 8, 9]}, [[1, 2, 3]], 10, set(), 5),
+    ({0: [5], 1: [6]}, [[1], [1, 2]], 1, set(), 100),
+    ({0: [7, 7, 2], 1: [2, 9], 2: [8, 2, 8], 3: [1, 1, 1, 1, 1, 2]}, [[1], [2, 2], [3, 3, 3], [4]], 6, {2}, 100),
+    ({0: [3, 3, 3, 3], 1: [4, 2, 4, 4]}, [[1] * 6, [1] * 2], 9, {2}, 8),      # one ends by context, one on a stop
+]
+
+
+@pytest.mark.parametrize("script,prompts,max_new,stop,max_len", CASES)
+def test_running_ahead_gives_the_plain_loop_s_results(script, prompts, max_new, stop, max_len):
+    """Same tokens, reasons, token callbacks in the same order, every slot given back; the only
+    extra work is one row-step for each sequence that ends on a stop token."""
+    ids = list(range(len(prompts)))
+    plain_eng, plain_seen = ScriptedEngine(len(prompts)), []
+    plain = run_batch(plain_eng, scripted_sampler({r: t + [0] * 4 for r, t in script.items()}), prompts, ids,
+                      max_new, stop, max_len, on_token=lambda r, t: plain_seen.append((r, t)))
+    eng, seen = AheadEngine(len(prompts)), []
+    sampler = AheadSampler(script, eng)
+    ahead = run_batch_ahead(eng, sampler, prompts, ids, max_new, stop, max_len, on_token=lambda r, t: seen.append((r, t)))
+    assert [(r.tokens, r.finish_reason) for r in ahead] == [(r.tokens, r.finish_reason) for r in plain]
+    assert seen == plain_seen
+    assert not eng.held and sorted(eng.free) == list(range(len(prompts)))
+    rows_plain = sum(len(e) for _, e in plain_eng.steps[1:])
+    rows_ahead = sum(len(e) for _, e in eng.steps[1:])
+    stopped_after_start = sum(1 for r in plain if r.finish_reason == "stop")
+    assert rows_plain <= rows_ahead <= rows_plain + stopped_after_start
+    # the host reads the ids of step k only after step k + 1 was launched (except at the very end)
+    for k, steps_run in enumerate(sampler.waits[:-1]):
+        assert steps_run == k + 2, "the next step was not launched before the host waited"
+
+
+def test_running_ahead_is_chosen_by_generate_when_both_sides_can():
+    eng = AheadEngine(2)
+    sampler = AheadSampler({i: [30 + i, 40 + i, 2] for i in range(5)}, eng)
+    res = generate(eng, sampler, [[1, i] for i in range(5)], 8, stop_ids=[2], max_tokens=64 * 2,
+                   max_sequences=2, max_seq_len=64, page_tokens=64)
+    assert [r.tokens for r in res] == [[30 + i, 40 + i] for i in range(5)] and sampler.waits
+    eng2 = AheadEngine(2)
+    sampler2 = AheadSampler({i: [30 + i, 40 + i, 2] for i in range(5)}, eng2)
+    res2 = generate(eng2, sampler2, [[1, i] for i in range(5)], 8, stop_ids=[2], max_tokens=64 * 2,
+                    max_sequences=2, max_seq_len=64, page_tokens=64, run_ahead=False)
+    assert [r.tokens for r in res2] == [r.tokens for r in res] and not sampler2.waits
 
 
 def test_stop_token_is_not_kept_and_shorter_sequences_end_earlier():

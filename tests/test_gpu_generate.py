@@ -56,6 +56,69 @@ def test_stop_tokens_and_batches_one_after_another(loaded):
     session.engine.cache.check()
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_running_ahead_changes_no_token(loaded, tmp_path, dtype):
+    """The loop that feeds chosen ids from device memory and reads them one step behind against
+    the loop that waits for them every step: greedy and temperature, stop tokens that end
+    sequences in the middle of a batch, more requests than slots."""
+    from inference_engine_rust_b200 import LoadedModel
+    folder, model, w = loaded["A"]
+    cfg = TINY["A"]
+    if dtype == "bfloat16":
+        model = LoadedModel.load(make_folder(tmp_path, cfg, seed=31, dtype="bfloat16"), dtype="bfloat16")
+    prompts = prompts_for(cfg, [9, 4, 30, 17, 2, 12, 6, 70], seed=4)
+    session = model.session(max_tokens=64 * 4, max_sequences=3, poison_cache=True)
+    for temperature in (0.0, 0.9):
+        free_run = session.generate(prompts, max_new_tokens=12, temperature=temperature, seed=5, stop_ids=[],
+                                    run_ahead=False)
+        stop = {free_run[0][3], free_run[2][0], free_run[5][7], free_run[7][11]}
+        seen_a, seen_b = [], []
+        plain = session.generate(prompts, max_new_tokens=12, temperature=temperature, seed=5, stop_ids=stop,
+                                 full=True, run_ahead=False, on_token=lambda r, t: seen_a.append((r, t)))
+        ahead = session.generate(prompts, max_new_tokens=12, temperature=temperature, seed=5, stop_ids=stop,
+                                 full=True, on_token=lambda r, t: seen_b.append((r, t)))
+        assert [(r.tokens, r.finish_reason) for r in ahead] == [(r.tokens, r.finish_reason) for r in plain]
+        assert seen_a == seen_b and any(r.finish_reason == "stop" for r in plain)
+        session.engine.cache.check()
+        assert session.engine.cache.slots.held_count == 0
+
+
+def test_a_step_takes_its_tokens_from_device_memory(loaded):
+    """`step_tokens_on_device` against `step` with the same ids from the host: the same logits to
+    the bit, also when the rows used are not all of the tensor and when graphs are off; what it
+    cannot run is refused on the host."""
+    from inference_engine_rust_b200 import StepError
+    folder, model, w = loaded["B"]
+    cfg = TINY["B"]
+    prompts = prompts_for(cfg, [4, 9, 17], seed=6)
+    ids = torch.tensor([5, 77, 300, 9, 41], dtype=torch.int32, device="cuda:0")
+    for use_graphs in (True, False):
+        a = model.session(max_tokens=512, use_graphs=use_graphs)
+        b = model.session(max_tokens=512, use_graphs=use_graphs)
+        a.prefill(prompts)
+        b.prefill(prompts)
+        for rows in ([0, 1, 2], [1, 2, 4], [4, 1, 3]):
+            want = a.decode_tokens([int(ids[r]) for r in rows])
+            got = b.engine.step_tokens_on_device(b._slots, ids, rows)
+            assert torch.equal(got, want)
+        assert torch.equal(b.decode_tokens_on_device(ids[:3]), a.decode_tokens([5, 77, 300]))
+        b.engine.check_device()
+        with pytest.raises(StepError):
+            b.engine.step_tokens_on_device(b._slots, ids.long())
+        with pytest.raises(StepError):
+            b.engine.step_tokens_on_device(b._slots, ids, [0, 1, 5])
+        with pytest.raises(StepError):
+            b.engine.step_tokens_on_device(b._slots[:2], ids, [0, 1, 2])
+        # an id outside the vocabulary is reported by the device
+        bad = torch.tensor([1, cfg["vocab_size"], 2], dtype=torch.int32, device="cuda:0")
+        b.decode_tokens_on_device(bad)
+        from inference_engine_rust_b200.engine.engine import DeviceFault
+        with pytest.raises(DeviceFault):
+            b.engine.check_device()
+        a.reset()
+        b.reset()
+
+
 def test_default_stop_is_the_configured_eos(loaded):
     folder, model, w = loaded["B"]
     cfg = TINY["B"]
