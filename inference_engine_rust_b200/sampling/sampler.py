@@ -51,6 +51,9 @@ class Sampler:
         self._host: List[Optional[torch.Tensor]] = [None] * 4
         self._events: list = [None] * 4
         self._turn = 0
+        self._ctr_host: List[Optional[torch.Tensor]] = [None] * 4
+        self._ctr_events: list = [None] * 4
+        self._ctr_turn = 0
 
     def sample_device(self, logits: torch.Tensor, request_ids: Sequence[int],
                       steps: Sequence[int]) -> torch.Tensor:
@@ -67,10 +70,32 @@ class Sampler:
         else:
             if len(request_ids) != rows or len(steps) != rows:
                 raise SamplingError("one request id and one step per row are needed")
-            ctr = torch.tensor([list(request_ids), list(steps)], dtype=torch.int32).to(logits.device)
+            ctr = self._counters_to_device(request_ids, steps, logits.device)
             B.sample_temperature(logits, float(self.params.temperature), self.params.seed,
                                  ctr[0], ctr[1], out, self.err, stream)
         return out
+
+    def _counters_to_device(self, request_ids: Sequence[int], steps: Sequence[int], device) -> torch.Tensor:
+        """int32 [2, rows] on the device, sent from a page-locked buffer without waiting for the
+        device (a copy out of ordinary memory would hold the host until the stream has drained)."""
+        rows = len(request_ids)
+        i = self._ctr_turn
+        self._ctr_turn = (i + 1) % len(self._ctr_host)
+        if self._ctr_events[i] is not None:
+            self._ctr_events[i].synchronize()          # the copy that last used this buffer is over
+        buf = self._ctr_host[i]
+        if buf is None or buf.shape[1] < rows:
+            buf = self._ctr_host[i] = torch.empty((2, max(rows, 64)), dtype=torch.int32, pin_memory=True)
+        view = buf[:, :rows]
+        view[0] = torch.tensor(list(request_ids), dtype=torch.int32)
+        view[1] = torch.tensor(list(steps), dtype=torch.int32)
+        dev = torch.empty((2, rows), dtype=torch.int32, device=device)
+        dev.copy_(view, non_blocking=True)
+        ev = self._ctr_events[i]
+        if ev is None:
+            ev = self._ctr_events[i] = torch.cuda.Event()
+        ev.record()
+        return dev
 
     def read_async(self, tokens: torch.Tensor) -> "PendingTokens":
         """Start the copy of device token ids (int32 [rows], as `sample_device` returns them) and
