@@ -65,3 +65,36 @@ def test_loaded_model_holds_the_folder_s_tensors(tmp_path, dtype):
         qkv = torch.cat([src.get(pre + f"self_attn.{p}_proj.weight") for p in "qkv"], dim=0).to(want_dt)
         assert torch.equal(mixer.qkv.weight.cpu(), qkv)
         assert torch.equal(mixer.o.weight.cpu(), src.get(pre + "self_attn.o_proj.weight").to(want_dt))
+
+
+def test_a_folder_with_32_bit_scales_and_table_in_a_bfloat16_run(tmp_path):
+    """Norm scales and the embedding table stored in 32-bit stay 32-bit in a bfloat16 run (the
+    kernels read them as they are), matrices stay bfloat16; the model still agrees with the
+    plain implementation run on exactly these values."""
+    from helpers import TINY_A, compare, plain_weights, prompts_for
+    from plain import mistral_plain as P
+    from inference_engine_rust_b200 import LoadedModel
+    from inference_engine_rust_b200.weights import TensorSource, write_safetensors
+    d = make_folder(tmp_path, TINY_A, seed=9, dtype="bfloat16")
+    src = TensorSource(d)
+    torch.manual_seed(0)
+    tensors = {}
+    for n in src.names():
+        t = src.get(n).clone()
+        if n.endswith("norm.weight") or n == "model.embed_tokens.weight":
+            t = t.float() + 1e-3 * torch.randn(t.shape)          # values that bfloat16 cannot hold
+        tensors[n] = t
+    write_safetensors(os.path.join(d, "model.safetensors"), tensors)
+    loaded = LoadedModel.load(d, dtype="bfloat16")
+    m = loaded.model
+    assert m.embedding.dtype == torch.float32 and torch.equal(m.embedding.cpu(), tensors["model.embed_tokens.weight"])
+    assert m.final_norm.weight.dtype == torch.float32 and torch.equal(m.final_norm.weight.cpu(), tensors["model.norm.weight"])
+    norm1, mixer, _, ffn = m._layer_parts[1]
+    assert torch.equal(norm1.weight.cpu(), tensors["model.layers.1.input_layernorm.weight"])
+    assert mixer.qkv.weight.dtype == torch.bfloat16 and ffn.down.weight.dtype == torch.bfloat16
+    prompt = prompts_for(TINY_A, [37], seed=2)[0]
+    eng = loaded.session(max_tokens=128, poison_cache=True).engine
+    slot = eng.open_sequence()
+    got = eng.step([(slot, prompt)], want="all")
+    eng.check_device()
+    compare(got, P.forward(TINY_A, plain_weights(d), prompt, P.bf16_rounding), "bfloat16", "32-bit scales and table")
