@@ -116,6 +116,32 @@ def test_running_ahead_gives_the_plain_loop_s_results(script, prompts, max_new, 
         assert steps_run == k + 2, "the next step was not launched before the host waited"
 
 
+def test_running_ahead_equals_the_plain_loop_on_random_scripts():
+    """Three hundred random batches: sizes, prompt lengths, limits, stop tokens that fall anywhere
+    (also on the first token, also for every sequence at once)."""
+    import random
+    rnd = random.Random(7)
+    for case in range(300):
+        n = rnd.randint(1, 6)
+        max_new = rnd.randint(1, 9)
+        prompts = [[1] * rnd.randint(1, 12) for _ in range(n)]
+        max_len = rnd.choice([100, max(len(p) for p in prompts) + rnd.randint(0, 6)])
+        stop = set(rnd.sample(range(2, 8), rnd.randint(0, 3)))
+        script = {r: [rnd.randint(2, 12) for _ in range(max_new + 1)] for r in range(n)}
+        ids = list(range(n))
+        e1, seen1 = ScriptedEngine(n), []
+        plain = run_batch(e1, scripted_sampler(script), prompts, ids, max_new, stop, max_len,
+                          on_token=lambda r, t: seen1.append((r, t)))
+        e2, seen2 = AheadEngine(n), []
+        ahead = run_batch_ahead(e2, AheadSampler(script, e2), prompts, ids, max_new, stop, max_len,
+                                on_token=lambda r, t: seen2.append((r, t)))
+        assert [(r.tokens, r.finish_reason) for r in ahead] == [(r.tokens, r.finish_reason) for r in plain], case
+        assert seen1 == seen2 and not e2.held and len(e2.free) == n, case
+        # what each slot was fed is what the plain loop fed it, plus at most one token after a stop
+        for (k1, s1), (k2, s2) in zip(e1.steps, e2.steps):
+            assert k1 == k2 and set(s1) <= set(s2), case
+
+
 def test_running_ahead_is_chosen_by_generate_when_both_sides_can():
     eng = AheadEngine(2)
     sampler = AheadSampler({i: [30 + i, 40 + i, 2] for i in range(5)}, eng)
