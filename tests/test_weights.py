@@ -150,6 +150,10 @@ def test_sharded_folder(tmp_path):
     src = TensorSource(str(tmp_path))
     assert torch.equal(src.get("a"), t["a"]) and torch.equal(src.get("b"), t["b"])
     assert src.describe("b") == ("BF16", (4,))
+    # the native reader goes file by file
+    into = {"b": torch.zeros(4, dtype=torch.bfloat16), "a": torch.zeros(2, 3)}
+    src.read_into(into, threads=2, chunk_bytes=5)
+    assert torch.equal(into["a"], t["a"]) and torch.equal(into["b"], t["b"])
 
 
 def test_integer_tables_and_kind_check(tmp_path):
