@@ -40,13 +40,16 @@ class LoadedModel:
 
     @classmethod
     def load(cls, model_dir: str, dtype="bfloat16", device="cuda:0",
-             plain_kernels: bool = False) -> "LoadedModel":
+             plain_kernels: bool = False, strict: bool = True) -> "LoadedModel":
         """A folder with config.json and model.safetensors (or sharded safetensors with their
         index).  `dtype`: bfloat16 = the kernels and precisions used for serving; float32 =
-        the whole model in true 32-bit."""
+        the whole model in true 32-bit.  `strict=False` accepts a folder that carries tensors
+        the model does not use (they are listed in `.model.ignored_tensors`); missing tensors
+        and wrong shapes are errors either way.  A folder without `lm_head.weight` gets the
+        embedding table as its output head."""
         config = load_config(model_dir)
         model = cls._build(config, dtype, device, plain_kernels)
-        model.load(TensorSource(model_dir), where=model_dir)
+        model.load(TensorSource(model_dir), where=model_dir, strict=strict)
         return cls(config, model)
 
     @classmethod
@@ -107,13 +110,19 @@ class InferenceSession:
 
     def prefill(self, prompts: Sequence[Sequence[int]], want="last") -> Optional[torch.Tensor]:
         """Start a batch: one prompt per sequence, unequal lengths allowed.  Returns the
-        logits at the wanted places (default: each prompt's last token)."""
+        logits at the wanted places (default: each prompt's last token).  A prompt is run whole,
+        from position 0: a sequence that already holds tokens can only go on one token at a
+        time (`decode_tokens`), so a long prompt cannot be fed in portions and a running
+        sequence cannot take a turn of several tokens at once (the engine refuses such a step
+        with `StepError`; a windowed cache keeps only the newest positions of a prompt, which
+        is right only if the prompt is attended to within the step that brings it)."""
         if self._slots:
             raise RuntimeError("a batch is running; reset() before starting another")
         if len(prompts) == 0:
             raise ValueError("prefill needs at least one prompt")
-        self._slots = [self.engine.open_sequence() for _ in prompts]
         try:
+            for _ in prompts:                    # one by one: reset() gives back what was opened
+                self._slots.append(self.engine.open_sequence())
             return self.engine.step(list(zip(self._slots, prompts)), want=want)
         except Exception:
             self.reset()
@@ -121,7 +130,9 @@ class InferenceSession:
 
     def decode_tokens(self, tokens: Sequence[Optional[int]], want="last") -> Optional[torch.Tensor]:
         """One more token for each sequence of the batch; None ends that sequence (its slot is
-        given back).  Logits come back in the order of the sequences that went on."""
+        given back).  Logits come back in the order of the sequences that went on.  Exactly
+        one token per sequence and call: several tokens for a running sequence are several
+        calls."""
         if len(tokens) != len(self._slots):
             raise ValueError(f"{len(self._slots)} sequences are running, {len(tokens)} tokens given")
         entries, keep = [], []

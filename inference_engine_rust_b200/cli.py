@@ -7,6 +7,8 @@ continuation is printed as ids.  Generation stops at the configuration's EOS id
 the same option, src/bin/chat.rs:49-51).
 
     python -m inference_engine_rust_b200 -m DIR -n 32 "1 415 7 88"
+    python -m inference_engine_rust_b200 -m DIR -n 32 --prompt-file requests.txt     # one request per line, run as batches
+    python -m inference_engine_rust_b200 --random tiny-a --seed 3 -n 8 "1 5 9"       # no folder: seeded random weights
     python -m inference_engine_rust_b200 random-model --config config.json --seed 0 --out DIR
     python -m inference_engine_rust_b200 bench -m DIR [--json] [--runs 5] all --decode-tokens 128
 
@@ -147,33 +149,66 @@ def main(argv: Optional[List[str]] = None) -> int:
         return _random_model(argv[1:])
     if argv and argv[0] == "bench":
         return _bench(argv[1:])
+    from .config.presets import PRESETS
     ap = argparse.ArgumentParser(prog="inference_engine_rust_b200",
                                  description="Greedy or sampled generation from a model folder (token ids in, token ids out)")
-    ap.add_argument("-m", "--model", default="model/mistral-7b-v0.1",
-                    help="model folder with config.json and safetensors (relative to cwd is fine)")
+    ap.add_argument("-m", "--model", default=None,
+                    help="model folder with config.json and safetensors (relative to cwd is fine; "
+                         "default: model/mistral-7b-v0.1 unless --random is given)")
+    ap.add_argument("--random", choices=sorted(PRESETS), default=None, metavar="PRESET",
+                    help="no folder: seeded random weights for a named configuration "
+                         f"({', '.join(sorted(PRESETS))}); --seed seeds them")
     ap.add_argument("-n", "--new-tokens", type=int, default=20, help="how many new tokens to append after the prompt")
     ap.add_argument("--temperature", type=float, default=0.0, help="0 = greedy; > 0 = temperature sampling")
-    ap.add_argument("--seed", type=int, default=0, help="seed of the sampling draws")
+    ap.add_argument("--seed", type=int, default=0, help="seed of the sampling draws (and of --random weights)")
     ap.add_argument("--stop-token", type=int, action="append", default=None,
                     help="stop id (repeatable); default: the configuration's EOS; a negative id = never stop")
-    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
-    ap.add_argument("--max-tokens", type=int, default=None, help="positions the cache holds (default: prompt + new tokens)")
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "bf16", "float32", "fp32"])
+    ap.add_argument("--max-tokens", type=int, default=None,
+                    help="positions the cache holds over all requests (default: what the requests need)")
+    ap.add_argument("--max-context", type=int, default=None,
+                    help="the longest a single sequence may grow (default: the configuration's limit)")
+    ap.add_argument("--max-batch", type=int, default=None, help="most requests that run together")
     ap.add_argument("--plain", action="store_true", help="run the plain reference kernels only")
+    ap.add_argument("--ignore-extra-tensors", action="store_true",
+                    help="accept a folder that carries tensors the model does not use")
+    ap.add_argument("--prompt-file", default=None, metavar="FILE",
+                    help="one request per line (token ids; empty lines and lines starting with # are skipped; "
+                         "'-' = standard input): requests of unequal lengths run together as batches, "
+                         "one output line per request")
     ap.add_argument("prompt", nargs="?", metavar="PROMPT", help="token ids; if omitted, one line is read from stdin")
     a = ap.parse_args(argv)
 
-    if a.prompt is not None:
+    if a.model is not None and a.random is not None:
+        print("error: give either --model or --random, not both", file=sys.stderr)
+        return 2
+    if a.prompt_file is not None and a.prompt is not None:
+        print("error: give either PROMPT or --prompt-file, not both", file=sys.stderr)
+        return 2
+    texts: List[str]
+    if a.prompt_file is not None:
+        try:
+            f = sys.stdin if a.prompt_file == "-" else open(a.prompt_file, "r", encoding="utf-8")
+        except OSError as e:
+            print(f"error: {e}", file=sys.stderr)
+            return 2
+        with f:
+            texts = [ln.strip() for ln in f if ln.strip() and not ln.lstrip().startswith("#")]
+        if not texts:
+            print(f"error: no request in {a.prompt_file}", file=sys.stderr)
+            return 2
+    elif a.prompt is not None:
         if not a.prompt.strip():
             print("error: prompt is empty", file=sys.stderr)                 # src/main.rs:59-61
             return 2
-        text = a.prompt
+        texts = [a.prompt]
     else:
-        text = sys.stdin.readline().rstrip("\r\n")
-    if not text.strip():
-        print("error: no prompt: pass PROMPT or pipe a line on stdin", file=sys.stderr)   # src/main.rs:71-75
-        return 2
+        texts = [sys.stdin.readline().rstrip("\r\n")]
+        if not texts[0].strip():
+            print("error: no prompt: pass PROMPT or pipe a line on stdin", file=sys.stderr)   # src/main.rs:71-75
+            return 2
     try:
-        ids = parse_ids(text)
+        requests = [parse_ids(t) for t in texts]
     except ValueError as e:
         print(f"error: {e}", file=sys.stderr)
         return 2
@@ -182,11 +217,36 @@ def main(argv: Optional[List[str]] = None) -> int:
         return 2
 
     from .api import LoadedModel
-    model = LoadedModel.load(a.model, dtype=a.dtype, plain_kernels=a.plain)
-    max_tokens = a.max_tokens or (len(ids) + a.new_tokens + 64)
-    session = model.session(max_tokens=max_tokens)
+    from .weights import WeightError
+    from .config import ConfigError
+    try:
+        if a.random is not None:
+            from .config.presets import preset
+            model = LoadedModel.random(preset(a.random), seed=a.seed, dtype=a.dtype, plain_kernels=a.plain,
+                                       on_device=True)
+        else:
+            model = LoadedModel.load(a.model or "model/mistral-7b-v0.1", dtype=a.dtype, plain_kernels=a.plain,
+                                     strict=not a.ignore_extra_tensors)
+    except (WeightError, ConfigError, OSError) as e:
+        print(f"error: {e}", file=sys.stderr)
+        return 1
+    for note in model.model.notes:
+        print(f"note: {note}", file=sys.stderr)
+    limit = model.spec.max_position if a.max_context is None else min(a.max_context, model.spec.max_position)
+    if limit <= 0:
+        print("error: --max-context must be positive", file=sys.stderr)
+        return 2
+    # room for every request at its longest, each rounded up to a page, unless told otherwise
+    from .cache import PAGE_TOKENS
+    need = sum(-(-min(len(r) + a.new_tokens, limit) // PAGE_TOKENS) * PAGE_TOKENS for r in requests)
+    session = model.session(max_tokens=a.max_tokens or need, max_seq_len=limit)
     stop = None if a.stop_token is None else [s for s in a.stop_token if s >= 0]
-    out = session.generate([ids], max_new_tokens=a.new_tokens, temperature=a.temperature, seed=a.seed,
-                           stop_ids=stop)[0]
-    print(" ".join(str(t) for t in out))
+    try:
+        outs = session.generate(requests, max_new_tokens=a.new_tokens, temperature=a.temperature, seed=a.seed,
+                                stop_ids=stop, max_batch=a.max_batch)
+    except ValueError as e:                      # a request that cannot fit, an id outside the vocabulary
+        print(f"error: {e}", file=sys.stderr)
+        return 1
+    for out in outs:
+        print(" ".join(str(t) for t in out))
     return 0

@@ -393,7 +393,12 @@ attention_decode_tc_kernel(DecodeTcParams p, IertBatchView b, IertKvView c) {
 // outside [j_min, pos] hold whatever the page held before: their scores are masked as before
 // (a select, so not even NaN gets through), and each warp zeroes its own rows of the values
 // that are out of range before it multiplies by them (0 x NaN would be NaN).  Every wait on a
-// barrier is bounded; when one runs out the kernel records it and goes on to its end.
+// barrier is bounded.  When one runs out, the warp that saw it records the fault and raises a flag
+// in shared memory that every other wait of the CTA polls: the producer stops asking for pages,
+// the consumers leave the loop over pages, one thread then waits (bounded again) until the
+// producer has stopped and every copy it had asked for has landed, and only then does the CTA
+// touch the ring again: it skips the merge and writes an empty partial result (maximum -inf, sum
+// 0; zeros if it is the only part), so that nothing stale is mixed in.
 constexpr int TMA_THREADS = THREADS + 32;
 constexpr int BOX_BYTES = PAGE * 128;                   // 64 positions x 64 dimensions of bf16
 constexpr int BOXES = HD / 64;
@@ -404,12 +409,22 @@ __device__ __forceinline__ uint8_t* swz(uint8_t* tile, int row, int col) {
   return tile + (col >> 6) * BOX_BYTES + row * 128 + ((((col & 63) >> 3) ^ (row & 7)) << 4);
 }
 
+// Bounded wait that gives up early when another warp of the CTA has raised the abort flag.
+__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < (1u << 24); ++i) {
+    if (sm100::mbar_try_wait(bar, parity)) return true;
+    if ((i & 255u) == 255u && *abort_flag) return false;
+  }
+  return false;
+}
+
 __global__ void __launch_bounds__(TMA_THREADS)
 attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                             DecodeTcParams p, IertBatchView b, IertKvView c) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
   __shared__ int red[8];
-  __shared__ __align__(8) uint64_t full_bar[NSTAGE], empty_bar[NSTAGE];
+  __shared__ __align__(8) uint64_t full_bar[NSTAGE], empty_bar[NSTAGE], prod_done;
+  __shared__ volatile int abort_s, armed_s;      // a wait ran out; pages the producer has asked for
   // the swizzle pattern repeats every 1,024 bytes of shared memory: the ring starts on such a boundary
   uint8_t* smem = smem_raw + ((1024u - (sm100::smem_addr(smem_raw) & 1023u)) & 1023u);
   auto k_tile = [&](int i) { return smem + (size_t)(2 * i) * TMA_TILE_BYTES; };
@@ -459,6 +474,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < NSTAGE; ++i) { sm100::mbar_init(&full_bar[i], 1); sm100::mbar_init(&empty_bar[i], WARPS); }
+    sm100::mbar_init(&prod_done, 1);
+    abort_s = 0; armed_s = 0;
     sm100::mbar_fence_init();
   }
   __syncthreads();
@@ -467,7 +484,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     // ---- the producer: page numbers of up to 32 pages at a time, one per lane, then one thread
     // arms the barrier and asks for the boxes
     if (lane == 0) { sm100::tma_prefetch_desc(&map_k); sm100::tma_prefetch_desc(&map_v); }
-    bool waited = false;
+    bool waited = false, stop = false;
+    int armed = 0;
     for (int base = my_lo; base < my_hi; base += 32) {
       const int mine = base + lane;
       int page = -1;
@@ -476,12 +494,17 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         const int pg = base + k, i = pg - my_lo, buf = i % NSTAGE;
         const int pgid = __shfl_sync(0xffffffffu, page, k);
         const bool ok = pgid >= 0 && pgid < c.n_pages;
-        if (lane != 0) continue;
+        if (lane != 0 || stop) continue;
+        if (abort_s) { stop = true; continue; }
         if (!ok) atomicOr(p.err, IERT_ERR_PAGE_RANGE);
         // without the fused cache write the kernel in front wrote the newest row: wait for it first
         if (!fused && !waited && pg == pos / PAGE) { pdl_wait(); waited = true; }
-        if (i >= NSTAGE && !sm100::mbar_wait(&empty_bar[buf], ((i / NSTAGE) - 1) & 1)) {
-          atomicOr(p.err, IERT_ERR_WAIT_EXPIRED);
+        if (i >= NSTAGE && !wait_or_abort(&empty_bar[buf], ((i / NSTAGE) - 1) & 1, &abort_s)) {
+          // the slot may still be in use: nothing more is asked for
+          if (!abort_s) atomicOr(p.err, IERT_ERR_WAIT_EXPIRED);
+          abort_s = 1;
+          stop = true;
+          continue;
         }
         sm100::mbar_expect_tx(&full_bar[buf], 2 * TMA_TILE_BYTES);
         const int row0 = ((ok ? pgid : 0) * c.kv_heads + kvh) * PAGE;
@@ -490,7 +513,13 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
           sm100::tma_load_2d(k_tile(buf) + bx * BOX_BYTES, &map_k, &full_bar[buf], bx * 64, row0);
           sm100::tma_load_2d(v_tile(buf) + bx * BOX_BYTES, &map_v, &full_bar[buf], bx * 64, row0);
         }
+        armed = i + 1;
       }
+    }
+    if (lane == 0) {               // tell the consumers how far the producer came, and that it has stopped
+      armed_s = armed;
+      __threadfence_block();
+      sm100::mbar_arrive(&prod_done);
     }
     return;
   }
@@ -567,8 +596,10 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 
   for (int pg = my_lo; pg < my_hi; ++pg) {
     const int i = pg - my_lo, buf = i % NSTAGE;
-    if (!sm100::mbar_wait(&full_bar[buf], (i / NSTAGE) & 1)) {
-      if (lane == 0) atomicOr(p.err, IERT_ERR_WAIT_EXPIRED);
+    if (!wait_or_abort(&full_bar[buf], (i / NSTAGE) & 1, &abort_s)) {
+      if (lane == 0 && !abort_s) atomicOr(p.err, IERT_ERR_WAIT_EXPIRED);
+      __syncwarp();
+      abort_s = 1;
       break;
     }
     // this warp's 16 positions of the page: rows [16 warp, 16 warp + 16)
@@ -645,6 +676,29 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 
   // ---- merge the four warps in warp order (every page has been used: the ring is free)
   consumer_sync();
+  if (abort_s) {                   // the same for all four warps: every write of the flag precedes the barrier
+    // A wait ran out somewhere in this CTA.  Copies that the producer asked for may still be on
+    // their way into the ring: wait (bounded) until the producer has stopped, then for the last
+    // page asked for in every slot, before the ring is touched or the CTA leaves.
+    if (threadIdx.x == 0) {
+      sm100::mbar_wait(&prod_done, 0);
+      const int armed = armed_s;
+      for (int buf = 0; buf < NSTAGE; ++buf) {
+        if (armed <= buf) continue;
+        const int last = ((armed - 1 - buf) / NSTAGE) * NSTAGE + buf;      // the last page asked for in this slot
+        sm100::mbar_wait(&full_bar[buf], (last / NSTAGE) & 1);
+      }
+    }
+    consumer_sync();
+    // no merge of what the warps hold: an empty partial result (the merge kernel skips it), or zeros
+    if (p.splits == 1) {
+      for (int i = threadIdx.x; i < n_g * HD; i += THREADS)
+        p.out[((size_t)t * p.heads + head0) * HD + i] = __float2bfloat16_rn(0.f);
+    } else if (threadIdx.x < n_g) {
+      pml[(size_t)threadIdx.x * p.splits * 2] = -INFINITY; pml[(size_t)threadIdx.x * p.splits * 2 + 1] = 0.f;
+    }
+    return;
+  }
   l_row += __shfl_xor_sync(0xffffffffu, l_row, 1);
   l_row += __shfl_xor_sync(0xffffffffu, l_row, 2);
   float* o_s = reinterpret_cast<float*>(smem);                 // [WARPS][8][HD]
@@ -716,6 +770,12 @@ __global__ void attention_decode_tc_combine_kernel(DecodeTcParams p, IertBatchVi
 }
 
 }  // namespace
+
+// CTAs of these kernels that one SM holds at once, as the callers' rules for cutting sequences
+// into parts assume it: two (with 128-wide heads the three-page rings of keys and values take
+// half an SM's shared memory; the TMA kernel's 160 threads x 168 registers allow two as well).
+// Smaller heads would fit more, but the rules were measured with two.
+IERT_API int iert_attention_decode_tc_ctas_per_sm() { return 2; }
 
 IERT_API long long iert_attention_decode_tc_scratch_floats(int n_tokens, int heads, int splits) {
   return (long long)n_tokens * heads * splits * (HD + 2);

@@ -301,6 +301,7 @@ def _attention_lib(head_dim: int):
                                                   c_float, c_int, c_void_p, c_void_p]
         lib.iert_attention_prefill_tc.restype = c_int
         lib.iert_attention_prefill_tc_available.restype = c_int
+        lib.iert_attention_decode_tc_ctas_per_sm.restype = c_int
         if os.environ.get("IERT_PDL", "1") == "0":
             lib.iert_set_pdl(0)
         _attn_libs[head_dim] = lib
@@ -334,6 +335,14 @@ def attention_prefill(qkv, out, batch: BatchView, heads: int, kv_heads: int, hea
         raise KernelError("attention_prefill: the launch failed")
     launch_count += 1
     return True
+
+
+def attention_decode_ctas_per_sm(head_dim: int) -> int:
+    """CTAs of the tensor-core decode-attention kernels that one SM holds at once (a fact of those
+    kernels, kept with them)."""
+    if head_dim % 16 or not 16 <= head_dim <= 256:
+        raise KernelError(f"no tensor-core decode attention for head size {head_dim}")
+    return int(_attention_lib(head_dim).iert_attention_decode_tc_ctas_per_sm())
 
 
 def attention_decode_tc(qkv, out, batch: BatchView, kv: KvView, heads: int, scale: float, splits: int,

@@ -156,6 +156,7 @@ __device__ __forceinline__ void pdl_launch_dependents() {
 
 // Defined in runtime.cu.
 int iert_check_launch(const char* what);
+int iert_sm_count_cached();
 extern int iert_pdl_enabled;
 
 // Launch `kernel` with programmatic stream serialization (see pdl_wait) when enabled.

@@ -395,12 +395,14 @@ IERT_API int iert_silu_mul(const void* gu, void* out, int dtype, int n_tokens, i
   if (dtype == IERT_BF16 && inter % 8 == 0 && ((uintptr_t)gu & 15) == 0 && ((uintptr_t)out & 15) == 0) {
     const size_t total8 = total / 8;
     const size_t want = (total8 + threads - 1) / threads;
-    const int blocks = (int)(want < 148 * 32 ? want : 148 * 32);
+    const size_t cap = (size_t)iert_sm_count_cached() * 32;
+    const int blocks = (int)(want < cap ? want : cap);
     launch_dep(silu_mul_bf16x8_kernel, blocks, threads, 0, stream, (const __nv_bfloat16*)gu,
                (__nv_bfloat16*)out, inter, total8);
     return iert_check_launch("silu_mul");
   }
-  const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+  const size_t cap16 = (size_t)iert_sm_count_cached() * 16;
+  const int blocks = (int)((total + threads - 1) / threads < cap16 ? (total + threads - 1) / threads : cap16);
   if (dtype == IERT_F32)
     launch_dep(silu_mul_kernel<float>, blocks, threads, 0, stream, (const float*)gu, (float*)out, inter, total);
   else if (dtype == IERT_BF16)
@@ -424,7 +426,8 @@ IERT_API int iert_add_into(float* residual, const void* y, int y_dtype, long lon
   if (n <= 0) return IERT_OK;
   const int threads = 256;
   const long long want = (n + threads - 1) / threads;
-  const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+  const long long cap = (long long)iert_sm_count_cached() * 16;
+  const int blocks = (int)(want < cap ? want : cap);
   if (y_dtype == IERT_F32)
     add_into_kernel<float><<<blocks, threads, 0, stream>>>(residual, (const float*)y, (size_t)n);
   else if (y_dtype == IERT_BF16)

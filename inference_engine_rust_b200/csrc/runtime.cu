@@ -34,6 +34,20 @@ IERT_API int iert_device_arch() {
   return major * 10 + minor;
 }
 
+// The SM count of the current device, asked once (grids of grid-stride kernels are sized by it).
+int iert_sm_count_cached() {
+  static int n = 0;
+  if (n <= 0) {
+    int dev = 0, v = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess &&
+        cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0)
+      n = v;
+    else
+      return 1;
+  }
+  return n;
+}
+
 IERT_API int iert_sm_count() {
   int dev = 0, n = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return -1;

@@ -16,7 +16,7 @@ from typing import List, Optional, Sequence, Tuple, Union
 import numpy as np
 import torch
 
-from ..cache import Cache, CacheError, CacheFull
+from ..cache import PAGE_TOKENS, Cache, CacheError, CacheFull
 from ..csrc import bindings as B
 from ..parts.base import StepContext
 from .model import Model
@@ -138,14 +138,15 @@ class Engine:
     """A model, its cache, and the step function over them."""
 
     def __init__(self, model: Model, *, max_tokens: int, max_sequences: Optional[int] = None,
-                 max_seq_len: Optional[int] = None, poison_cache: bool = False, use_graphs: bool = True):
+                 max_seq_len: Optional[int] = None, poison_cache: bool = False, use_graphs: bool = True,
+                 page_tokens: int = PAGE_TOKENS):
         if not model.loaded:
             raise ValueError("the model has no weights yet (load() or load_random() first)")
         B.require_device()
         self.model = model
         self.rt = model.rt
         spec = model.spec
-        n_pages = -(-max_tokens // 64)
+        n_pages = -(-max_tokens // page_tokens)
         if max_sequences is None:
             max_sequences = max(1, min(n_pages, 1024))
         if max_seq_len is None:
@@ -153,7 +154,7 @@ class Engine:
         self.cache = Cache(model.cache_requests(), max_tokens=max_tokens,
                            max_seq_len=min(max_seq_len, spec.max_position),
                            max_sequences=max_sequences, dtype=self.rt.dtype, device=self.rt.device,
-                           poison=poison_cache)
+                           page_tokens=page_tokens, poison=poison_cache)
         self._staging = _Staging(self.rt.device)
         self._meta_dev: Optional[torch.Tensor] = None
         self.steps_run = 0
@@ -291,7 +292,7 @@ class Engine:
     def _unequal(self, pos0) -> bool:
         """Do the mixers want this one-token step cut by the sequences' lengths?  Steps of either
         kind replay a graph of their own."""
-        return len(pos0) >= 2 and self.model.cut_by_length(pos0)
+        return len(pos0) >= 2 and self.model.cut_by_length(pos0, self.cache)
 
     @staticmethod
     def _place_device_tokens(dest: torch.Tensor, device_tokens) -> None:

@@ -96,7 +96,7 @@ def run_batch_ahead(engine, sampler, prompts: Sequence[Sequence[int]], request_i
         for res in results:
             res.finish_reason = "length"
         return results
-    slots = [engine.open_sequence() for _ in prompts]
+    slots: List[Optional[int]] = []          # opened one by one inside the try: whatever was opened is given back
 
     def goes_on_if_kept(res: GenerationResult) -> bool:
         """Will the sequence run its next token, if that token is no stop token?"""
@@ -104,6 +104,8 @@ def run_batch_ahead(engine, sampler, prompts: Sequence[Sequence[int]], request_i
         return n < max_new_tokens and res.prompt_len + n <= max_seq_len
 
     try:
+        for _ in prompts:
+            slots.append(engine.open_sequence())
         layout = list(range(len(prompts)))         # batch indices in the row order of `chosen_dev`
         logits = engine.step([(slots[i], list(prompts[i])) for i in layout], want="last")
         step_no = 0
@@ -146,9 +148,11 @@ def run_batch(engine, sampler: Callable, prompts: Sequence[Sequence[int]], reque
         for res in results:
             res.finish_reason = "length"
         return results
-    slots = [engine.open_sequence() for _ in prompts]
+    slots: List[Optional[int]] = []          # opened one by one inside the try: whatever was opened is given back
     live = list(range(len(prompts)))           # indices into this batch, in batch order
     try:
+        for _ in prompts:
+            slots.append(engine.open_sequence())
         logits = engine.step([(slots[i], list(prompts[i])) for i in live], want="last")
         step_no = 0
         while live:

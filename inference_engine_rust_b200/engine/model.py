@@ -41,6 +41,8 @@ class Model:
         self.embedding: Optional[torch.Tensor] = None
         self.lm_head: Optional[Linear] = None
         self.loaded = False
+        self.ignored_tensors: List[str] = []
+        self.notes: List[str] = []       # what loading decided on its own (tied head, ignored tensors)
 
     # ---- weights ------------------------------------------------------------------------
     def expected_tensors(self) -> Dict[str, TensorSpec]:
@@ -61,12 +63,28 @@ class Model:
                 out[ls.ffn_prefix + local] = ts
         return out
 
-    def load(self, source, where: str = "weights") -> None:
+    def load(self, source, where: str = "weights", strict: bool = True) -> None:
         """Check `source` against the expected tensors (one error for everything that is
-        wrong), then hand each part its tensors."""
+        wrong), then hand each part its tensors.
+
+        A source without the output head's tensor ties the head to the embedding table, as
+        the reference does whenever `output.weight` is absent
+        (src/model_weights/names.rs:300-310), whatever the configuration's flag says.
+        `strict=False` accepts tensors the model does not know (a checkpoint that carries
+        extras) and lists them in `self.ignored_tensors`."""
         expected = self.expected_tensors()
-        check_source(expected, source, where)
         rt, spec = self.rt, self.spec
+        head_name = spec.lm_head_name
+        if head_name is not None and head_name not in set(source.names()):
+            expected.pop(head_name)
+            head_name = None
+            self.notes.append(f"{where}: no {spec.lm_head_name!r}; the output head is tied to "
+                              f"{spec.embedding_name!r}")
+        self.ignored_tensors = check_source(expected, source, where, strict=strict)
+        if self.ignored_tensors:
+            self.notes.append(f"{where}: {len(self.ignored_tensors)} tensor(s) the model does not use were "
+                              f"ignored: " + ", ".join(self.ignored_tensors[:8])
+                              + (" ..." if len(self.ignored_tensors) > 8 else ""))
 
         # every tensor to the device first (files: one pass of the native reader per file), then
         # each part takes its own; a part that fuses matrices lets go of the separate ones
@@ -77,9 +95,9 @@ class Model:
 
         self.embedding = get(spec.embedding_name)
         self.final_norm.load({"weight": get(spec.final_norm_name)})
-        head = self.embedding if spec.lm_head_name is None else get(spec.lm_head_name)
+        head = self.embedding if head_name is None else get(head_name)
         self.lm_head = Linear(head, rt)
-        if spec.lm_head_name is None and self.lm_head.weight.dtype == self.embedding.dtype:
+        if head_name is None and self.lm_head.weight.dtype == self.embedding.dtype:
             self.embedding = self.lm_head.weight          # tied: one copy
         for ls, (norm1, mixer, norm2, ffn) in zip(spec.layers, self._layer_parts):
             norm1.load({"weight": get(ls.mixer_norm_name)})
@@ -128,21 +146,23 @@ class Model:
         return total
 
     # ---- forward --------------------------------------------------------------------------
-    def cut_by_length(self, pos0) -> bool:
-        """Does any mixer want this one-token step (positions of the live sequences) cut by length?"""
+    def cut_by_length(self, pos0, cache) -> bool:
+        """Does any mixer want this one-token step (positions of the live sequences) cut by length?
+        Each is asked with the view of the cache that its layer reads."""
         if self._cut_askers is None:
             # every mixer that has the (optional) method, one per `cut_by_length_key()` where mixers
             # say that their answers are the same (layers of equal shape): asked every step
             seen, self._cut_askers = set(), []
-            for parts in self._layer_parts:
-                ask = getattr(parts[1], "cut_by_length", None)
+            for pos, e in enumerate(self.spec.schedule):
+                mixer = self._layer_parts[e.layer][1]
+                ask = getattr(mixer, "cut_by_length", None)
                 if ask is None:
                     continue
-                key = getattr(parts[1], "cut_by_length_key", lambda m=parts[1]: id(m))()
+                key = getattr(mixer, "cut_by_length_key", lambda m=mixer: id(m))()
                 if key not in seen:
                     seen.add(key)
-                    self._cut_askers.append(ask)
-        return any(ask(pos0) for ask in self._cut_askers)
+                    self._cut_askers.append((ask, self.spec.cache_entry(pos)))
+        return any(ask(pos0, cache.layer_view(entry)) for ask, entry in self._cut_askers)
 
     def forward(self, ctx: StepContext, tokens: torch.Tensor, cache, logit_rows: Optional[torch.Tensor],
                 n_logit_rows: int, logits_out: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:

@@ -73,13 +73,14 @@ class Attention(Mixer):
         return self.qkv.nbytes() + self.o.nbytes()
 
     def cut_by_length_key(self):
-        return ("attention", self.heads, self.kv_heads, self.window, self.rt.fast)
+        return ("attention", self.heads, self.kv_heads, self.head_dim, self.window, self.rt.fast)
 
-    def cut_by_length(self, pos0) -> bool:
-        if not self.rt.fast:
+    def cut_by_length(self, pos0, cache_view) -> bool:
+        if not self.rt.fast or cache_view is None:
             return False
         from . import fast_attention
-        return fast_attention.wants_length_cut(pos0, self.kv_heads, self.heads // self.kv_heads, self.window)
+        return fast_attention.wants_length_cut(pos0, self.kv_heads, self.heads // self.kv_heads, self.window,
+                                               cache_view.group.page_tokens, self.head_dim)
 
     def forward(self, xn, residual, ctx: StepContext, cache_view, writes_cache: bool) -> None:
         rt, ws, T = self.rt, self.rt.workspace, ctx.n_tokens

@@ -169,8 +169,9 @@ class Mixer(Part):
     def cache_request(self) -> CacheRequest:
         return None
 
-    def cut_by_length(self, pos0) -> bool:
-        """Asked once per one-token step with the positions of the live sequences: would this
+    def cut_by_length(self, pos0, cache_view) -> bool:
+        """Asked once per one-token step with the positions of the live sequences and the view of
+        the cache that this mixer's layer reads: would this
         mixer rather cut its work by the sequences' lengths than evenly?  The engine replays a
         captured step of its own for either answer and passes the answer on as
         `StepContext.unequal_lengths`.  The default is no.  Mixers whose answers are always the

@@ -59,11 +59,17 @@ _FLOAT_NAMES = {"F32", "BF16", "F16", "F64"}
 _INT_NAMES = {"I64", "I32", "I16", "I8", "U8"}
 
 
-def check_source(expected: Mapping[str, TensorSpec], source: TensorSource, where: str) -> None:
+def check_source(expected: Mapping[str, TensorSpec], source: TensorSource, where: str,
+                 strict: bool = True):
+    """Compare what the model expects with what `source` holds; everything that is wrong comes
+    in ONE `WeightError`.  `strict` (the default): a tensor the model does not know is an
+    error.  Not strict: such tensors are left alone, as the reference loads only the names it
+    resolves (src/model_weights/names.rs:224-276), and their names are returned."""
     have = set(source.names())
     want = set(expected)
     missing = want - have
-    unexpected = have - want
+    extra = have - want
+    unexpected = extra if strict else set()
     wrong_shape, wrong_kind = [], []
     for name in want & have:
         dt, shape = source.describe(name)
@@ -75,6 +81,7 @@ def check_source(expected: Mapping[str, TensorSpec], source: TensorSource, where
             wrong_kind.append((name, dt, "floating point"))
     if missing or unexpected or wrong_shape or wrong_kind:
         raise WeightError(where, missing, unexpected, wrong_shape, wrong_kind)
+    return sorted(extra)
 
 
 def stored_dtype_policy(t: torch.Tensor, run_dtype: torch.dtype) -> torch.dtype:

@@ -80,7 +80,8 @@ def prompts_for(cfg: dict, lengths: Sequence[int], seed: int = 0) -> List[List[i
 #   value, so the bound is stated in units of the largest logit of the tensor:
 #   every value within 2^-6 * (max|plain| + |plain|), and the root-mean-square error within
 #   2^-8 * max|plain|.  A fault of the cache or the batch (a wrong key, a wrong position, a
-#   stale slot) moves logits by tenths of that scale.
+#   stale slot) moves logits by tenths of that scale: tests/test_tolerance_teeth.py plants such
+#   faults in the plain implementation and checks that this bound refuses each of them.
 TOL = {
     "float32": dict(atol=2e-4, rtol=2e-4),
     "bfloat16": dict(scaled=2.0 ** -6, rms=2.0 ** -8),

@@ -111,9 +111,10 @@ def rope(vec: Tensor, base: float, pos: int, head_dim: int, rotary_dim: int,
 
 
 def rope_sequence(x: Tensor, base: float, head_dim: int, rotary_dim: int, pairing: str,
-                  first_pos: int = 0) -> Tensor:
+                  first_pos: int = 0, positions: Optional[Sequence[int]] = None) -> Tensor:
     """`rope` on every head of every row of x [T, heads, head_dim]; row t is at position
-    first_pos + t (prefill: the row index, src/layers/attention.rs:314-343)."""
+    first_pos + t (prefill: the row index, src/layers/attention.rs:314-343).  `positions`
+    overrides that (only the tests that plant a fault use it)."""
     out = x.clone().to(torch.float32)
     half = rotary_dim // 2
     if pairing == "interleaved":
@@ -123,7 +124,7 @@ def rope_sequence(x: Tensor, base: float, head_dim: int, rotary_dim: int, pairin
         i0 = torch.arange(half)
         i1 = i0 + half
     for t in range(x.shape[0]):
-        ang = rope_angles(first_pos + t, base, rotary_dim)
+        ang = rope_angles(first_pos + t if positions is None else positions[t], base, rotary_dim)
         cos, sin = torch.cos(ang), torch.sin(ang)
         a, b = x[t][:, i0].to(torch.float32), x[t][:, i1].to(torch.float32)
         out[t][:, i0] = a * cos - b * sin
@@ -149,20 +150,23 @@ def attention_layer(xn: Tensor, wq: Tensor, wk: Tensor, wv: Tensor, wo: Tensor, 
                     kv_heads: int, head_dim: int, rope_theta: float, window: Optional[int],
                     pairing: str = "half", rotary_dim: Optional[int] = None,
                     scale: Optional[float] = None, rnd: Round = no_rounding,
-                    return_parts: bool = False):
+                    return_parts: bool = False, kv_head_of: Optional[Callable[[int], int]] = None,
+                    positions: Optional[Sequence[int]] = None):
     """Attention of one whole sequence starting at position 0.
     Projections src/layers/attention.rs:245-254; rotation of every Q and K head at its row
     index :314-343; scores over j in [j_min, pos] with j_min = pos - (window - 1), scaled by
     1/sqrt(head_dim), softmax, weighted values :357-415 (grouped heads: kv_head =
-    head / (heads / kv_heads), :372); output projection :417-421."""
+    head / (heads / kv_heads), :372); output projection :417-421.
+    `kv_head_of` and `positions` replace the head grouping and the row positions; they exist
+    for the tests that plant a fault and check that the tolerances catch it."""
     T = xn.shape[0]
     rotary_dim = head_dim if rotary_dim is None else rotary_dim
     scale = 1.0 / math.sqrt(head_dim) if scale is None else scale
     q = rnd(matmul(xn, wq)).view(T, heads, head_dim)
     k = rnd(matmul(xn, wk)).view(T, kv_heads, head_dim)
     v = rnd(matmul(xn, wv)).view(T, kv_heads, head_dim)
-    q_r = rope_sequence(q, rope_theta, head_dim, rotary_dim, pairing)
-    k_r = rope_sequence(k, rope_theta, head_dim, rotary_dim, pairing)
+    q_r = rope_sequence(q, rope_theta, head_dim, rotary_dim, pairing, positions=positions)
+    k_r = rope_sequence(k, rope_theta, head_dim, rotary_dim, pairing, positions=positions)
     q_r, k_r = rnd(q_r), rnd(k_r)
     group = heads // kv_heads
     out = torch.zeros(T, heads, head_dim, dtype=torch.float32)
@@ -172,7 +176,7 @@ def attention_layer(xn: Tensor, wq: Tensor, wk: Tensor, wv: Tensor, wo: Tensor, 
     if window is not None:
         visible = visible & (cols >= rows - (window - 1))
     for h in range(heads):
-        kvh = h // group
+        kvh = h // group if kv_head_of is None else kv_head_of(h)
         scores = (q_r[:, h] @ k_r[:, kvh].t()) * scale
         scores = scores.masked_fill(~visible, float("-inf"))
         p = softmax(scores)
@@ -191,7 +195,8 @@ def ffn_layer(xn: Tensor, w_gate: Tensor, w_up: Tensor, w_down: Tensor, rnd: Rou
     return matmul(rnd(swiglu(g, u)), w_down)
 
 
-def block(x: Tensor, cfg: dict, w: Dict[str, Tensor], layer: int, rnd: Round = no_rounding) -> Tensor:
+def block(x: Tensor, cfg: dict, w: Dict[str, Tensor], layer: int, rnd: Round = no_rounding,
+          **attention_options) -> Tensor:
     """x += attention(norm(x)); x += ffn(norm(x)).  src/layers/block.rs:19-24;
     residual on the un-normed input src/layers/attention.rs:757-759, src/layers/ffn.rs:113-116."""
     p = f"model.layers.{layer}."
@@ -202,14 +207,15 @@ def block(x: Tensor, cfg: dict, w: Dict[str, Tensor], layer: int, rnd: Round = n
         w[p + "self_attn.v_proj.weight"], w[p + "self_attn.o_proj.weight"],
         heads=cfg["num_attention_heads"], kv_heads=cfg["num_key_value_heads"],
         head_dim=cfg["head_dim"], rope_theta=cfg["rope_theta"], window=cfg.get("sliding_window"),
-        rnd=rnd)
+        rnd=rnd, **attention_options)
     xn = rnd(rmsnorm(x, w[p + "post_attention_layernorm.weight"], eps))
     x = x + ffn_layer(xn, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"],
                       w[p + "mlp.down_proj.weight"], rnd)
     return x
 
 
-def forward(cfg: dict, w: Dict[str, Tensor], ids: Sequence[int], rnd: Round = no_rounding) -> Tensor:
+def forward(cfg: dict, w: Dict[str, Tensor], ids: Sequence[int], rnd: Round = no_rounding,
+            **attention_options) -> Tensor:
     """Logits [len(ids), vocab] of one whole sequence.  Embedding src/engine/embed.rs:104-138;
     layer loop src/engine/runtime.rs:27-31; final norm and output head :89-107 (there for the
     last row only; here for every row); tied output src/model_weights/names.rs:300-310."""
@@ -217,7 +223,7 @@ def forward(cfg: dict, w: Dict[str, Tensor], ids: Sequence[int], rnd: Round = no
         raise ValueError("empty prompt")                      # src/engine/embed.rs:109-111
     x = embed(w["model.embed_tokens.weight"], ids, 1.0)
     for layer in range(cfg["num_hidden_layers"]):
-        x = block(x, cfg, w, layer, rnd)
+        x = block(x, cfg, w, layer, rnd, **attention_options)
     hn = rnd(rmsnorm(x, w["model.norm.weight"], cfg["rms_norm_eps"]))
     head = w["model.embed_tokens.weight"] if cfg.get("tie_word_embeddings") else w["lm_head.weight"]
     return matmul(hn, head)

@@ -272,3 +272,22 @@ def test_no_device_and_no_compiler_fail_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(build.os.path, "isfile", lambda p: False if str(p).endswith("nvcc") else real(p))
     with pytest.raises(build.BuildError, match="nvcc not found"):
         build.find_nvcc()
+
+
+@pytest.mark.parametrize("run", [run_batch, run_batch_ahead])
+def test_slots_opened_before_a_failed_open_are_given_back(run):
+    """Fewer free slots than prompts: the open that fails must not leak the slots opened before it."""
+    class Full(Exception):
+        pass
+
+    class TwoSlots(AheadEngine):
+        def open_sequence(self):
+            if not self.free:
+                raise Full("no slot is free")
+            return super().open_sequence()
+
+    eng = TwoSlots(2)
+    sampler = AheadSampler({0: [5], 1: [6], 2: [7]}, eng)
+    with pytest.raises(Full):
+        run(eng, sampler, [[1], [2], [3]], [0, 1, 2], 4, set(), 100)
+    assert eng.held == {} and sorted(eng.free) == [0, 1] and eng.steps == []

@@ -199,6 +199,74 @@ def test_command_line(loaded):
     assert bad.returncode != 0 and "prompt" in bad.stderr.lower()
 
 
+def test_command_line_runs_a_file_of_unequal_requests(loaded, tmp_path):
+    """`--prompt-file`: one request per line becomes one generation call, whose batches hold
+    requests of unequal lengths; one output line per request, in order.  With `--max-batch 2` the
+    three requests run as two batches one after the other (slots used again)."""
+    folder, model, w = loaded["B"]
+    cfg = TINY["B"]
+    prompts = prompts_for(cfg, [7, 1, 19], seed=11)
+    want = [P.generate_greedy(cfg, w, p, 6) for p in prompts]
+    f = tmp_path / "requests.txt"
+    f.write_text("# three requests\n" + "\n".join(",".join(map(str, p)) for p in prompts) + "\n\n")
+    base = [sys.executable, "-m", "inference_engine_rust_b200", "-m", folder, "--dtype", "float32", "-n", "6",
+            "--stop-token", "-1"]
+    for extra in ([], ["--max-batch", "2"]):
+        out = subprocess.run(base + extra + ["--prompt-file", str(f)], cwd=ROOT, capture_output=True, text=True, timeout=300)
+        assert out.returncode == 0, out.stderr
+        lines = out.stdout.strip().splitlines()
+        assert [ln.split() for ln in lines] == [[str(t) for t in r] for r in want]
+    # --max-context ends a request when its sequence is full: of 22 positions the prompt takes 19, three
+    # new tokens are run, and the fourth is still chosen (from the last position's logits) and kept
+    out = subprocess.run(base + ["--max-context", "22", "--prompt-file", str(f)], cwd=ROOT, capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr
+    lines = [ln.split() for ln in out.stdout.strip().splitlines()]
+    assert lines[0] == [str(t) for t in want[0]] and lines[2] == [str(t) for t in want[2][:4]]
+    both = subprocess.run(base + ["--prompt-file", str(f), "1 2"], cwd=ROOT, capture_output=True, text=True, timeout=300)
+    assert both.returncode == 2 and "either" in both.stderr
+
+
+def test_command_line_random_preset_and_lenient_loading(loaded, tmp_path):
+    """`--random PRESET --seed N` needs no folder and gives the tokens of the same seeded weights
+    written to a folder; a folder with a tensor the model does not use is refused unless
+    `--ignore-extra-tensors` is given; a folder without the output head runs with the tied one."""
+    from safetensors.torch import load_file, save_file
+    from inference_engine_rust_b200 import write_random_model
+    from inference_engine_rust_b200.config import preset
+    cfg = preset("tiny-a")
+    d = str(tmp_path / "tiny_a")
+    write_random_model(d, cfg, seed=9, dtype="bfloat16", std=0.02)
+    prompt = "5 9 200 31"
+    tail = ["--dtype", "float32", "-n", "5", "--stop-token", "-1", prompt]
+    run = lambda args: subprocess.run([sys.executable, "-m", "inference_engine_rust_b200"] + args, cwd=ROOT,
+                                      capture_output=True, text=True, timeout=300)
+    a = run(["--random", "tiny-a", "--seed", "9"] + tail)
+    assert a.returncode == 0, a.stderr
+    assert len(a.stdout.split()) == 5
+    assert run(["--random", "tiny-a", "--seed", "9"] + tail).stdout == a.stdout, "same seed, same tokens"
+    assert run(["--random", "tiny-c"] + tail).returncode == 2               # no such preset
+    assert run(["--random", "tiny-a", "-m", d] + tail).returncode == 2      # one or the other
+    # extras
+    t = load_file(os.path.join(d, "model.safetensors"))
+    want = P.generate_greedy(cfg, {k: v.float() for k, v in t.items()}, [5, 9, 200, 31], 5)
+    t["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(8)
+    save_file(t, os.path.join(d, "model.safetensors"))
+    strict = run(["-m", d] + tail)
+    assert strict.returncode == 1 and "unexpected (1)" in strict.stderr and "rotary_emb" in strict.stderr
+    lenient = run(["-m", d, "--ignore-extra-tensors"] + tail)
+    assert lenient.returncode == 0, lenient.stderr
+    assert lenient.stdout.split() == [str(x) for x in want] and "ignored" in lenient.stderr
+    # no output head in the folder: tied to the embedding
+    del t["lm_head.weight"], t["model.layers.0.self_attn.rotary_emb.inv_freq"]
+    save_file(t, os.path.join(d, "model.safetensors"))
+    tied = run(["-m", d] + tail)
+    assert tied.returncode == 0, tied.stderr
+    w_tied = {k: v.float() for k, v in t.items()}
+    w_tied["lm_head.weight"] = w_tied["model.embed_tokens.weight"]
+    assert tied.stdout.split() == [str(x) for x in P.generate_greedy(cfg, w_tied, [5, 9, 200, 31], 5)]
+    assert "tied" in tied.stderr
+
+
 def test_bench_subcommand(loaded, capsys):
     """The reference's bench suite (cold start, interactive TTFT, decode throughput) through the
     command line's own entry, on a tiny model; the decode loop it times is the greedy loop."""

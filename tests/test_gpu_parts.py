@@ -242,7 +242,7 @@ def plain_toy(cfg: ToyConfig, w, ids):
                 for h in range(4):
                     s = (q[:, h] @ src["k"][:, h // 2].t()) * 0.25
                     out[:, h] = P.softmax(s.masked_fill(~mask, float("-inf"))) @ src["v"][:, h // 2]
-                y = P.matmul(out.reshape(T, 64), w[p + "mix.o_proj.weight"])
+                y = P.matmul(out.reshape(T, 64, 128), w[p + "mix.o_proj.weight"])
             x = x + y
         xn = P.rmsnorm(x, w[p + "n2.weight"], 1e-5)
         x = x + P.ffn_layer(xn, w[p + "ffn.gate_proj.weight"], w[p + "ffn.up_proj.weight"], w[p + "ffn.down_proj.weight"])
@@ -549,11 +549,11 @@ def test_attention_asks_for_a_cut_by_length_when_it_pays():
     from inference_engine_rust_b200.parts import fast_attention as FA
     from inference_engine_rust_b200.csrc import bindings as B
     slots = 2 * B.sm_count()
-    assert not FA.wants_length_cut([2047] * 8, 8, 4, None)
-    assert not FA.wants_length_cut([2047], 8, 4, None)
-    assert FA.wants_length_cut([8191] + [1023] * 7, 8, 4, None)
-    assert not FA.wants_length_cut([8191] + [1023] * 7, 8, 4, 1024), "a window makes them equal"
+    assert not FA.wants_length_cut([2047] * 8, 8, 4, None, 64, 128)
+    assert not FA.wants_length_cut([2047], 8, 4, None, 64, 128)
+    assert FA.wants_length_cut([8191] + [1023] * 7, 8, 4, None, 64, 128)
+    assert not FA.wants_length_cut([8191] + [1023] * 7, 8, 4, 1024, 64, 128), "a window makes them equal"
     full = slots // 8                                   # sequences whose CTAs fill the slots exactly
-    assert not FA.wants_length_cut([2047] * full, 8, 4, None)
-    assert FA.wants_length_cut([2047] * (full + full // 3), 8, 4, None), "one and a third rounds"
-    assert not FA.wants_length_cut([2047] * (2 * full - 2), 8, 4, None), "almost two full rounds"
+    assert not FA.wants_length_cut([2047] * full, 8, 4, None, 64, 128)
+    assert FA.wants_length_cut([2047] * (full + full // 3), 8, 4, None, 64, 128), "one and a third rounds"
+    assert not FA.wants_length_cut([2047] * (2 * full - 2), 8, 4, None, 64, 128), "almost two full rounds"

@@ -219,3 +219,47 @@ def test_fetch_many_without_a_device_goes_tensor_by_tensor(tmp_path):
     got = fetch_many(src, names, torch.float32, "cpu")
     for n in names:
         assert got[n].dtype == torch.float32 and torch.equal(got[n], src.get(n).float())
+
+
+def test_a_folder_without_the_output_head_ties_it_to_the_embedding(tmp_path):
+    """src/model_weights/names.rs:300-310: no `output.weight` means the embedding table is the head,
+    whatever the configuration's flag says."""
+    d = make_folder(tmp_path, TINY_A, seed=4)
+    src = TensorSource(d)
+    tensors = {n: src.get(n).clone() for n in src.names() if n != "lm_head.weight"}
+    bare = tmp_path / "no_head"
+    bare.mkdir()
+    write_safetensors(str(bare / "model.safetensors"), tensors)
+    m = cpu_model(TINY_A)                                  # tie_word_embeddings is false in Tiny A
+    m.load(TensorSource(str(bare)), where="no_head")
+    assert m.lm_head.weight is m.embedding
+    assert torch.equal(m.lm_head.weight, tensors["model.embed_tokens.weight"])
+    assert any("tied" in n for n in m.notes)
+    # the untouched folder keeps its own head
+    m2 = cpu_model(TINY_A)
+    m2.load(src)
+    assert torch.equal(m2.lm_head.weight, src.get("lm_head.weight")) and m2.notes == []
+
+
+def test_extra_tensors_are_an_error_unless_asked_otherwise(tmp_path):
+    d = make_folder(tmp_path, TINY_B, seed=4)
+    src = TensorSource(d)
+    tensors = {n: src.get(n).clone() for n in src.names()}
+    tensors["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(16)
+    tensors["optimizer.step"] = torch.zeros(1)
+    del tensors["model.norm.weight"]
+    extra = tmp_path / "extra"
+    extra.mkdir()
+    write_safetensors(str(extra / "model.safetensors"), tensors)
+    with pytest.raises(WeightError) as e:                  # not strict: extras pass, what is missing does not
+        cpu_model(TINY_B).load(TensorSource(str(extra)), strict=False)
+    assert e.value.missing == ["model.norm.weight"] and e.value.unexpected == []
+    tensors["model.norm.weight"] = src.get("model.norm.weight").clone()
+    write_safetensors(str(extra / "model.safetensors"), tensors)
+    with pytest.raises(WeightError) as e:
+        cpu_model(TINY_B).load(TensorSource(str(extra)))
+    assert e.value.unexpected == ["model.layers.0.self_attn.rotary_emb.inv_freq", "optimizer.step"]
+    m = cpu_model(TINY_B)
+    m.load(TensorSource(str(extra)), strict=False)
+    assert m.ignored_tensors == ["model.layers.0.self_attn.rotary_emb.inv_freq", "optimizer.step"]
+    assert m.loaded and any("ignored" in n for n in m.notes)
