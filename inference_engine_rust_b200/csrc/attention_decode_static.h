@@ -22,7 +22,11 @@
 //     is refused with IERT_STATIC_SCRATCH_TOO_SMALL and launches nothing; ask for fewer splits
 //     or use `iert_attention_decode` with a buffer of your own.
 //   * The first call on each device looks up the array's device address (with that device
-//     current) and remembers it.  Make that first call outside any stream capture.
+//     current) and remembers it.  Make that first call outside any stream capture.  It may also
+//     be the moment at which the CUDA runtime loads this library's code, the 8 MiB array
+//     included, onto the device (module loading is lazy by default), so device memory in use can
+//     still grow during that one call: a host that must not see that later makes one call at
+//     start-up.  From the second call on nothing is loaded or looked up.
 //   * All calls on one device share the one array.  Nothing in it has to be cleared between
 //     calls, because every element a call reads was written earlier in the same call; but two
 //     calls whose kernels can overlap on the GPU (different streams without an ordering

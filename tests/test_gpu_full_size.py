@@ -1,18 +1,24 @@
 """The engine at Mistral-7B layer sizes (hidden 4096, 32 heads / 8 kv heads of 128, feed-forward
 14336, vocabulary 32000; two layers so that it stays small): the kernels run the shapes they
 run in production (k of 4096 and 14336, split-K, 128-wide heads, four query heads per kv
-head).  The plain implementation on the CPU is out of reach at this size, so the oracle here is
-the engine's own true 32-bit path (plain FFMA kernels), which the tiny-model tests pin to the
-plain implementation:
+head).
 
+  * the plain implementation on the CPU, on the same weights (made on the device, copied back),
+    for the 37-token and the 300-token request: the engine's float32 path against it at the
+    float32 tolerance, the bfloat16 engine (tcgen05 projections and prompt attention, TMA decode
+    attention) against the plain implementation with bfloat16 rounding;
   * float32: the logits of a request do not depend on how its tokens are cut into steps or on
     what else is in the batch;
   * bfloat16 (tensor-core kernels) against float32 on the same bf16-rounded weights.
+
+The reference's like checks: logits of a prompt against an independent implementation with
+difference statistics (tests/prefill_smoke.rs:99-143, tests/common/llama_logits_helpers.rs:16-89).
 """
 import pytest
 import torch
 
 from helpers import compare
+from plain import mistral_plain as P
 
 pytestmark = pytest.mark.gpu
 
@@ -38,6 +44,20 @@ def models():
     g = torch.Generator().manual_seed(3)
     prompts = [torch.randint(0, CFG["vocab_size"], (n,), generator=g).tolist() for n in LENGTHS]
     return bf, LoadedModel(bf.config, f32), prompts
+
+
+@pytest.fixture(scope="module")
+def plain_logits(models):
+    """Logits of the plain implementation for requests 1 (37 tokens) and 0 (300 tokens: the window
+    of 160 binds), without rounding and with the rounding of a bfloat16 engine."""
+    from inference_engine_rust_b200.weights import RandomSource
+    bf, f32, prompts = models
+    src = RandomSource(f32.model.expected_tensors(), 5, 0.02, dtype=torch.bfloat16, device="cuda:0")
+    w = {name: src.get(name).float().cpu() for name in src.names()}
+    out = {}
+    for i in (1, 0):
+        out[i] = (P.forward(CFG, w, prompts[i], P.no_rounding), P.forward(CFG, w, prompts[i], P.bf16_rounding))
+    return out
 
 
 def run_whole(model, prompts):
@@ -74,6 +94,25 @@ def run_batched_with_tails(model, prompts, tails):
     return [torch.cat(g) for g in got]
 
 
+def test_float32_matches_the_plain_implementation(models, plain_logits):
+    bf, f32, prompts = models
+    whole = run_whole(f32, prompts)
+    for i, (exact, _) in plain_logits.items():
+        compare(whole[i], exact, "float32", f"7B sizes, float32 whole against the plain implementation, request {i}")
+    cut = run_batched_with_tails(f32, prompts, tails=[32, 5, 17])
+    for i, (exact, _) in plain_logits.items():
+        compare(cut[i], exact, "float32", f"7B sizes, float32 batched and decoded against the plain implementation, request {i}")
+
+
+def test_bfloat16_matches_the_plain_implementation(models, plain_logits):
+    bf, f32, prompts = models
+    whole = run_whole(bf, prompts)
+    cut = run_batched_with_tails(bf, prompts, tails=[32, 5, 17])
+    for i, (_, rounded) in plain_logits.items():
+        compare(whole[i], rounded, "bfloat16", f"7B sizes, bfloat16 whole against the plain implementation, request {i}")
+        compare(cut[i], rounded, "bfloat16", f"7B sizes, bfloat16 batched and decoded against the plain implementation, request {i}")
+
+
 def test_float32_does_not_depend_on_the_cutting(models):
     bf, f32, prompts = models
     whole = run_whole(f32, prompts)
@@ -105,3 +144,26 @@ def test_bfloat16_runs_are_bitwise_repeatable(models):
     w1, w2 = run_whole(bf, prompts), run_whole(bf, prompts)
     for i, (x, y) in enumerate(zip(w1, w2)):
         assert torch.equal(x, y), f"request {i}: two identical prompt runs differ"
+
+
+def test_a_prompt_of_2400_tokens_then_three_tokens(models):
+    """2,400 tokens in one step: the down projection's activations (2,400 x 14,336) exceed 64 MB, so
+    its token tiles are walked in groups, the residual adds go through TMA, and the prompt spans 38
+    pages; then three tokens one by one.  bfloat16 against the float32 path at chosen places."""
+    bf, f32, prompts = models
+    g = torch.Generator().manual_seed(17)
+    prompt = torch.randint(0, CFG["vocab_size"], (2400,), generator=g).tolist()
+    tail = torch.randint(0, CFG["vocab_size"], (3,), generator=g).tolist()
+    places = [0, 1, 63, 64, 127, 128, 255, 256, 1023, 1024, 2047, 2399]
+    out = {}
+    for name, model in (("float32", f32), ("bfloat16", bf)):
+        eng = model.session(max_tokens=64 * 40, max_sequences=1, poison_cache=True).engine
+        s = eng.open_sequence()
+        rows = [eng.step([(s, prompt)], want=[places]).clone()]
+        for t in tail:
+            rows.append(eng.step([(s, [t])], want="last").clone())
+        eng.check_device()
+        eng.close_sequence(s)
+        eng.cache.check()
+        out[name] = torch.cat(rows)
+    compare(out["bfloat16"], out["float32"], "bfloat16", "7B sizes, 2,400-token prompt and three tokens")

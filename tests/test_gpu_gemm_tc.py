@@ -97,6 +97,36 @@ def test_residual_add_over_many_tokens(M, N, K):
     assert int(sc.counters.abs().sum()) == 0, "a tile's flag was left raised"
 
 
+def test_token_tiles_walked_in_groups():
+    """Activations above 64 MB: the token tiles are walked in groups sized for the L2 (another
+    order of the tiles, the same products).  Weight-major with the residual add (k of 14,336, the
+    last wave cut into parts), token-major store, and the gated form; repeatable to the bit."""
+    from inference_engine_rust_b200.csrc import bindings as B
+    a = run(2400, 256, 14336, B.GEMM_ADD_RESIDUAL, torch.float32)
+    b = run(2400, 256, 14336, B.GEMM_ADD_RESIDUAL, torch.float32)
+    assert torch.equal(a, b)
+    a = run(8400, 384, 4096, B.GEMM_STORE, torch.bfloat16)
+    b = run(8400, 384, 4096, B.GEMM_STORE, torch.bfloat16)
+    assert torch.equal(a, b)
+    run(8400, 1280, 4096, B.GEMM_ADD_RESIDUAL, torch.float32)
+    run(2400, 4096, 14336, B.GEMM_ADD_RESIDUAL, torch.float32)     # 10 token tiles x 32 row tiles in 3 groups
+    # gated: 8,400 tokens x 4,096 is 69 MB of activations
+    M, I, K = 8400, 384, 4096
+    g = torch.Generator(device=DEV).manual_seed(7)
+    x = torch.randn(M, K, device=DEV, generator=g).bfloat16()
+    w = (torch.randn(2 * I, K, device=DEV, generator=g) * (2.0 / K ** 0.5)).bfloat16()
+    act = torch.full((M, I), float("nan"), device=DEV, dtype=torch.bfloat16)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    assert B.gemm_tc_gated(x, w, act, M, err, B.stream_ptr())
+    torch.cuda.synchronize()
+    assert err.item() == 0
+    gate = x.double() @ w[:I].double().t()
+    up = x.double() @ w[I:].double().t()
+    ref = gate * torch.sigmoid(gate) * up
+    bound = 1e-3 + (2.0 ** -8) * ref.abs() + 1e-3 * (gate.abs() + 1) * up.abs()
+    assert torch.isfinite(act).all() and bool(((act.double() - ref).abs() <= bound).all())
+
+
 def test_many_tiles_per_cta():
     from inference_engine_rust_b200.csrc import bindings as B
     run(1500, 4096, 256, B.GEMM_STORE, torch.bfloat16)                         # 32 x 6 tiles on 148 CTAs

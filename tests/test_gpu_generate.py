@@ -83,6 +83,50 @@ def test_running_ahead_changes_no_token(loaded, tmp_path, dtype):
         assert session.engine.cache.slots.held_count == 0
 
 
+@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_generation_across_a_page_boundary_and_a_ring_wrap(loaded, tmp_path, name, dtype):
+    """Prompts of 60 and 125 tokens and 12 new tokens: decoding crosses positions 64 and 128, so a
+    page is taken in the middle of a run (with the device one step ahead of the host, the page
+    table is brought up to date while the step before still runs) and, with Tiny A's window of
+    16, the 64-position ring wraps.  A third, short request ends early.  Both loops, poisoned
+    cache.  Greedy: the plain implementation's tokens (float32; in bfloat16 the two loops agree
+    and every token is the argmax of the plain logits within the tolerance).  Temperature: the
+    two loops agree."""
+    from inference_engine_rust_b200 import LoadedModel
+    folder, model, w = loaded[name]
+    cfg = TINY[name]
+    if dtype == "bfloat16":
+        folder = make_folder(tmp_path, cfg, seed=31, dtype="bfloat16")
+        model = LoadedModel.load(folder, dtype="bfloat16")
+        w = plain_weights(folder)
+    prompts = prompts_for(cfg, [60, 125, 3], seed=13)
+    session = model.session(max_tokens=64 * 6, max_sequences=3, poison_cache=True)
+    by_loop = {}
+    for run_ahead in (False, True):
+        res = session.generate(prompts, max_new_tokens=12, stop_ids=[], full=True, run_ahead=run_ahead)
+        by_loop[run_ahead] = [r.tokens for r in res]
+        assert all(len(r.tokens) == 12 and r.finish_reason == "length" for r in res)
+        session.engine.cache.check()
+        assert session.engine.cache.slots.held_count == 0
+    assert by_loop[True] == by_loop[False]
+    if dtype == "float32":
+        assert by_loop[True] == [P.generate_greedy(cfg, w, p, 12) for p in prompts]
+    else:
+        for p, toks in zip(prompts, by_loop[True]):
+            logits = P.forward(cfg, w, list(p) + toks[:-1], P.bf16_rounding)[len(p) - 1:]
+            for row, tok in zip(logits, toks):       # the chosen token is the best, or within rounding of the best
+                assert row[tok] >= row.max() - 2.0 ** -6 * 2 * row.abs().max()
+    # a stop token met in the middle of the second page, and sampling: the loops still agree
+    stop = {by_loop[True][0][7], by_loop[True][1][5]}
+    for temperature in (0.0, 0.8):
+        a = session.generate(prompts, max_new_tokens=12, temperature=temperature, seed=3, stop_ids=stop, full=True,
+                             run_ahead=False)
+        b = session.generate(prompts, max_new_tokens=12, temperature=temperature, seed=3, stop_ids=stop, full=True)
+        assert [(r.tokens, r.finish_reason) for r in a] == [(r.tokens, r.finish_reason) for r in b]
+    assert session.engine.cache.slots.held_count == 0
+
+
 def test_a_step_takes_its_tokens_from_device_memory(loaded):
     """`step_tokens_on_device` against `step` with the same ids from the host: the same logits to
     the bit, also when the rows used are not all of the tensor and when graphs are off; what it
@@ -247,7 +291,7 @@ def test_command_line_random_preset_and_lenient_loading(loaded, tmp_path):
     assert run(["--random", "tiny-c"] + tail).returncode == 2               # no such preset
     assert run(["--random", "tiny-a", "-m", d] + tail).returncode == 2      # one or the other
     # extras
-    t = load_file(os.path.join(d, "model.safetensors"))
+    t = {k: v.clone() for k, v in load_file(os.path.join(d, "model.safetensors")).items()}   # not the file's mapping
     want = P.generate_greedy(cfg, {k: v.float() for k, v in t.items()}, [5, 9, 200, 31], 5)
     t["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(8)
     save_file(t, os.path.join(d, "model.safetensors"))

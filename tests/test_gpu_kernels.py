@@ -324,6 +324,80 @@ def test_attention_decode_batch_with_padding(heads, kvh, hd, window):
                 f"cut by length, {splits} parts at most, {target} CTAs aimed for"
 
 
+@pytest.mark.parametrize("heads,kvh,hd", [(32, 8, 128), (12, 2, 64), (6, 3, 32)])
+@pytest.mark.parametrize("window", [None, 4096])
+def test_attention_decode_over_long_contexts(heads, kvh, hd, window):
+    """Sequences of 9,000, 64, 4,097 and 700 tokens (over 140 pages; the window of 4,096 cuts two of
+    them, one of them by a single key): the split-KV kernels with an even cut into 8 and 16 parts
+    and cut by length, against the plain kernel and against a float32 statement of the same
+    attention in the manner of the plain implementation.  In every sequence the last query is
+    made to single out the FIRST key it may see, so that the far edge decides the result."""
+    b = B()
+    torch.manual_seed(11)
+    dtype = torch.bfloat16
+    lens = [9000, 64, 4097, 700]
+    pages = sum(-(-n // 64) for n in lens)
+    cache = make_cache(kvh, hd, window, dtype, max_tokens=64 * pages, max_seq_len=9024, slots=4)
+    slots = [cache.open_sequence() for _ in lens]
+    for s_, n in zip(slots, lens):
+        cache.reserve(s_, n)
+    cache.upload()
+    kvs = cache.layer_view(0).struct
+    W, group = heads + 2 * kvh, heads // kvh
+    scale = 1.0 / math.sqrt(hd)
+    ident = torch.zeros(hd // 2, device=DEV)
+    err = err_word()
+    fill = torch.randn(sum(n - 1 for n in lens), W, hd, device=DEV) * 0.7
+    nxt = torch.randn(len(lens), W, hd, device=DEV) * 0.7
+    at = 0
+    for i, n in enumerate(lens):
+        first = max(0, n - window) if window else 0            # the first key the token at position n - 1 sees
+        nxt[i, :heads] *= 3.0
+        if first < n - 1:
+            fill[at + first, heads:heads + kvh] = nxt[i, 0:heads:group] * 1.0      # aligned with head 0 of each group
+        at += n - 1
+    fill, nxt = fill.to(dtype).view(-1, W * hd), nxt.to(dtype).view(-1, W * hd)
+    view, keep = make_batch([n - 1 for n in lens], [0] * len(lens), slots)
+    b.rope_kv_store(fill, view, kvs, ident, heads, hd, b.PAIR_HALF, True, err, stream())
+    view1, keep1 = make_batch([1] * len(lens), [n - 1 for n in lens], slots)
+    b.rope_kv_store(nxt, view1, kvs, ident, heads, hd, b.PAIR_HALF, True, err, stream())
+    plain = torch.empty(len(lens), heads * hd, device=DEV, dtype=dtype)
+    b.attention_plain(nxt, plain, view1, kvs, heads, scale, True, err, stream())
+    assert err.item() == 0
+    # the same attention stated in float32 on the bf16 values (src/layers/attention.rs:609-652)
+    ref = torch.empty(len(lens), heads, hd, device=DEV)
+    at, dominated = 0, 0
+    f, x = fill.float().view(-1, W, hd), nxt.float().view(-1, W, hd)
+    for i, n in enumerate(lens):
+        k_all = torch.cat([f[at:at + n - 1, heads:heads + kvh], x[i:i + 1, heads:heads + kvh]])
+        v_all = torch.cat([f[at:at + n - 1, heads + kvh:], x[i:i + 1, heads + kvh:]])
+        lo = max(0, n - window) if window else 0
+        for h in range(heads):
+            p_ = P.softmax((k_all[lo:n, h // group] @ x[i, h]) * scale)
+            ref[i, h] = p_ @ v_all[lo:n, h // group]
+            if h % group == 0 and n > 64:
+                dominated += int(p_[0] > 0.5)
+        at += n - 1
+    assert dominated >= 3 * kvh, "the first visible key does not dominate: a wrong far edge would not show"
+    assert torch.allclose(plain.float().view_as(ref), ref, atol=2e-2, rtol=2e-2), "the plain kernel"
+    for parts in (8, 16):
+        n_s = b.attention_decode_scratch_floats(len(lens), heads, hd, parts)
+        for target in (0, 64, 296, 1024):                      # 0: every sequence into all parts
+            scratch = torch.full((n_s,), float("nan"), device=DEV)
+            tc = torch.full_like(plain, float("nan"))
+            assert b.attention_decode_tc(nxt, tc, view1, kvs, heads, scale, parts, scratch, err, stream(),
+                                         target_ctas=target)
+            assert err.item() == 0 and torch.isfinite(tc).all()
+            what = f"{parts} parts at most, {target} CTAs aimed for"
+            assert torch.allclose(tc.float(), plain.float(), atol=2e-2, rtol=2e-2), what + ": against the plain kernel"
+            assert torch.allclose(tc.float().view_as(ref), ref, atol=2e-2, rtol=2e-2), what + ": against float32"
+        scratch = torch.full((n_s,), float("nan"), device=DEV)
+        cc = torch.full_like(plain, float("nan"))
+        assert b.attention_decode(nxt, cc, view1, kvs, heads, scale, parts, scratch, err, stream())
+        assert err.item() == 0
+        assert torch.allclose(cc.float().view_as(ref), ref, atol=2e-2, rtol=2e-2), f"CUDA-core kernel, {parts} splits"
+
+
 @pytest.mark.parametrize("heads,kvh,hd,window,pairing,rotary", [
     (32, 8, 128, None, "half", 128), (12, 2, 64, 40, "interleaved", 64), (6, 1, 32, 100, "half", 16),
     (20, 2, 48, None, "interleaved", 32)])
@@ -487,3 +561,12 @@ def test_attention_prefill_against_plain_kernel(heads, kvh, hd, window):
     lo = far
     p_far = P.softmax((x[lo:last + 1, heads] @ x[last, 0]) * scale)
     assert p_far[0] > 0.5, "the far key does not dominate"
+    # the kernel the engine runs for this head size, also against the per-row statement of the
+    # same attention (softmax of the plain implementation), not only against its sibling kernel
+    t = 0
+    for n in q_lens:
+        blk = x[t:t + n]
+        ref = _plain_attention(blk[:, :heads], blk[:, heads:heads + kvh], blk[:, heads + kvh:], heads, kvh, scale, window)
+        got = fast[t:t + n].float().cpu().view(n, heads, hd)
+        assert torch.allclose(got, ref, atol=2e-2, rtol=2e-2), f"prompt of {n} tokens against the per-row statement"
+        t += n

@@ -242,7 +242,7 @@ def plain_toy(cfg: ToyConfig, w, ids):
                 for h in range(4):
                     s = (q[:, h] @ src["k"][:, h // 2].t()) * 0.25
                     out[:, h] = P.softmax(s.masked_fill(~mask, float("-inf"))) @ src["v"][:, h // 2]
-                y = P.matmul(out.reshape(T, 64, 128), w[p + "mix.o_proj.weight"])
+                y = P.matmul(out.reshape(T, 64), w[p + "mix.o_proj.weight"])
             x = x + y
         xn = P.rmsnorm(x, w[p + "n2.weight"], 1e-5)
         x = x + P.ffn_layer(xn, w[p + "ffn.gate_proj.weight"], w[p + "ffn.up_proj.weight"], w[p + "ffn.down_proj.weight"])

@@ -10,7 +10,10 @@ results of the key splits in a fixed 8 MiB array inside the library image.
 Checked here: two calls in a row give what the ordinary entry point gives (the array keeps
 the first call's contents, and the second call must not be disturbed by them), a call that
 would need more than the array holds is refused with its own status and launches nothing,
-and the messages name the limit.  The file is collected last on purpose, and it passes alone
+the messages name the limit, and, after one warm-up call (which may load the library's code
+and its array onto the device), further calls leave the device's free memory as the driver
+reports it (cudaMemGetInfo) exactly where it was: torch's own counter cannot see a
+cudaMalloc made behind its back, the driver's can.  The file is collected last on purpose, and it passes alone
 in a fresh process as well as after the other tests.
 """
 import ctypes
@@ -100,6 +103,31 @@ def test_two_calls_in_a_row_match_the_ordinary_entry_point():
         # same kernels, same split order: the tolerance of the kernel tests holds with room to spare
         assert torch.allclose(got.float(), want.float(), atol=2e-2, rtol=2e-2), f"call {round_no}"
         assert torch.equal(got, want), f"call {round_no}: the two entry points run the same arithmetic"
+
+
+def test_calls_after_the_first_take_no_device_memory():
+    """The free device memory that the driver reports does not move over a run of calls, once a
+    first call has loaded what the runtime loads lazily.  torch allocates nothing in between
+    either (its tensors are made before), so any change would be the library's."""
+    lib, B = library()
+    heads, kvh, hd, splits = 32, 8, 128, 4
+    lens = [300, 64, 700, 1]
+    cache, kv, view, keep, step, err = decoding_batch(B, heads, kvh, hd, None, lens, seed=21)
+    scale = 1.0 / math.sqrt(hd)
+    got = torch.zeros((len(lens), heads * hd), device=DEV, dtype=torch.bfloat16)
+    call = lambda: lib.iert_attention_decode_static(step.data_ptr(), got.data_ptr(), byref(view), byref(kv), heads,
+                                                    scale, splits, err.data_ptr(), B.stream_ptr())
+    assert call() == 0                         # warm-up: address look-up, lazy loading of the kernels
+    torch.cuda.synchronize()
+    free_before, total = torch.cuda.mem_get_info()
+    torch_before = torch.cuda.memory_allocated()
+    for _ in range(8):
+        assert call() == 0
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before, f"free device memory moved by {free_before - free_after} bytes over 8 calls"
+    assert torch.cuda.memory_allocated() == torch_before
+    assert err.item() == 0 and torch.isfinite(got).all()
 
 
 def test_a_call_beyond_the_fixed_array_is_refused():
