@@ -95,6 +95,8 @@ def _declare(lib) -> None:
     lib.iert_gemm_tc_gated.argtypes = [P, c_longlong, P, c_longlong, P, c_longlong, c_int, c_int, c_int, c_int,
                                        c_int, P, S]
     lib.iert_gemm_tc_gated.restype = c_int
+    lib.iert_gemm_rows.argtypes = [P, c_longlong, P, c_longlong, P, c_int, c_longlong, c_int, c_int, c_int, c_int, c_int, P, S]
+    lib.iert_gemm_rows.restype = c_int
     lib.iert_gemm_tc_workspace_bytes.restype = c_longlong
     lib.iert_gemm_tc_counter_count.restype = c_int
     for name, args in sigs.items():
@@ -258,6 +260,20 @@ def gemm_tc(x, w, out, M: int, mode: int, err, stream, force_bt: int = 0, force_
     if status == 1:
         return False
     check(status, "gemm_tc")
+    return True
+
+
+def gemm_rows(x, w, out, M: int, mode: int, err, stream, force_stages: int = 0) -> bool:
+    """out[:M] (=|+=) x[:M] @ w.T for one-token steps (M <= 32, bf16 operands): 16 weight rows per
+    CTA over all of k, no split-K.  Returns False, having launched nothing, when the operands do
+    not meet the kernel's rules."""
+    N, K = w.shape
+    status = core().iert_gemm_rows(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(),
+                                   dtype_code(out.dtype), out.stride(0), M, N, K, mode, force_stages,
+                                   err.data_ptr(), stream)
+    if status == 1:
+        return False
+    check(status, "gemm_rows")
     return True
 
 

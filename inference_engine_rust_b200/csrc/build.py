@@ -34,7 +34,7 @@ NVCC_FLAGS = [
 # the model's sizes; kernels specialised on a size are separate libraries made on demand.
 CORE_SOURCES = [
     "runtime.cu", "elementwise.cu", "gemm_plain.cu", "attention_plain.cu", "sampling.cu",
-    "gemm_tc.cu", "attention_decode.cu",
+    "gemm_tc.cu", "gemm_rows.cu", "attention_decode.cu",
 ]
 # the native reader of weight files (host code), loaded by the weights package
 IO_SOURCES = ["weight_reader.cu"]

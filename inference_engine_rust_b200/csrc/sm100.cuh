@@ -59,6 +59,15 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
       : "memory");
 }
 
+// 3-D tile load: c0 along the contiguous dimension, then c1, c2 (same alignment rule for c0).
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1,
+                                            int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_addr(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_addr(bar)), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+
 // ---- TMA reduce (shared -> global, element-wise add at the destination) -------------------
 // One thread.  The box [c1 .. c1 + box rows) x [c0 .. c0 + box cols) of the tensor gets the
 // tile at `smem_src` added to it (fp32 add performed by the memory system); parts of the box

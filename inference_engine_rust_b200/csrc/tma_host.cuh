@@ -71,4 +71,33 @@ inline bool tensor_map_2d(const void* ptr, long long rows, long long cols, long 
   return true;
 }
 
+// The same matrix (cols a multiple of 64) seen as [cols / 64] k-blocks of [rows, 64]: boxes of
+// `box_kblocks` k-blocks x box_rows rows x 64 elements, laid out in shared memory k-block after
+// k-block, each a 128-byte-swizzled tile of box_rows rows.  One copy brings several k-blocks.
+inline bool tensor_map_kblocks(const void* ptr, long long rows, long long cols, long long ld, int box_rows,
+                               int box_kblocks, CUtensorMap* out) {
+  static std::unordered_map<Key, CUtensorMap, KeyHash> cache;
+  static std::mutex mu;
+  if (cols % 64) return false;
+  Key key{ptr, rows, cols, ld, box_rows * 1024 + box_kblocks};
+  std::lock_guard<std::mutex> g(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) { *out = it->second; return true; }
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[3] = {64u, (cuuint64_t)rows, (cuuint64_t)(cols / 64)};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * 2, 128u};
+  cuuint32_t box[3] = {64u, (cuuint32_t)box_rows, (cuuint32_t)box_kblocks};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUtensorMap m;
+  CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return false;
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, m);
+  *out = m;
+  return true;
+}
+
 }  // namespace tma_host

@@ -1,5 +1,7 @@
-"""Dispatch of a projection to the tcgen05 tensor-core kernel."""
+"""Dispatch of a projection to the tensor-core kernels."""
 from __future__ import annotations
+
+import os
 
 import torch
 
@@ -15,12 +17,21 @@ GATED_MIN_ROWS = 128
 GATED_MAX_DECODE_ROWS = 64
 
 
+# One-token steps of up to this many tokens: a matrix whose 128-row tiles would not fill the device
+# (the tcgen05 kernel would split k and add partial tiles through memory) goes to the kernel that
+# gives every CTA 16 rows over all of k instead.
+ROWS_KERNEL_MAX_TOKENS = int(os.environ.get("IERT_GEMM_ROWS_MAX", "16"))      # 0: never (for comparison)
+
+
 def apply(linear, x, out, n_rows: int, mode: int, stream: int) -> bool:
     """Run the tensor-core product if it takes these operands (bf16, K and row strides
     multiples of 8, 16-byte aligned); False means nothing was launched and the caller runs the
     plain kernel."""
     if x.dtype != torch.bfloat16 or linear.weight.dtype != torch.bfloat16:
         return False
+    if n_rows <= ROWS_KERNEL_MAX_TOKENS and 2 * -(-linear.out_features // 128) <= 2 * B.sm_count():
+        if B.gemm_rows(x, linear.weight, out, n_rows, mode, linear.rt.err, stream):
+            return True
     return B.gemm_tc(x, linear.weight, out, n_rows, mode, linear.rt.err, stream)
 
 
