@@ -44,6 +44,23 @@ class BatchView(Structure):
                 ("pos0", c_void_p), ("n_seqs", c_int), ("n_tokens", c_int)]
 
 
+class NormAhead(Structure):
+    """Mirror of `IertNormAhead` (common.cuh): the first half of an RMSNorm, written by the kernel that
+    writes the rows."""
+    _fields_ = [("weight", c_void_p), ("weight_dtype", c_int), ("scaled_out", c_void_p), ("ld", c_longlong),
+                ("sumsq_out", c_void_p), ("parts", c_int)]
+
+
+class RowScale(Structure):
+    """Mirror of `IertRowScale`: the second half, applied by the projection that reads the scaled rows."""
+    _fields_ = [("sumsq", c_void_p), ("parts", c_int), ("hidden", c_int), ("eps", c_float)]
+
+
+def norm_ahead(weight, scaled_out, sumsq_out) -> NormAhead:
+    return NormAhead(weight=weight.data_ptr(), weight_dtype=dtype_code(weight.dtype), scaled_out=scaled_out.data_ptr(),
+                     ld=scaled_out.stride(0), sumsq_out=sumsq_out.data_ptr(), parts=0)
+
+
 def dtype_code(dt: torch.dtype) -> int:
     if dt == torch.float32:
         return F32
@@ -74,7 +91,7 @@ def _declare(lib) -> None:
     lib.iert_device_arch.restype = c_int
     lib.iert_sm_count.restype = c_int
     sigs = {
-        "iert_embed_gather": [P, c_int, P, P, c_int, c_int, c_int, c_float, P, S],
+        "iert_embed_gather": [P, c_int, P, P, c_int, c_int, c_int, c_float, P, POINTER(NormAhead), S],
         "iert_rmsnorm": [P, P, c_int, P, c_int, P, c_int, c_int, c_float, S],
         "iert_rope_kv_store": [P, c_int, POINTER(BatchView), POINTER(KvView), P, c_int, c_int, c_int, c_int, P, S],
         "iert_silu_mul": [P, P, c_int, c_int, c_int, S],
@@ -95,8 +112,12 @@ def _declare(lib) -> None:
     lib.iert_gemm_tc_gated.argtypes = [P, c_longlong, P, c_longlong, P, c_longlong, c_int, c_int, c_int, c_int,
                                        c_int, P, S]
     lib.iert_gemm_tc_gated.restype = c_int
-    lib.iert_gemm_rows.argtypes = [P, c_longlong, P, c_longlong, P, c_int, c_longlong, c_int, c_int, c_int, c_int, c_int, P, S]
+    lib.iert_gemm_rows.argtypes = [P, c_longlong, P, c_longlong, P, c_int, c_longlong, c_int, c_int, c_int, c_int,
+                                   POINTER(RowScale), POINTER(NormAhead), c_int, P, S]
     lib.iert_gemm_rows.restype = c_int
+    lib.iert_gemm_tc_gated_scaled.argtypes = [P, c_longlong, P, c_longlong, P, c_longlong, c_int, c_int, c_int,
+                                              POINTER(RowScale), c_int, P, S]
+    lib.iert_gemm_tc_gated_scaled.restype = c_int
     lib.iert_gemm_tc_workspace_bytes.restype = c_longlong
     lib.iert_gemm_tc_counter_count.restype = c_int
     for name, args in sigs.items():
@@ -142,11 +163,14 @@ def describe_error_bits(bits: int) -> str:
 # thin wrappers: tensors in, launch, nothing returned
 
 
-def embed_gather(table, ids, x, scale: float, err, stream) -> None:
+def embed_gather(table, ids, x, scale: float, err, stream, ahead: Optional[NormAhead] = None) -> int:
+    """x[t] = table[ids[t]] * scale.  `ahead`: also the first half of the norm that follows
+    (`norm_ahead`); returns the partial sums of squares per row it wrote (0 without `ahead`)."""
     vocab, hidden = table.shape
     check(core().iert_embed_gather(table.data_ptr(), dtype_code(table.dtype), ids.data_ptr(),
                                    x.data_ptr(), ids.numel(), hidden, vocab, scale,
-                                   err.data_ptr(), stream), "embed_gather")
+                                   err.data_ptr(), byref(ahead) if ahead is not None else None, stream), "embed_gather")
+    return int(ahead.parts) if ahead is not None else 0
 
 
 def rmsnorm(x, w, out, eps: float, stream, rows_idx=None, rows: Optional[int] = None) -> None:
@@ -263,17 +287,35 @@ def gemm_tc(x, w, out, M: int, mode: int, err, stream, force_bt: int = 0, force_
     return True
 
 
-def gemm_rows(x, w, out, M: int, mode: int, err, stream, force_stages: int = 0) -> bool:
+def gemm_rows(x, w, out, M: int, mode: int, err, stream, scale: Optional[RowScale] = None,
+              ahead: Optional[NormAhead] = None, force_stages: int = 0) -> bool:
     """out[:M] (=|+=) x[:M] @ w.T for one-token steps (M <= 32, bf16 operands): 16 weight rows per
-    CTA over all of k, no split-K.  Returns False, having launched nothing, when the operands do
-    not meet the kernel's rules."""
+    CTA over all of k, no split-K.  `scale`: x is the first half of an RMSNorm and the outputs
+    are multiplied by the rows' 1 / rms; `ahead` (with a residual add): the first half of the
+    next norm is written beside the new rows and `ahead.parts` is set.  Returns False, having
+    launched nothing, when the operands do not meet the kernel's rules."""
     N, K = w.shape
     status = core().iert_gemm_rows(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(),
-                                   dtype_code(out.dtype), out.stride(0), M, N, K, mode, force_stages,
+                                   dtype_code(out.dtype), out.stride(0), M, N, K, mode,
+                                   byref(scale) if scale is not None else None,
+                                   byref(ahead) if ahead is not None else None, force_stages,
                                    err.data_ptr(), stream)
     if status == 1:
         return False
     check(status, "gemm_rows")
+    return True
+
+
+def gemm_tc_gated_scaled(x, w, act, M: int, scale: RowScale, err, stream, force_bt: int = 0) -> bool:
+    """`gemm_tc_gated` in its one-token form for an x that is the first half of an RMSNorm: gate and
+    up are multiplied by the rows' 1 / rms before the activation."""
+    two_i, K = w.shape
+    status = core().iert_gemm_tc_gated_scaled(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), act.data_ptr(),
+                                              act.stride(0), M, two_i // 2, K, byref(scale), force_bt,
+                                              err.data_ptr(), stream)
+    if status == 1:
+        return False
+    check(status, "gemm_tc_gated_scaled")
     return True
 
 

@@ -64,7 +64,66 @@ struct IertBatchView {
   int n_tokens;
 };
 
+// An RMSNorm split in two around a kernel boundary (one-token steps, where a norm kernel of its own
+// costs more than its work).  The kernel that writes new residual rows x[t, :] also writes
+//   scaled[t, n] = bf16(x[t, n] * weight[n])          (no row statistic needed: element by element)
+//   sumsq[t, p]  = sum of x[t, n]^2 over part p of the row's columns
+// (`IertNormAhead`), and the projection that reads `scaled` as its input multiplies its outputs by
+// 1 / sqrt(sum_p sumsq[t, p] / hidden + eps) (`IertRowScale`): the product is linear in its input,
+// so this is the projection of the normalised row, with one bf16 rounding before the factor instead
+// of after it.  Statistics are fp32 and summed in a fixed order.
+struct IertNormAhead {
+  const void* weight;      // the norm's scale vector [N]
+  int weight_dtype;
+  void* scaled_out;        // bf16 [M, N], row stride ld
+  long long ld;
+  float* sumsq_out;        // fp32 [M, parts]; parts is set by the launcher
+  int parts;
+};
+struct IertRowScale {
+  const float* sumsq;      // fp32 [M, parts]
+  int parts;
+  int hidden;              // the length of the normalised rows
+  float eps;
+};
+
 namespace iert {
+
+// 1 / sqrt(mean + eps) of up to `n_tokens` rows from their partial sums of squares into out[t]
+// (shared memory), by a group of `nthreads` threads (a multiple of 32) numbered `tid`: a warp takes
+// rows w, w + nwarps, ..., two at a time; a lane loads every 32nd partial sum of both rows, eight
+// each before the first is used (one round trip to the L2 for up to 256 parts), adds its own in
+// order and the warp adds the lanes by shuffles.  The order of the additions depends on the number
+// of parts alone.
+__device__ __forceinline__ void row_scales_from_parts(const IertRowScale& rs, int n_tokens, float* out, int tid, int nthreads) {
+  const int warp = tid >> 5, lane = tid & 31, nwarps = nthreads >> 5;
+  for (int t0 = warp; t0 < n_tokens; t0 += 2 * nwarps) {
+    const int t1 = t0 + nwarps;
+    const float* p0 = rs.sumsq + (size_t)t0 * rs.parts;
+    const float* p1 = rs.sumsq + (size_t)(t1 < n_tokens ? t1 : t0) * rs.parts;
+    float s0 = 0.f, s1 = 0.f;
+    for (int i0 = lane; i0 < rs.parts; i0 += 256) {
+      float a[8], b[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int i = i0 + 32 * j;
+        a[j] = i < rs.parts ? __ldcg(p0 + i) : 0.f;
+        b[j] = i < rs.parts ? __ldcg(p1 + i) : 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { s0 += a[j]; s1 += b[j]; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      s0 += __shfl_xor_sync(0xffffffffu, s0, o);
+      s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+    }
+    if (lane == 0) {
+      out[t0] = 1.0f / sqrtf(s0 / (float)rs.hidden + rs.eps);
+      if (t1 < n_tokens) out[t1] = 1.0f / sqrtf(s1 / (float)rs.hidden + rs.eps);
+    }
+  }
+}
 
 __device__ __forceinline__ float to_f32(float x) { return x; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 x) { return __bfloat162float(x); }

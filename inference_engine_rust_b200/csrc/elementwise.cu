@@ -12,31 +12,53 @@ using namespace iert;
 template <typename TW>
 __global__ void embed_gather_kernel(const TW* __restrict__ table, const int* __restrict__ ids,
                                     float* __restrict__ x, int hidden, int vocab, float scale,
-                                    int* __restrict__ err) {
+                                    int* __restrict__ err, IertNormAhead ahead) {
+  __shared__ float scratch[33];
   pdl_launch_dependents();     // the next kernel may start its preamble now
   pdl_wait();                  // everything below may depend on the kernel before
   const int t = blockIdx.x;
   const int id = ids[t];
   float* row = x + (size_t)t * hidden;
-  if (id < 0 || id >= vocab) {
-    if (threadIdx.x == 0) atomicOr(err, IERT_ERR_TOKEN_RANGE);
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) row[i] = 0.f;
-    return;
+  const bool in_range = id >= 0 && id < vocab;
+  if (!in_range && threadIdx.x == 0) atomicOr(err, IERT_ERR_TOKEN_RANGE);
+  const TW* src = table + (size_t)(in_range ? id : 0) * hidden;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float v = in_range ? to_f32(src[i]) * scale : 0.f;
+    row[i] = v;
+    if (ahead.scaled_out) {    // the first half of the norm that follows (see IertNormAhead)
+      const float g = ahead.weight_dtype == IERT_F32 ? ((const float*)ahead.weight)[i]
+                                                     : __bfloat162float(((const __nv_bfloat16*)ahead.weight)[i]);
+      ((__nv_bfloat16*)ahead.scaled_out)[(size_t)t * ahead.ld + i] = __float2bfloat16_rn(v * g);
+      ss += v * v;
+    }
   }
-  const TW* src = table + (size_t)id * hidden;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) row[i] = to_f32(src[i]) * scale;
+  if (ahead.scaled_out) {      // (the same for the whole block)
+    ss = block_sum(ss, scratch);
+    if (threadIdx.x == 0) ahead.sumsq_out[t] = ss;
+  }
 }
 
+// ahead (optional): the first half of the RMSNorm that follows, over the rows just written; ahead->parts is
+// set to 1 (one sum of squares per row).
 IERT_API int iert_embed_gather(const void* table, int table_dtype, const int* ids, float* x,
                                int n_tokens, int hidden, int vocab, float scale, int* err,
-                               cudaStream_t stream) {
+                               IertNormAhead* ahead, cudaStream_t stream) {
   if (n_tokens <= 0) return IERT_OK;
   if (hidden <= 0 || vocab <= 0) return IERT_BAD_ARGUMENT;
+  IertNormAhead a = {nullptr, 0, nullptr, 0, nullptr, 0};
+  if (ahead) {
+    if (!ahead->weight || !ahead->scaled_out || !ahead->sumsq_out ||
+        (ahead->weight_dtype != IERT_F32 && ahead->weight_dtype != IERT_BF16))
+      return IERT_BAD_ARGUMENT;
+    ahead->parts = 1;
+    a = *ahead;
+  }
   const int threads = hidden >= 1024 ? 256 : 128;
   if (table_dtype == IERT_F32)
-    launch_dep(embed_gather_kernel<float>, n_tokens, threads, 0, stream, (const float*)table, ids, x, hidden, vocab, scale, err);
+    launch_dep(embed_gather_kernel<float>, n_tokens, threads, 0, stream, (const float*)table, ids, x, hidden, vocab, scale, err, a);
   else if (table_dtype == IERT_BF16)
-    launch_dep(embed_gather_kernel<__nv_bfloat16>, n_tokens, threads, 0, stream, (const __nv_bfloat16*)table, ids, x, hidden, vocab, scale, err);
+    launch_dep(embed_gather_kernel<__nv_bfloat16>, n_tokens, threads, 0, stream, (const __nv_bfloat16*)table, ids, x, hidden, vocab, scale, err, a);
   else
     return IERT_BAD_ARGUMENT;
   return iert_check_launch("embed_gather");

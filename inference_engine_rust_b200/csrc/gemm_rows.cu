@@ -69,6 +69,8 @@ struct RowsParams {
   int kb_total, n_stages, stages;         // k-blocks, ring uses (KPS k-blocks each), ring depth
   int boxes3d;                            // K is a multiple of 64: one copy brings a stage's weights, one its tokens
   int* err;
+  IertRowScale scale;                     // scale.sumsq != null: the outputs are multiplied by the rows' 1 / rms
+  IertNormAhead ahead;                    // ahead.scaled_out != null (residual add): the next norm's first half
   int trace_seq;
 };
 
@@ -109,6 +111,7 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full[MAX_STAGES], empty[MAX_STAGES];
   __shared__ int abort_s;
+  __shared__ float rstd_s[32];
   uint8_t* smem = smem_raw + ((1024u - (sm100::smem_addr(smem_raw) & 1023u)) & 1023u);
   volatile int* abort_flag = &abort_s;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -178,6 +181,10 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     }
   } else {
     // ---------------- four computing warps ----------------
+    if (p.scale.sumsq) {                  // the input rows' 1 / rms, while the first weights are on their way
+      pdl_wait();
+      row_scales_from_parts(p.scale, p.M, rstd_s, threadIdx.x, WARPS * 32);
+    }
     float acc[NT][4];
 #pragma unroll
     for (int t = 0; t < NT; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
@@ -241,18 +248,37 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         r0[8 * NT * 8] = acc[t][2]; r0[8 * NT * 8 + 1] = acc[t][3];        // row g + 8
       }
       asm volatile("bar.sync 1, %0;" ::"n"(WARPS * 32) : "memory");
-      // thread -> (token, row): consecutive threads walk the 16 rows of one token (64 contiguous bytes of out)
+      // thread -> (token, row): consecutive threads walk the 16 rows of one token (64 contiguous bytes of
+      // out); the 16 threads of a token are half a warp
       for (int i = threadIdx.x; i < ROWS * NT * 8; i += WARPS * 32) {
-        const int tok = i / ROWS, row = i % ROWS;
-        if (tok >= p.M || n0 + row >= p.N) continue;
+        const int tok = i / ROWS, row = i % ROWS, n = n0 + row;
+        const bool live = tok < p.M && n < p.N;
         float v = 0.f;
 #pragma unroll
         for (int w = 0; w < WARPS; ++w) v += red[((size_t)w * ROWS + row) * (NT * 8) + tok];
-        if (p.out_dtype == IERT_F32) {
-          float* o = (float*)p.out + (long long)tok * p.ldo + n0 + row;
-          *o = p.mode == MODE_ADD_RESIDUAL ? *o + v : v;
-        } else {
-          ((__nv_bfloat16*)p.out)[(long long)tok * p.ldo + n0 + row] = __float2bfloat16_rn(v);
+        if (p.scale.sumsq && tok < p.M) v *= rstd_s[tok];
+        if (live) {
+          if (p.out_dtype == IERT_F32) {
+            float* o = (float*)p.out + (long long)tok * p.ldo + n;
+            if (p.mode == MODE_ADD_RESIDUAL) v += *o;
+            *o = v;
+          } else {
+            ((__nv_bfloat16*)p.out)[(long long)tok * p.ldo + n] = __float2bfloat16_rn(v);
+          }
+        }
+        if (p.ahead.scaled_out) {           // (the same for every thread) v is the new residual value
+          float ss = 0.f;
+          if (live) {
+            const float g = p.ahead.weight_dtype == IERT_F32 ? ((const float*)p.ahead.weight)[n]
+                                                             : __bfloat162float(((const __nv_bfloat16*)p.ahead.weight)[n]);
+            ((__nv_bfloat16*)p.ahead.scaled_out)[(long long)tok * p.ahead.ld + n] = __float2bfloat16_rn(v * g);
+            ss = v * v;
+          }
+          ss += __shfl_xor_sync(0xffffffffu, ss, 8);
+          ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+          ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+          ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+          if (row == 0 && tok < p.M) p.ahead.sumsq_out[(size_t)tok * p.ahead.parts + blockIdx.x] = ss;
         }
       }
     }
@@ -302,19 +328,30 @@ IERT_API int iert_gemm_rows_trace_read(unsigned long long* stamps, int* meta) {
 // row stride ldo.  mode 0 stores, mode 1 adds into out (fp32).  K, ldx and ldw must be multiples of
 // 8 and the pointers 16-byte aligned (TMA); otherwise, or with more than 32 tokens,
 // IERT_BAD_ARGUMENT is returned and nothing is launched.  force_stages: 0 = choose.
+//   scale (optional)  the rows of x are the first half of an RMSNorm (IertNormAhead of the kernel that
+//                     wrote them): the outputs are multiplied by each row's 1 / rms (see common.cuh).
+//   ahead (optional; mode 1)  the first half of the NEXT norm over the new rows of `out`: ahead->parts
+//                     is set to the number of partial sums per row written (one per CTA).
 IERT_API int iert_gemm_rows(const void* x, long long ldx, const void* w, long long ldw, void* out, int out_dtype,
-                            long long ldo, int M, int N, int K, int mode, int force_stages, int* err,
-                            cudaStream_t stream) {
+                            long long ldo, int M, int N, int K, int mode, const IertRowScale* scale,
+                            IertNormAhead* ahead, int force_stages, int* err, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return IERT_OK;
   if (M > 32 || K <= 0 || (K & 7) || (ldx & 7) || (ldw & 7) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15))
     return IERT_BAD_ARGUMENT;
   if (mode != MODE_STORE && mode != MODE_ADD_RESIDUAL) return IERT_BAD_ARGUMENT;
   if (out_dtype != IERT_F32 && out_dtype != IERT_BF16) return IERT_BAD_ARGUMENT;
   if (mode == MODE_ADD_RESIDUAL && out_dtype != IERT_F32) return IERT_BAD_ARGUMENT;
+  if (scale && (!scale->sumsq || scale->parts <= 0 || scale->hidden <= 0)) return IERT_BAD_ARGUMENT;
+  if (ahead && (mode != MODE_ADD_RESIDUAL || !ahead->weight || !ahead->scaled_out || !ahead->sumsq_out ||
+                (ahead->weight_dtype != IERT_F32 && ahead->weight_dtype != IERT_BF16)))
+    return IERT_BAD_ARGUMENT;
   const int nt = M <= 8 ? 1 : M <= 16 ? 2 : 4;
   RowsParams p;
   p.out = out; p.ldo = ldo; p.out_dtype = out_dtype; p.mode = mode;
   p.M = M; p.N = N; p.K = K; p.err = err;
+  p.scale = IertRowScale{nullptr, 0, 0, 0.f};
+  if (scale) p.scale = *scale;
+  p.ahead = IertNormAhead{nullptr, 0, nullptr, 0, nullptr, 0};
   p.kb_total = (K + KB - 1) / KB;
   p.n_stages = (p.kb_total + KPS - 1) / KPS;
   const int stage_bytes = KPS * (W_BYTES + nt * 8 * KB * 2);
@@ -337,6 +374,10 @@ IERT_API int iert_gemm_rows(const void* x, long long ldx, const void* w, long lo
               tma_host::tensor_map_kblocks(x, M, K, ldx, nt * 8, KPS, &mx);
   if (!p.boxes3d && (!tma_host::tensor_map_2d(w, N, K, ldw, ROWS, &mw) || !tma_host::tensor_map_2d(x, M, K, ldx, nt * 8, &mx)))
     return IERT_BAD_ARGUMENT;
+  if (ahead) {
+    ahead->parts = grid;
+    p.ahead = *ahead;
+  }
   switch (nt) {
     case 1: return launch<1>(mw, mx, p, grid, stream);
     case 2: return launch<2>(mw, mx, p, grid, stream);

@@ -56,7 +56,7 @@ constexpr int THREADS = 192;
 constexpr int W_STAGE_BYTES = TILE_N * TILE_K * 2;
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 constexpr int OUT_STAGE_BYTES = 32 * TILE_N * 4;   // residual add by TMA: 32 tokens x 128 outputs fp32, two of them
-constexpr int XCH_BYTES = 16 * 64 * 4 + 16;   // weight-major gated tile: 16 tokens x 64 up values, aligned
+constexpr int XCH_BYTES = 16 * 64 * 4 + 16 + 256;   // weight-major gated tile: 16 tokens x 64 up values, aligned; 64 row scales
 
 enum : int { MODE_STORE = 0, MODE_ADD_RESIDUAL = 1, MODE_GATED_SILU = 2 };
 
@@ -77,6 +77,8 @@ struct GemmParams {
   int tail_parts;     // > 1: the tiles from full_tiles on are cut into this many parts of k (see WorkIter)
   int full_tiles;
   int* err;
+  IertRowScale scale;   // weight-major gated tiles: scale.sumsq != null: x is the first half of an RMSNorm (see
+                        // common.cuh) and gate and up are multiplied by the rows' 1 / rms before the activation
 };
 
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
@@ -367,6 +369,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   } else {
     // ---------------- epilogue: 4 warps, warp w reads TMEM lanes 32*(w%4).. ----------------
     pdl_wait();
+    float* rstd_s = reinterpret_cast<float*>(xch_s + 16 * 64 * 4);     // [64] (weight-major gated tiles only)
+    const bool scaled = !GATED && BT <= 64 && p.mode == MODE_GATED_SILU && p.scale.sumsq != nullptr;
+    if (scaled) {                          // the rows' 1 / rms, while the weights stream
+      row_scales_from_parts(p.scale, p.M < BT ? p.M : BT, rstd_s, (int)threadIdx.x - 64, 128);
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+    }
     const int q = warp & 3;
     const int n_local = q * 32 + lane;
     int acc = 0;
@@ -490,9 +498,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             if (i < p.N) {
 #pragma unroll
               for (int j = 0; j < 16; ++j)
-                if (c + j < t_valid)
+                if (c + j < t_valid) {
+                  const float r = scaled ? rstd_s[c + j] : 1.0f;
                   ((__nv_bfloat16*)p.out)[(long long)(t0 + c + j) * p.ldo + i] =
-                      __float2bfloat16_rn(silu_mul(v[j], xch[j * 64 + n_local]));
+                      __float2bfloat16_rn(silu_mul(v[j] * r, xch[j * 64 + n_local] * r));
+                }
             }
           }
           asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -890,6 +900,7 @@ IERT_API int iert_gemm_tc(const void* x, long long ldx, const void* w, long long
   if (bt != 16 && bt != 32 && bt != 64 && bt != 128 && bt != 256) return IERT_BAD_ARGUMENT;
 
   GemmParams p;
+  p.scale = IertRowScale{nullptr, 0, 0, 0.f};
   p.tail_parts = 1; p.full_tiles = 0; p.tma_out = 0; p.t_group = 1 << 30;
   p.out = out; p.ldo = ldo; p.out_dtype = out_dtype; p.mode = mode;
   p.M = M; p.N = N; p.K = K;
@@ -1010,13 +1021,16 @@ IERT_API int iert_gemm_tc(const void* x, long long ldx, const void* w, long long
 // act[t, i] = silu(x[t] . w[i]) * (x[t] . w[inter + i]) for w = [gate; up] of 2 * inter rows,
 // in one kernel (two accumulators per tile).  act: bf16 [M, inter], row stride ldo.  Whole
 // tiles only; same alignment rules as iert_gemm_tc.
-IERT_API int iert_gemm_tc_gated(const void* x, long long ldx, const void* w, long long ldw, void* act,
-                                long long ldo, int M, int inter, int K, int force_bt, int force_stages,
-                                int* err, cudaStream_t stream) {
+namespace {
+int gemm_tc_gated_impl(const void* x, long long ldx, const void* w, long long ldw, void* act,
+                       long long ldo, int M, int inter, int K, const IertRowScale* scale, int force_bt, int force_stages,
+                       int* err, cudaStream_t stream) {
   if (M <= 0 || inter <= 0) return IERT_OK;
   if (K <= 0 || (K & 7) || (ldx & 7) || (ldw & 7) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15))
     return IERT_BAD_ARGUMENT;
+  if (scale && (!scale->sumsq || scale->parts <= 0 || scale->hidden <= 0)) return IERT_BAD_ARGUMENT;
   GemmParams p;
+  p.scale = IertRowScale{nullptr, 0, 0, 0.f};
   p.tail_parts = 1; p.full_tiles = 0; p.tma_out = 0; p.t_group = 1 << 30;
   p.out = act; p.ldo = ldo; p.out_dtype = IERT_BF16; p.mode = MODE_GATED_SILU;
   p.M = M; p.N = inter; p.K = K;
@@ -1035,6 +1049,7 @@ IERT_API int iert_gemm_tc_gated(const void* x, long long ldx, const void* w, lon
     p.kb_total = (K + TILE_K - 1) / TILE_K;
     p.splits = 1; p.kb_per_split = p.kb_total; p.coop_reduce = 0;
     p.ws = nullptr; p.counters = nullptr; p.err = err;
+    if (scale) p.scale = *scale;
     const int stage_bytes = W_STAGE_BYTES + wbt * TILE_K * 2;
     int stages = force_stages ? force_stages : (113 * 1024 - 2048 - XCH_BYTES) / stage_bytes;
     if (stages > 12) stages = 12;
@@ -1050,6 +1065,7 @@ IERT_API int iert_gemm_tc_gated(const void* x, long long ldx, const void* w, lon
       default: return launch<64, false>(mw, mx, p, grid, stream);
     }
   }
+  if (scale) return IERT_BAD_ARGUMENT;                 // only the one-token form scales its rows
   const int bt = 128;                                  // tokens per tile: the MMA's M side
   p.n_step = TILE_N; p.second_rows = inter;
   p.n_tiles = (inter + TILE_N - 1) / TILE_N;
@@ -1070,4 +1086,21 @@ IERT_API int iert_gemm_tc_gated(const void* x, long long ldx, const void* w, lon
   if (!tensor_map(w, 2ll * inter, K, ldw, TILE_N, &mw) || !tensor_map(x, M, K, ldx, bt, &mx)) return IERT_BAD_ARGUMENT;
   const int grid = tiles < slots ? tiles : slots;
   return launch<128, true>(mw, mx, p, grid, stream);
+}
+}  // namespace
+
+IERT_API int iert_gemm_tc_gated(const void* x, long long ldx, const void* w, long long ldw, void* act,
+                                long long ldo, int M, int inter, int K, int force_bt, int force_stages,
+                                int* err, cudaStream_t stream) {
+  return gemm_tc_gated_impl(x, ldx, w, ldw, act, ldo, M, inter, K, nullptr, force_bt, force_stages, err, stream);
+}
+
+// The one-token form (M <= 64) for an x that is the first half of an RMSNorm (IertNormAhead of the kernel
+// that wrote it): gate and up are multiplied by each row's 1 / rms before the activation.
+// IERT_BAD_ARGUMENT, nothing launched, where the one-token form does not apply.
+IERT_API int iert_gemm_tc_gated_scaled(const void* x, long long ldx, const void* w, long long ldw, void* act,
+                                       long long ldo, int M, int inter, int K, const IertRowScale* scale, int force_bt,
+                                       int* err, cudaStream_t stream) {
+  if (!scale) return IERT_BAD_ARGUMENT;
+  return gemm_tc_gated_impl(x, ldx, w, ldw, act, ldo, M, inter, K, scale, force_bt, 0, err, stream);
 }

@@ -174,10 +174,20 @@ class Model:
         rt, spec, ws = self.rt, self.spec, self.rt.workspace
         T, H = ctx.n_tokens, spec.hidden_size
         x = ws.take("model.residual", (T, H), torch.float32)
-        B.embed_gather(self.embedding, tokens, x, spec.embedding_scale, rt.err, ctx.stream)
-        for pos, e in enumerate(spec.schedule):
+        sched = spec.schedule
+        # the first block's first norm may ask the embedding kernel for its element-wise half
+        request = self.blocks[sched[0].layer].first_norm_request(ctx) if sched else None
+        ahead = finish = None
+        if request is not None:
+            from ..parts.norm import honour
+            ahead, finish = honour(request, x, ctx, "embed", 1)
+        B.embed_gather(self.embedding, tokens, x, spec.embedding_scale, rt.err, ctx.stream, ahead=ahead)
+        ctx.rows_ahead = finish() if finish is not None else None
+        for pos, e in enumerate(sched):
             view = cache.layer_view(spec.cache_entry(pos))
+            ctx.next_block = self.blocks[sched[pos + 1].layer] if pos + 1 < len(sched) else None
             self.blocks[e.layer].forward(x, ctx, view, e.writes_cache)
+        ctx.rows_ahead = None
         if n_logit_rows == 0:
             return None
         hn = ws.take("model.head_in", (n_logit_rows, H), rt.dtype)

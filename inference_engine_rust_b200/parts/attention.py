@@ -28,6 +28,7 @@ from .linear import Linear
 
 class Attention(Mixer):
     graph_safe = True
+    takes_lazy_input = True          # its input goes to a projection, which may finish a norm itself
 
     def __init__(self, spec, rt: Runtime):
         self.rt = rt
@@ -93,7 +94,7 @@ class Attention(Mixer):
             # position encoding is a plain rotation and the kernel takes the sizes
             from . import fast_attention
             if fast_attention.decode_with_rotation(self, qkv, out, ctx, cache_view, writes_cache):
-                self.o.apply(out, residual, T, ctx.stream, add_residual=True)
+                self.o.apply(out, residual, T, ctx.stream, add_residual=True, ctx=ctx)
                 return
         self.position.encode_and_store(qkv, ctx, kv, self.heads, writes_cache)
         from_cache = ctx.kind == "decode" or not writes_cache
@@ -110,7 +111,7 @@ class Attention(Mixer):
         if not done:
             B.attention_plain(qkv, out, ctx.batch, kv, self.heads, self.scale, from_cache,
                               rt.err, ctx.stream)
-        self.o.apply(out, residual, T, ctx.stream, add_residual=True)
+        self.o.apply(out, residual, T, ctx.stream, add_residual=True, ctx=ctx)
 
 
 register_part("mixer", "attention", Attention)

@@ -11,6 +11,9 @@ kind; the configuration then names that kind for the layers that use it.
     ffn       FeedForward(spec, rt)              .forward(xn, residual, ctx)
     block     Block(layer_spec, norm1, mixer, norm2, ffn, rt)   .forward(x, ctx, cache_view, writes_cache)
 
+Optional, for one-token steps (see `NormRequest`, `LazyInput`): a norm may let the kernel that writes
+its input rows do its element-wise half and the projection that reads its output its row-wise half.
+
 Mixers and feed-forwards ADD their result into `residual` (fp32, [tokens, hidden]): the
 residual sum stays in 32-bit and the last projection can fuse the addition.
 """
@@ -100,6 +103,28 @@ class Runtime:
         return not self.plain_only
 
 
+class LazyInput:
+    """The input of a part's first projection, not in memory in its final form: the projection's
+    kernel may finish it on the way (one-token steps, where a kernel boundary costs more than the
+    work), and `materialize(n_rows)` computes it into memory with the kernel of its own, for
+    whoever cannot.  A part says with `takes_lazy_input = True` that it hands its input to
+    `Linear.apply` (or calls `materialize`) and never reads it as a tensor."""
+
+    def materialize(self, n_rows: int) -> torch.Tensor:
+        raise NotImplementedError
+
+
+@dataclass
+class NormRequest:
+    """What a norm asks of whoever writes the rows it will be applied to next (one-token steps): to
+    write, beside the new rows x, bf16(x * weight) and partial sums of squares of each row.  The
+    row factor 1 / sqrt(mean(x^2) + eps) is applied later, by the projection that reads the scaled
+    rows.  Whoever cannot do that ignores the request and the norm runs as a kernel of its own."""
+    norm: object                  # the Norm that asks
+    weight: torch.Tensor
+    eps: float
+
+
 @dataclass
 class StepContext:
     """The sequences of the running step as parts see them.
@@ -122,6 +147,10 @@ class StepContext:
     stream: int
     rt: Runtime
     unequal_lengths: bool = False                  # one-token step whose mixers want a cut by length
+    norm_ahead: Optional[NormRequest] = None      # set before a part (or the embedding) runs: the norm that will be
+                                                   # applied next to the residual rows it writes
+    rows_ahead: Optional[LazyInput] = None         # set by whoever honoured `norm_ahead`: that norm's lazy result
+    next_block: object = None                      # the block that runs after the current one (None: the last)
     slot_ids_dev: Optional[torch.Tensor] = None   # int32 [n_seqs] view, for parts written in Python
     pos0_dev: Optional[torch.Tensor] = None
     cu_q_dev: Optional[torch.Tensor] = None
@@ -149,6 +178,11 @@ class Part:
 class Norm(Part):
     def forward(self, x, out, ctx, rows_idx=None, rows=None) -> None:
         raise NotImplementedError
+
+    def request_ahead(self) -> Optional[NormRequest]:
+        """A request to whoever writes the rows this norm is applied to next (see `NormRequest`), or
+        None (the default) if this norm cannot be split that way."""
+        return None
 
 
 class PositionEncoding(Part):
@@ -191,3 +225,8 @@ class FeedForward(Part):
 class Block(Part):
     def forward(self, x, ctx: StepContext, cache_view, writes_cache: bool) -> None:
         raise NotImplementedError
+
+    def first_norm_request(self, ctx: StepContext) -> Optional[NormRequest]:
+        """What this block's first norm asks of whoever writes the rows the block will receive (the
+        block before it, or the embedding); None (the default): nothing."""
+        return None

@@ -13,11 +13,36 @@ class PreNormBlock(Block):
         self.norm1, self.mixer, self.norm2, self.ffn, self.rt = norm1, mixer, norm2, ffn, rt
 
     def forward(self, x, ctx: StepContext, cache_view, writes_cache: bool) -> None:
-        xn = self.rt.workspace.take("block.normed", x.shape, self.rt.dtype)
-        self.norm1.forward(x, xn, ctx, rows=ctx.n_tokens)
+        xn = self._normed(self.norm1, x, ctx)
+        ctx.norm_ahead = self._request(self.norm2, self.ffn, ctx)     # of whoever adds the mixer's result into x
         self.mixer.forward(xn, x, ctx, cache_view, writes_cache)
-        self.norm2.forward(x, xn, ctx, rows=ctx.n_tokens)
+        xn = self._normed(self.norm2, x, ctx)
+        nxt = ctx.next_block
+        ctx.norm_ahead = nxt.first_norm_request(ctx) if nxt is not None else None
         self.ffn.forward(xn, x, ctx)
+        ctx.norm_ahead = None
+
+    def first_norm_request(self, ctx: StepContext):
+        return self._request(self.norm1, self.mixer, ctx)
+
+    def _request(self, norm, part, ctx: StepContext):
+        """In one-token steps of few sequences a norm may ask whoever writes its input rows to do its
+        element-wise half (`NormRequest`), if the part behind it hands its input to a projection."""
+        from . import fast_linear
+        if (self.rt.fast and ctx.kind == "decode" and ctx.n_tokens <= fast_linear.ROWS_KERNEL_MAX_TOKENS
+                and getattr(part, "takes_lazy_input", False) and fast_linear.norm_ahead_enabled()):
+            return norm.request_ahead()
+        return None
+
+    def _normed(self, norm, x, ctx: StepContext):
+        """norm(x): what the writer of x left behind for this norm, if it honoured the norm's request,
+        else the norm's own kernel."""
+        lazy, ctx.rows_ahead = ctx.rows_ahead, None
+        if lazy is not None and getattr(lazy, "norm", None) is norm and lazy.rows is x:
+            return lazy
+        xn = self.rt.workspace.take("block.normed", x.shape, self.rt.dtype)
+        norm.forward(x, xn, ctx, rows=ctx.n_tokens)
+        return xn
 
 
 register_part("block", "prenorm", PreNormBlock)

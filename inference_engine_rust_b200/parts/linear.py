@@ -9,8 +9,15 @@ from __future__ import annotations
 
 import torch
 
+from typing import Optional, Union
+
 from ..csrc import bindings as B
-from .base import Runtime
+from .base import LazyInput, NormRequest, Runtime
+
+
+def as_tensor(x: Union[torch.Tensor, LazyInput], n_rows: int) -> torch.Tensor:
+    """`x` itself, or a lazy input computed into memory."""
+    return x.materialize(n_rows) if isinstance(x, LazyInput) else x
 
 
 class Linear:
@@ -29,13 +36,16 @@ class Linear:
     def nbytes(self) -> int:
         return self.weight.numel() * self.weight.element_size()
 
-    def apply(self, x: torch.Tensor, out: torch.Tensor, n_rows: int, stream: int,
-              add_residual: bool = False) -> None:
+    def apply(self, x: Union[torch.Tensor, LazyInput], out: torch.Tensor, n_rows: int, stream: int,
+              add_residual: bool = False, ctx=None) -> None:
         """out[:n_rows] = x[:n_rows] . W^T, or out[:n_rows] += ... when `add_residual`
-        (out is then the fp32 residual stream)."""
+        (out is then the fp32 residual stream).  `x` may be a `LazyInput`: the kernel finishes it
+        on the way if it can, else it is computed into memory first.  With `add_residual` and a
+        step context whose `norm_ahead` is set, the kernel does the next norm's first half where
+        it can and leaves the result in `ctx.rows_ahead`."""
         mode = B.GEMM_ADD_RESIDUAL if add_residual else B.GEMM_STORE
         if self.rt.fast:
             from . import fast_linear
-            if fast_linear.apply(self, x, out, n_rows, mode, stream):
+            if fast_linear.apply(self, x, out, n_rows, mode, stream, ctx if add_residual else None):
                 return
-        B.gemm_plain(x, self.weight, out, n_rows, mode, stream)
+        B.gemm_plain(as_tensor(x, n_rows), self.weight, out, n_rows, mode, stream)

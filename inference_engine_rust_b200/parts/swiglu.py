@@ -16,6 +16,7 @@ from .linear import Linear
 
 class SwiGLU(FeedForward):
     graph_safe = True
+    takes_lazy_input = True          # its input goes to a projection, which may finish a norm itself
 
     def __init__(self, spec, rt: Runtime):
         self.rt = rt
@@ -52,7 +53,7 @@ class SwiGLU(FeedForward):
             gu = ws.take("ffn.gate_up", (T, 2 * I), rt.dtype)
             self.gate_up.apply(xn, gu, T, ctx.stream)
             B.silu_mul(gu, act, T, I, ctx.stream)
-        self.down.apply(act, residual, T, ctx.stream, add_residual=True)
+        self.down.apply(act, residual, T, ctx.stream, add_residual=True, ctx=ctx)
 
 
 register_part("ffn", "swiglu", SwiGLU)
