@@ -28,21 +28,9 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# Layer sizes of Mistral 7B v0.1 (the benchmark configuration; the library itself takes
-# every size from config.json).
-MISTRAL_7B = {
-    "architectures": ["MistralForCausalLM"], "model_type": "mistral",
-    "num_hidden_layers": 32, "hidden_size": 4096, "num_attention_heads": 32, "num_key_value_heads": 8,
-    "head_dim": 128, "intermediate_size": 14336, "vocab_size": 32000, "rope_theta": 10000.0,
-    "sliding_window": 4096, "rms_norm_eps": 1e-5, "max_position_embeddings": 32768,
-    "tie_word_embeddings": False, "hidden_act": "silu", "bos_token_id": 1, "eos_token_id": 2,
-}
-# Other sizes of the same architecture, for measurements beyond the headline (--sizes).
-OTHER_SIZES = {
-    "7b-v0.3": dict(MISTRAL_7B, vocab_size=32768, rope_theta=1e6, sliding_window=None),
-    "nemo-12b": dict(MISTRAL_7B, num_hidden_layers=40, hidden_size=5120, vocab_size=131072, rope_theta=1e6,
-                     sliding_window=None, max_position_embeddings=131072),
-}
+# Layer sizes come from the package's named configurations (the library itself takes every size
+# from config.json): Mistral 7B v0.1 is the benchmark configuration, the other two are measured
+# beside it (`points`) and on their own (--sizes).
 SIZE_NAMES = {"7b-v0.1": "Mistral-7B-v0.1 sizes", "7b-v0.3": "Mistral-7B-v0.3 sizes", "nemo-12b": "Mistral-NeMo-12B sizes"}
 CONTEXT = 2048          # tokens each sequence holds when decoding starts
 MAX_CONTEXT = 4096      # the benchmark's context length: what each sequence's cache may grow to
@@ -102,73 +90,60 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(rows)}
 
 
-def main() -> int:
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=128)
-    ap.add_argument("--warmup", type=int, default=8)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (reported)")
-    ap.add_argument("--sizes", default="7b-v0.1", choices=sorted(SIZE_NAMES), help="layer sizes (default: the headline configuration)")
-    ap.add_argument("--max-context", type=int, default=MAX_CONTEXT, help="what each sequence's cache may grow to")
-    ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS)
-    ap.add_argument("--points", default="1,64", help="other decode batch sizes to report, comma separated ('' = none)")
-    ap.add_argument("--no-prefill", action="store_true")
-    ap.add_argument("--context", type=int, default=CONTEXT, help="tokens each sequence holds when decoding starts")
-    a = ap.parse_args()
+class Rig:
+    """One random-weight model of a named configuration with a session sized for the batches to be
+    measured, and the measurements themselves."""
 
-    if a.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "the reference is a Rust crate (no setup.py/pyproject; no cargo or rustc on this image), "
-                          "pip cannot install it and it has no GPU or safetensors path"}))
-        return 0
-    if a.gpus != 1:
-        print(f"bench.py: this library runs on one GPU; --gpus {a.gpus} is not supported")
-        return 2
-    if a.warmup < 3:
-        a.warmup = 3
+    def __init__(self, sizes: str, layers, batches, context: int, max_context: int, prefill_tokens: int,
+                 steps: int, warmup: int, seed: int = 0):
+        import numpy as np
+        import torch
+        from inference_engine_rust_b200 import LoadedModel, Sampler, SamplingParams
+        from inference_engine_rust_b200.config import preset
+        self.np, self.torch = np, torch
+        base = preset(sizes)
+        self.full_layers = base["num_hidden_layers"]
+        self.layers = layers or self.full_layers
+        self.cfg = dict(base, num_hidden_layers=self.layers)
+        self.context, self.prefill_tokens = context, prefill_tokens
+        self.max_context = max(max_context, context + 3 * (steps + warmup) + 8, prefill_tokens)
+        t0 = time.time()
+        self.model = LoadedModel.random(self.cfg, seed=seed, dtype="bfloat16", std=0.02, on_device=True)
+        torch.cuda.synchronize()
+        self.load_s = time.time() - t0
+        biggest = max(batches)
+        per_seq = -(-(context + 3 * (steps + warmup) + 8) // 64) * 64     # the timed run and the two end-to-end runs
+        self.session = self.model.session(max_tokens=max(biggest * per_seq, -(-prefill_tokens // 64) * 64),
+                                          max_sequences=biggest, max_seq_len=self.max_context)
+        self.eng = self.session.engine
+        self.sampler = Sampler(SamplingParams(temperature=0.0), self.eng.rt.err)
+        self.rng = np.random.default_rng(0)
+        self.vocab = self.cfg["vocab_size"]
 
-    import numpy as np
-    import torch
-    from inference_engine_rust_b200 import LoadedModel, Sampler, SamplingParams
-    from inference_engine_rust_b200.csrc import bindings as B
+    def close(self):
+        self.model = self.session = self.eng = self.sampler = None
+        self.torch.cuda.empty_cache()
 
-    pk = peaks()
-    base = MISTRAL_7B if a.sizes == "7b-v0.1" else OTHER_SIZES[a.sizes]
-    full_layers = base["num_hidden_layers"]
-    a.layers = a.layers or full_layers
-    a.max_context = max(a.max_context, a.context + 3 * (a.steps + a.warmup) + 8, a.prefill_tokens)
-    cfg = dict(base, num_hidden_layers=a.layers)
-    t0 = time.time()
-    model = LoadedModel.random(cfg, seed=0, dtype="bfloat16", std=0.02, on_device=True)
-    torch.cuda.synchronize()
-    load_s = time.time() - t0
-    batches = [a.batch] + [int(b) for b in a.points.split(",") if b.strip()]
-    biggest = max(batches)
-    per_seq = -(-(a.context + 3 * (a.steps + a.warmup) + 8) // 64) * 64     # the timed run and the two end-to-end runs
-    session = model.session(max_tokens=max(biggest * per_seq, -(-a.prefill_tokens // 64) * 64), max_sequences=biggest, max_seq_len=a.max_context)
-    eng = session.engine
-    sampler = Sampler(SamplingParams(temperature=0.0), eng.rt.err)
-    rng = np.random.default_rng(0)
-    vocab = cfg["vocab_size"]
-    clocks = ClockSampler()
-    clocks.start()
-
-    def prefill_slots(n):
+    def prefill_slots(self, n):
         slots = []
         for _ in range(n):
-            s = eng.open_sequence()
-            eng.step([(s, rng.integers(0, vocab, a.context).tolist())], want=None)
+            s = self.eng.open_sequence()
+            self.eng.step([(s, self.rng.integers(0, self.vocab, self.context).tolist())], want=None)
             slots.append(s)
-        torch.cuda.synchronize()
+        self.torch.cuda.synchronize()
         return slots
 
-    def decode_device(slots, steps, warmup):
+    def release(self, slots):
+        for s in slots:
+            self.eng.close_sequence(s)
+
+    def decode_device(self, slots, steps, warmup):
         """K steps timed on the device; tokens of each step are given by the host ahead of
         time (random ids), the next-token choice is launched but not waited for."""
+        from inference_engine_rust_b200.csrc import bindings as B
+        torch, eng = self.torch, self.eng
         n = len(slots)
-        toks = rng.integers(0, vocab, (steps + warmup, n))
+        toks = self.rng.integers(0, self.vocab, (steps + warmup, n))
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         launches0 = 0
         for i in range(steps + warmup):
@@ -177,18 +152,19 @@ def main() -> int:
                 launches0 = B.launch_count + eng.graph_launches
                 start.record()
             logits = eng.step([(s, [int(t)]) for s, t in zip(slots, toks[i])], want="last")
-            sampler.sample_device(logits, list(range(n)), [i] * n)
+            self.sampler.sample_device(logits, list(range(n)), [i] * n)
         end.record()
         torch.cuda.synchronize()
         eng.check_device()
         launches = B.launch_count + eng.graph_launches - launches0
         return start.elapsed_time(end) / steps, launches
 
-    def decode_e2e(slots, steps, warmup):
+    def decode_e2e(self, slots, steps, warmup):
         """The same through the call a user makes every step: host ids in (pinned staging and
         one copy to the device), host ids out (the sampled tokens read back)."""
+        torch, eng = self.torch, self.eng
         n = len(slots)
-        cur = rng.integers(0, vocab, n).tolist()
+        cur = self.rng.integers(0, self.vocab, n).tolist()
         h2d = d2h = 0
         for i in range(steps + warmup):
             if i == warmup:
@@ -196,19 +172,20 @@ def main() -> int:
                 t_start = time.perf_counter()
                 h2d = d2h = 0
             logits = eng.step([(s, [t]) for s, t in zip(slots, cur)], want="last")
-            cur = sampler(logits, list(range(n)), [i] * n)
+            cur = self.sampler(logits, list(range(n)), [i] * n)
             h2d += eng.h2d_bytes_last_step
             d2h += 4 * n + 4
         torch.cuda.synchronize()
         dt = time.perf_counter() - t_start
         return dt * 1e3 / steps, h2d // steps, d2h // steps
 
-    def decode_e2e_run_ahead(slots, steps, warmup):
+    def decode_e2e_run_ahead(self, slots, steps, warmup):
         """As the library's generation loop runs it: the ids chosen on the device feed the next step
         from device memory, and the host reads every step's ids while the next step runs."""
+        torch, eng, sampler = self.torch, self.eng, self.sampler
         n = len(slots)
         reqs = list(range(n))
-        logits = eng.step([(s, [int(t)]) for s, t in zip(slots, rng.integers(0, vocab, n))], want="last")
+        logits = eng.step([(s, [int(t)]) for s, t in zip(slots, self.rng.integers(0, self.vocab, n))], want="last")
         chosen = sampler.sample_device(logits, reqs, [0] * n)
         pending = sampler.read_async(chosen)
         for i in range(steps + warmup):
@@ -223,30 +200,22 @@ def main() -> int:
         torch.cuda.synchronize()
         return (time.perf_counter() - t_start) * 1e3 / steps
 
-    result = {}
-    points = {}
-    main_stats = None
-    for nb in batches:
-        slots = prefill_slots(nb)
-        m0 = clocks.mark()
-        ms, launches = decode_device(slots, a.steps, a.warmup)
-        m1 = clocks.mark()
-        if nb == a.batch and main_stats is None:
-            kv_bytes = eng.cache.kv_bytes_read(slots)
-            e2e_ms, h2d, d2h = decode_e2e(slots, min(a.steps, 64), a.warmup)
-            ahead_ms = decode_e2e_run_ahead(slots, min(a.steps, 64), a.warmup)
-            main_stats = dict(ms=ms, launches=launches, kv_bytes=kv_bytes, e2e_ms=e2e_ms, h2d=h2d, d2h=d2h, ahead_ms=ahead_ms,
-                              clocks=clocks.summary(m0, m1))
-        else:
-            points[f"decode_b{nb}"] = round(nb * 1e3 / ms, 1)
-        for s in slots:
-            eng.close_sequence(s)
+    def step_bytes(self, slots):
+        """Bytes a one-token step over `slots` has to read: every weight once, the live keys and values."""
+        return self.model.model.weight_bytes_per_step() + self.eng.cache.kv_bytes_read(slots)
 
-    prefill = None
-    if not a.no_prefill:
-        prompt = rng.integers(0, vocab, a.prefill_tokens).tolist()
+    def prefill_flops(self):
+        cfg, T, L = self.cfg, self.prefill_tokens, self.layers
+        H, I, V = cfg["hidden_size"], cfg["intermediate_size"], self.vocab
+        qkv = (cfg["num_attention_heads"] + 2 * cfg["num_key_value_heads"]) * cfg["head_dim"]
+        qd = cfg["num_attention_heads"] * cfg["head_dim"]
+        return 2 * T * L * (H * qkv + qd * H + 3 * H * I) + 2 * H * V + L * 2 * T * T * qd
+
+    def prefill(self, runs=5, warm=3):
+        torch, eng = self.torch, self.eng
+        prompt = self.rng.integers(0, self.vocab, self.prefill_tokens).tolist()
         times = []
-        for i in range(3 + 5):
+        for i in range(warm + runs):
             s = eng.open_sequence()
             start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             start.record()
@@ -254,26 +223,198 @@ def main() -> int:
             end.record()
             torch.cuda.synchronize()
             eng.close_sequence(s)
-            if i >= 3:
+            if i >= warm:
                 times.append(start.elapsed_time(end))
+        return times
+
+    # ---- the dominant kernels one by one -----------------------------------------------------
+    def kernel_table(self, batch: int, pk):
+        """CUDA-event times of the projections (at `batch` tokens and at the prefill length) and of
+        decode attention (over the live cache of `batch` sequences), each launched once per layer
+        in turn so that its operands come from memory, not from the L2 (32 layers of weights)."""
+        import torch
+        from inference_engine_rust_b200.parts.base import StepContext
+        from inference_engine_rust_b200.csrc import bindings as B
+        eng, rt, cfg = self.eng, self.eng.rt, self.cfg
+        blocks = eng.model.blocks
+        H, I = cfg["hidden_size"], cfg["intermediate_size"]
+        stream = B.stream_ptr()
+        out = []
+
+        def timed(fn, reps):
+            for _ in range(2):
+                fn()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            start.record()
+            for _ in range(reps):
+                fn()
+            end.record()
+            torch.cuda.synchronize()
+            return start.elapsed_time(end) * 1e3 / (reps * len(blocks))          # us per launch
+
+        for M, what in ((batch, f"one-token step, {batch} tokens"), (self.prefill_tokens, f"prompt, {self.prefill_tokens} tokens")):
+            x = (torch.randn(M, H, device=rt.device) * 0.5).bfloat16()
+            a_in = (torch.randn(M, I, device=rt.device) * 0.5).bfloat16()
+            res = torch.zeros(M, H, device=rt.device)
+            q_out = torch.empty(M, blocks[0].mixer.qkv.out_features, device=rt.device, dtype=torch.bfloat16)
+            act = torch.empty(M, I, device=rt.device, dtype=torch.bfloat16)
+            o_in = (torch.randn(M, blocks[0].mixer.q_dim, device=rt.device) * 0.5).bfloat16()
+            from inference_engine_rust_b200.parts import fast_linear
+            cases = [
+                ("qkv", lambda b: b.mixer.qkv.apply(x, q_out, M, stream), blocks[0].mixer.qkv),
+                ("o + residual", lambda b: b.mixer.o.apply(o_in, res, M, stream, add_residual=True), blocks[0].mixer.o),
+                ("gate-up + silu", lambda b: fast_linear.apply_gated(b.ffn.gate_up, x, act, M, stream), blocks[0].ffn.gate_up),
+                ("down + residual", lambda b: b.ffn.down.apply(a_in, res, M, stream, add_residual=True), blocks[0].ffn.down),
+            ]
+            for name, call, lin in cases:
+                us = timed(lambda: [call(b) for b in blocks], 3)
+                n, k = lin.weight.shape
+                flops, nbytes = 2.0 * M * n * k, lin.nbytes()
+                row = {"kernel": name, "where": what, "us": round(us, 2)}
+                if M <= 64:
+                    row["gb_s"] = round(nbytes / us / 1e3, 1)
+                    row["frac"] = round(nbytes / us / 1e3 / pk["hbm_gbs"], 3)
+                else:
+                    row["tflops"] = round(flops / us / 1e6, 1)
+                    row["frac"] = round(flops / us / 1e6 / pk["bf16_tflops"], 3)
+                out.append(row)
+        # decode attention over the live cache: the mixer's own kernel, layer after layer
+        slots = self.prefill_slots(batch)
+        n = len(slots)
+        o_cu, o_slot, o_pos, o_seq, o_tok, o_rows, total = eng._layout(n, n, 0)
+        meta = torch.zeros(total, dtype=torch.int32, device=rt.device)
+        pos0 = [eng.length(s) for s in slots]
+        meta[o_cu:o_cu + n + 1] = torch.arange(n + 1, dtype=torch.int32)
+        meta[o_slot:o_slot + n] = torch.tensor(slots, dtype=torch.int32)
+        meta[o_pos:o_pos + n] = torch.tensor(pos0, dtype=torch.int32)
+        meta[o_seq:o_seq + n] = torch.arange(n, dtype=torch.int32)
+        for s in slots:
+            eng.cache.reserve(s, eng.length(s) + 1)
+        eng.cache.upload()
+        ctx = eng._context("decode", meta, n, n, [1] * n, pos0, slots)
+        from inference_engine_rust_b200.parts import fast_attention
+        mix = blocks[0].mixer
+        qkv = (torch.randn(n, mix.q_dim + 2 * mix.kv_dim, device=rt.device) * 0.5).bfloat16()
+        a_out = torch.empty(n, mix.q_dim, device=rt.device, dtype=torch.bfloat16)
+        views = [eng.cache.layer_view(eng.model.spec.cache_entry(i)) for i in range(len(blocks))]
+        us = timed(lambda: [fast_attention.decode_with_rotation(b.mixer, qkv, a_out, ctx, v, True) for b, v in zip(blocks, views)], 3)
+        kv_bytes = eng.cache.kv_bytes_read(slots) / len(blocks)
+        out.append({"kernel": "decode attention (rotation, cache write, merge of the splits)", "where": f"{batch} sequences of {self.context} tokens",
+                    "us": round(us, 2), "gb_s": round(kv_bytes / us / 1e3, 1), "frac": round(kv_bytes / us / 1e3 / pk["hbm_gbs"], 3)})
+        eng.check_device()
+        self.release(slots)
+        return out
+
+
+def other_sizes_points(pk, steps: int, warmup: int):
+    """Short measurements at the two other configurations of the architecture: Mistral 7B v0.3 sizes
+    with eight sequences at 8,192 tokens of context, Mistral NeMo 12B sizes at batch 32 and batch 1
+    (2,048 tokens of context) and its 2,048-token prefill.  Each with its fraction of the measured
+    peak (the one-token steps of the memory rate, the prefill of the tensor rate)."""
+    pts = {}
+    rig = Rig("7b-v0.3", None, [8], 8192, 16384, 64, steps, warmup, seed=1)
+    slots = rig.prefill_slots(8)
+    ms, _ = rig.decode_device(slots, steps, warmup)
+    pts["v03_b8_ctx8192_ms"] = round(ms, 3)
+    pts["v03_b8_ctx8192_frac"] = round(rig.step_bytes(slots) / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+    rig.release(slots)
+    rig.close()
+    rig = Rig("nemo-12b", None, [32, 1], 2048, 4096, 2048, steps, warmup, seed=2)
+    for nb, key in ((32, "nemo_b32"), (1, "nemo_b1")):
+        slots = rig.prefill_slots(nb)
+        ms, _ = rig.decode_device(slots, steps, warmup)
+        if nb == 1:
+            pts["nemo_b1_tok_s"] = round(1e3 / ms, 1)
+        else:
+            pts["nemo_b32_ms"] = round(ms, 3)
+        pts[key + "_frac"] = round(rig.step_bytes(slots) / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+        rig.release(slots)
+    times = rig.prefill(runs=3, warm=2)
+    pms = statistics.median(times)
+    pts["nemo_prefill_2048_ms"] = round(pms, 2)
+    pts["nemo_prefill_2048_frac"] = round(rig.prefill_flops() / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)
+    rig.close()
+    return pts
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (reported)")
+    ap.add_argument("--sizes", default="7b-v0.1", choices=sorted(SIZE_NAMES), help="layer sizes (default: the headline configuration)")
+    ap.add_argument("--max-context", type=int, default=MAX_CONTEXT, help="what each sequence's cache may grow to")
+    ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS)
+    ap.add_argument("--points", default="1,64", help="other decode batch sizes to report, comma separated ('' = none)")
+    ap.add_argument("--no-prefill", action="store_true")
+    ap.add_argument("--context", type=int, default=CONTEXT, help="tokens each sequence holds when decoding starts")
+    ap.add_argument("--no-other-sizes", action="store_true",
+                    help="skip the short measurements at Mistral 7B v0.3 and NeMo 12B sizes (points v03_*, nemo_*)")
+    ap.add_argument("--kernels", action="store_true",
+                    help="also time the dominant kernels one by one with CUDA events (projections and decode "
+                         "attention at the decode batch, projections at the prefill length): key 'kernels'")
+    a = ap.parse_args()
+
+    if a.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference is a Rust crate (no setup.py/pyproject; no cargo or rustc on this image), "
+                          "pip cannot install it and it has no GPU or safetensors path"}))
+        return 0
+    if a.gpus != 1:
+        print(f"bench.py: this library runs on one GPU; --gpus {a.gpus} is not supported")
+        return 2
+    if a.warmup < 3:
+        a.warmup = 3
+
+    pk = peaks()
+    batches = [a.batch] + [int(b) for b in a.points.split(",") if b.strip()]
+    rig = Rig(a.sizes, a.layers, batches, a.context, a.max_context, a.prefill_tokens, a.steps, a.warmup)
+    cfg, vocab = rig.cfg, rig.vocab
+    clocks = ClockSampler()
+    clocks.start()
+
+    points = {}
+    main_stats = None
+    for nb in batches:
+        slots = rig.prefill_slots(nb)
+        m0 = clocks.mark()
+        ms, launches = rig.decode_device(slots, a.steps, a.warmup)
+        m1 = clocks.mark()
+        if nb == a.batch and main_stats is None:
+            step_bytes = rig.step_bytes(slots)
+            e2e_ms, h2d, d2h = rig.decode_e2e(slots, min(a.steps, 64), a.warmup)
+            ahead_ms = rig.decode_e2e_run_ahead(slots, min(a.steps, 64), a.warmup)
+            main_stats = dict(ms=ms, launches=launches, step_bytes=step_bytes, e2e_ms=e2e_ms, h2d=h2d, d2h=d2h,
+                              ahead_ms=ahead_ms, clocks=clocks.summary(m0, m1))
+        else:
+            points[f"decode_b{nb}"] = round(nb * 1e3 / ms, 1)
+            points[f"decode_b{nb}_frac"] = round(rig.step_bytes(slots) / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+        rig.release(slots)
+
+    prefill = None
+    if not a.no_prefill:
+        times = rig.prefill()
         pms = statistics.median(times)
-        H, I, V, L = cfg["hidden_size"], cfg["intermediate_size"], vocab, a.layers
-        qkv = (cfg["num_attention_heads"] + 2 * cfg["num_key_value_heads"]) * cfg["head_dim"]
-        qd = cfg["num_attention_heads"] * cfg["head_dim"]
-        T = a.prefill_tokens
-        flops = 2 * T * L * (H * qkv + qd * H + 3 * H * I) + 2 * H * V + L * 2 * T * T * qd
+        T, flops = a.prefill_tokens, rig.prefill_flops()
         prefill = {"value": round(T * 1e3 / pms, 1), "tokens": T, "ms": round(pms, 3),
                    "frac": round(flops / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4), "unit": "tokens/s",
                    "tflops": round(flops / (pms * 1e-3) / 1e12, 1), "peak_tflops": pk["bf16_tflops"],
                    "runs": len(times), "ms_min": round(min(times), 3), "ms_max": round(max(times), 3)}
         if "bf16_tflops_sustained" in pk:      # the step is tens of milliseconds of dense tensor work
             prefill["frac_of_sustained"] = round(flops / (pms * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12), 4)
+    kernels = rig.kernel_table(a.batch, pk) if a.kernels else None
+    load_s, layers, full_layers, max_context = rig.load_s, rig.layers, rig.full_layers, rig.max_context
+    rig.close()
+    if not a.no_other_sizes and a.sizes == "7b-v0.1" and a.layers is None:
+        points.update(other_sizes_points(pk, min(a.steps, 32), max(3, min(a.warmup, 4))))
     clocks.stop()
 
     ms = main_stats["ms"]
-    weight_bytes = model.model.weight_bytes_per_step()
-    step_bytes = weight_bytes + main_stats["kv_bytes"]
-    achieved = step_bytes / (ms * 1e-3) / 1e9
+    achieved = main_stats["step_bytes"] / (ms * 1e-3) / 1e9
     value = a.batch * 1e3 / ms
     line = {
         "metric": "decode tok/s at batch 1/8/64; prefill tok/s at 2,048 tokens (Mistral 7B)",
@@ -281,12 +422,12 @@ def main() -> int:
         "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic (random weights N(0, 0.02), uniform random token ids)",
         "impl": "ours",
-        "config": {"model": SIZE_NAMES[a.sizes], "layers": a.layers, "layers_of_config": full_layers,
+        "config": {"model": SIZE_NAMES[a.sizes], "layers": layers, "layers_of_config": full_layers,
                    "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
                    "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
                    "intermediate": cfg["intermediate_size"], "vocab": vocab, "sliding_window": cfg["sliding_window"],
                    "rope_theta": cfg["rope_theta"], "rms_norm_eps": cfg["rms_norm_eps"],
-                   "global_batch": a.batch, "seq_len": a.context, "max_context": a.max_context,
+                   "global_batch": a.batch, "seq_len": a.context, "max_context": max_context,
                    "prefill_tokens": a.prefill_tokens, "parallelism": "single GPU",
                    "l2": "inputs larger than L2 (weights read per step exceed 126 MB many times)",
                    "peaks": pk["source"]},
@@ -303,6 +444,8 @@ def main() -> int:
     }
     if prefill:
         line["prefill"] = prefill
+    if kernels is not None:
+        line["kernels"] = kernels
     print(json.dumps(line))
     return 0
 

@@ -7,7 +7,8 @@ of programmatic dependent ones; the last split of a tile adding alone; the resid
 written by the epilogue instead of added by TMA; another order of the tiles) the results are
 equal to the bit; where it changes the order of a sum or the kernel (no parts in the last wave,
 the mma.sync prompt attention, cp.async pages, a separate rotation kernel, an even cut of the
-keys) they agree within the bfloat16 tolerance of the logits.
+keys, split-K projections in one-token steps, norms as kernels of their own) they agree within
+the bfloat16 tolerance of the logits.
 """
 import os
 import subprocess
@@ -31,12 +32,14 @@ SWITCHES = {            # switch -> are the results equal to the bit with it off
     "IERT_FUSED_ROPE": False,
     "IERT_DECODE_TMA": False,
     "IERT_DECODE_BALANCE": False,
+    "IERT_GEMM_ROWS_MAX": False,        # 0: one-token projections on the tcgen05 kernel with split-K
+    "IERT_NORM_AHEAD": False,           # 0: every norm a kernel of its own
 }
 
 
 @pytest.fixture(scope="module")
 def runs(tmp_path_factory):
-    """All ten processes at once (each holds a two-layer model: they share the device easily)."""
+    """All the processes at once (each holds a two-layer model: they share the device easily)."""
     root = tmp_path_factory.mktemp("switches")
     procs = {}
     for name in [None] + list(SWITCHES):
