@@ -806,14 +806,18 @@ int sm_count() {
   return n;
 }
 
+// Dynamic shared memory of a launch: ring, alignment slack, barriers; the weight-major gated tile
+// adds its exchange buffer, the residual add by TMA its two staging buffers.  The one formula for
+// the launch and for the estimate of how many CTAs an SM holds (ctas_per_sm_of).
+constexpr size_t dynamic_smem_bytes(int stages, int stage_bytes, bool gated_weight_major, bool tma_out) {
+  return (size_t)stages * stage_bytes + 1024 + 256 + (gated_weight_major ? XCH_BYTES : 0) + (tma_out ? 2 * OUT_STAGE_BYTES + 128 : 0);
+}
+
 template <int BT, bool GATED>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, GemmParams p, int grid, cudaStream_t stream,
            const CUtensorMap* mo = nullptr) {
   constexpr int STAGE_BYTES = (GATED ? 2 : 1) * W_STAGE_BYTES + BT * TILE_K * 2;
-  // ring, alignment slack, barriers; the weight-major gated tile adds its exchange buffer, the
-  // residual add by TMA its two staging buffers
-  const size_t smem = (size_t)p.stages * STAGE_BYTES + 1024 + 256 + ((!GATED && p.mode == MODE_GATED_SILU) ? XCH_BYTES : 0) +
-                      (p.tma_out ? 2 * OUT_STAGE_BYTES + 128 : 0);
+  const size_t smem = dynamic_smem_bytes(p.stages, STAGE_BYTES, !GATED && p.mode == MODE_GATED_SILU, p.tma_out != 0);
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(gemm_tc_kernel<BT, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess)
@@ -834,7 +838,8 @@ int ctas_per_sm_of(int stages) {
   static int cached[13] = {0};
   if (stages < 0 || stages > 12) return 0;
   if (!cached[stages]) {
-    const size_t smem = (size_t)stages * (W_STAGE_BYTES + BT * TILE_K * 2) + 1024 + 256;
+    // (a plain weight-major launch: no exchange buffer, no TMA-out staging; only such launches reduce cooperatively)
+    const size_t smem = dynamic_smem_bytes(stages, W_STAGE_BYTES + BT * TILE_K * 2, false, false);
     int n = 0, dev = 0, smem_sm = 0, regs_sm = 0;
     cudaFuncAttributes a;
     if (cudaGetDevice(&dev) == cudaSuccess && cudaFuncGetAttributes(&a, gemm_tc_kernel<BT, false>) == cudaSuccess &&
@@ -985,9 +990,14 @@ IERT_API int iert_gemm_tc(const void* x, long long ldx, const void* w, long long
     if (st >= 2 && (force_stages <= 0 || st == stages)) { p.tma_out = 1; stages = st; p.stages = st; }
   }
   int grid = total_work < slots ? total_work : slots;
-  // the splits of a tile may wait for one another only if every CTA of the grid is resident
+  // The splits of a tile may wait for one another only if every CTA of the grid is resident.  Residency is
+  // estimated (resident_ctas_per_sm) from the registers, the tensor memory and the shared memory of a PLAIN
+  // weight-major launch: no gated tile (that is another entry point) and no residual add by TMA (that needs
+  // splits == 1, the cooperative reduction splits > 1).  A variant that breaks this must not reduce
+  // cooperatively, or its waits could expire: refuse it here rather than find out on the device.
   p.coop_reduce = splits > 1 && !no_coop() && total_work <= grid &&
                   grid <= sm_count() * resident_ctas_per_sm(bt, stages);
+  if (p.coop_reduce && (p.tma_out || p.mode == MODE_GATED_SILU || p.tail_parts > 1)) return IERT_BAD_ARGUMENT;
   // Residual adds over many tokens whose tiles leave the last wave part empty: the tiles of that
   // wave are cut into parts of k (see WorkIter).  One CTA per SM; parts chosen to fill the SMs.
   if (!force_splits && !no_tail_parts() && splits == 1 && mode == MODE_ADD_RESIDUAL && bt >= 128 && ctas_per_sm == 1 &&
