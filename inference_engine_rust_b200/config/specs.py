@@ -9,7 +9,7 @@ per-layer vectors (`LayerDims`, `LayerAttentionSpec`: src/model_config.rs:74-100
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Mapping, Optional, Sequence
+from typing import Any, Mapping, Optional, Sequence, Tuple
 
 
 @dataclass(frozen=True)
@@ -28,17 +28,23 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """A layer = block arrangement + norm + mixer + feed-forward, with the tensor-name
-    prefixes under which each part finds its weights."""
+    """A layer = block arrangement + norms + mixer + feed-forward, with the tensor-name
+    prefixes under which each part finds its weights.
+
+    The usual layer has two norms of one kind (before the mixer, before the feed-forward).  A block
+    arrangement that needs more (norms after the mixer or the feed-forward, a norm of another kind)
+    names them in `extra_norms`: role -> (spec, weight tensor name); its block class receives them
+    built, by role.  `ffn` may be None for a layer that has no feed-forward."""
 
     block: PartSpec            # arrangement, e.g. kind "prenorm"
     norm: PartSpec             # the norm used before the mixer and before the feed-forward
     mixer: PartSpec            # token mixer, e.g. kind "attention"
-    ffn: PartSpec              # feed-forward, e.g. kind "swiglu"
+    ffn: Optional[PartSpec]    # feed-forward, e.g. kind "swiglu"; None: the layer has none
     mixer_prefix: str          # e.g. "model.layers.3.self_attn."
     ffn_prefix: str            # e.g. "model.layers.3.mlp."
     mixer_norm_name: str       # e.g. "model.layers.3.input_layernorm.weight"
     ffn_norm_name: str         # e.g. "model.layers.3.post_attention_layernorm.weight"
+    extra_norms: Mapping[str, Tuple[PartSpec, str]] = field(default_factory=dict)
 
 
 @dataclass(frozen=True)

@@ -200,6 +200,29 @@ def rope_kv_store(qkv, batch: BatchView, kv: KvView, inv_freq, heads: int, rotar
                                     1 if write_cache else 0, err.data_ptr(), stream), "rope_kv_store")
 
 
+_no_rotation = {}
+
+
+def _zero_freq(device):
+    key = str(device)
+    if key not in _no_rotation:
+        _no_rotation[key] = torch.zeros(1, dtype=torch.float32, device=device)
+    return _no_rotation[key]
+
+
+def kv_store(qkv, batch: BatchView, kv: KvView, heads: int, err, stream) -> None:
+    """Write the step's keys and values (as they stand in the packed projection) into the cache."""
+    rope_kv_store(qkv, batch, kv, _zero_freq(qkv.device), heads, 0, PAIR_HALF, True, err, stream)
+
+
+def rotate_qk(qkv, batch: BatchView, inv_freq, heads: int, kv_heads: int, head_dim: int, rotary_dim: int,
+              pairing: int, err, stream) -> None:
+    """Rotate the step's queries and keys in place; nothing is stored."""
+    geometry = KvView(k=None, v=None, page_table=None, table_width=0, ring_pages=1, page_tokens=1, n_pages=0,
+                      kv_heads=kv_heads, head_dim=head_dim, dtype=dtype_code(qkv.dtype), window=0)
+    rope_kv_store(qkv, batch, geometry, inv_freq, heads, rotary_dim, pairing, False, err, stream)
+
+
 def silu_mul(gu, out, n_tokens: int, inter: int, stream) -> None:
     check(core().iert_silu_mul(gu.data_ptr(), out.data_ptr(), dtype_code(gu.dtype), n_tokens, inter,
                                stream), "silu_mul")

@@ -14,7 +14,7 @@ import torch
 from ..cache import CacheRequest
 from ..config.specs import ModelSpec
 from ..csrc import bindings as B
-from ..parts.base import Runtime, StepContext, part_class
+from ..parts.base import Runtime, StepContext, first_norm_request_of, part_class
 from ..parts.linear import Linear
 from ..weights.loader import (RandomSource, TensorSpec, WeightError, check_source, fetch_many)
 
@@ -28,14 +28,18 @@ class Model:
         self._layer_parts = []       # (norm1, mixer, norm2, ffn) per layer
         self._cut_askers = None
         h = spec.hidden_size
+        self._extra_norms = []       # {role: norm} per layer (arrangements with more than two norms)
         for ls in spec.layers:
             norm_cls = part_class("norm", ls.norm.kind)
             norm1 = norm_cls(ls.norm, h, rt)
-            norm2 = norm_cls(ls.norm, h, rt)
+            norm2 = norm_cls(ls.norm, h, rt) if ls.ffn is not None else None
             mixer = part_class("mixer", ls.mixer.kind)(ls.mixer, rt)
-            ffn = part_class("ffn", ls.ffn.kind)(ls.ffn, rt)
-            block = part_class("block", ls.block.kind)(ls, norm1, mixer, norm2, ffn, rt)
+            ffn = part_class("ffn", ls.ffn.kind)(ls.ffn, rt) if ls.ffn is not None else None
+            extra = {role: part_class("norm", ns.kind)(ns, h, rt) for role, (ns, _) in ls.extra_norms.items()}
+            kw = {"extra_norms": extra} if extra else {}
+            block = part_class("block", ls.block.kind)(ls, norm1, mixer, norm2, ffn, rt, **kw)
             self._layer_parts.append((norm1, mixer, norm2, ffn))
+            self._extra_norms.append(extra)
             self.blocks.append(block)
         self.final_norm = part_class("norm", spec.final_norm.kind)(spec.final_norm, h, rt)
         self.embedding: Optional[torch.Tensor] = None
@@ -54,13 +58,16 @@ class Model:
         }
         if spec.lm_head_name is not None:
             out[spec.lm_head_name] = TensorSpec((spec.vocab_size, spec.hidden_size))
-        for ls, (norm1, mixer, norm2, ffn) in zip(spec.layers, self._layer_parts):
+        for ls, (norm1, mixer, norm2, ffn), extra in zip(spec.layers, self._layer_parts, self._extra_norms):
             out[ls.mixer_norm_name] = norm1.tensor_specs()["weight"]
-            out[ls.ffn_norm_name] = norm2.tensor_specs()["weight"]
             for local, ts in mixer.tensor_specs().items():
                 out[ls.mixer_prefix + local] = ts
-            for local, ts in ffn.tensor_specs().items():
-                out[ls.ffn_prefix + local] = ts
+            if ffn is not None:
+                out[ls.ffn_norm_name] = norm2.tensor_specs()["weight"]
+                for local, ts in ffn.tensor_specs().items():
+                    out[ls.ffn_prefix + local] = ts
+            for role, norm in extra.items():
+                out[ls.extra_norms[role][1]] = norm.tensor_specs()["weight"]
         return out
 
     def load(self, source, where: str = "weights", strict: bool = True) -> None:
@@ -99,11 +106,14 @@ class Model:
         self.lm_head = Linear(head, rt)
         if head_name is None and self.lm_head.weight.dtype == self.embedding.dtype:
             self.embedding = self.lm_head.weight          # tied: one copy
-        for ls, (norm1, mixer, norm2, ffn) in zip(spec.layers, self._layer_parts):
+        for ls, (norm1, mixer, norm2, ffn), extra in zip(spec.layers, self._layer_parts, self._extra_norms):
             norm1.load({"weight": get(ls.mixer_norm_name)})
-            norm2.load({"weight": get(ls.ffn_norm_name)})
             mixer.load({local: get(ls.mixer_prefix + local) for local in mixer.tensor_specs()})
-            ffn.load({local: get(ls.ffn_prefix + local) for local in ffn.tensor_specs()})
+            if ffn is not None:
+                norm2.load({"weight": get(ls.ffn_norm_name)})
+                ffn.load({local: get(ls.ffn_prefix + local) for local in ffn.tensor_specs()})
+            for role, norm in extra.items():
+                norm.load({"weight": get(ls.extra_norms[role][1])})
         self.loaded = True
 
     def load_random(self, seed: int, std: float = 0.02, on_device: bool = False) -> None:
@@ -127,7 +137,8 @@ class Model:
         from device memory only, so a captured launch sequence stays right for later steps."""
         parts = [self.final_norm]
         for e in self.spec.schedule:
-            parts.extend(self._layer_parts[e.layer])
+            parts.extend(p for p in self._layer_parts[e.layer] if p is not None)
+            parts.extend(self._extra_norms[e.layer].values())
             parts.append(self.blocks[e.layer])
         return all(getattr(p, "graph_safe", False) for p in parts)
 
@@ -138,9 +149,9 @@ class Model:
         for e in self.spec.schedule:
             norm1, mixer, norm2, ffn = self._layer_parts[e.layer]
             for part in (mixer, ffn):
-                if hasattr(part, "weight_bytes"):
+                if part is not None and hasattr(part, "weight_bytes"):
                     total += part.weight_bytes()
-            for n in (norm1, norm2):
+            for n in (norm1, norm2, *self._extra_norms[e.layer].values()):
                 if getattr(n, "weight", None) is not None:
                     total += n.weight.numel() * n.weight.element_size()
         return total
@@ -176,7 +187,7 @@ class Model:
         x = ws.take("model.residual", (T, H), torch.float32)
         sched = spec.schedule
         # the first block's first norm may ask the embedding kernel for its element-wise half
-        request = self.blocks[sched[0].layer].first_norm_request(ctx) if sched else None
+        request = first_norm_request_of(self.blocks[sched[0].layer], ctx) if sched else None
         ahead = finish = None
         if request is not None:
             from ..parts.norm import honour

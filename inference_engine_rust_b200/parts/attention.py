@@ -96,7 +96,17 @@ class Attention(Mixer):
             if fast_attention.decode_with_rotation(self, qkv, out, ctx, cache_view, writes_cache):
                 self.o.apply(out, residual, T, ctx.stream, add_residual=True, ctx=ctx)
                 return
-        self.position.encode_and_store(qkv, ctx, kv, self.heads, writes_cache)
+        # positions for queries and keys, then the cache write (the mixer's own business); a plain
+        # rotation is fused with the write in one kernel
+        rot = getattr(self.position, "rotary_constants", lambda: None)()      # (optional in the interface)
+        if rot is not None:
+            inv_freq, rotary_dim, pairing = rot
+            B.rope_kv_store(qkv, ctx.batch, kv, inv_freq, self.heads, rotary_dim, pairing, writes_cache,
+                            rt.err, ctx.stream)
+        else:
+            self.position.encode(qkv, ctx, self.heads, self.kv_heads)
+            if writes_cache:
+                B.kv_store(qkv, ctx.batch, kv, self.heads, rt.err, ctx.stream)
         from_cache = ctx.kind == "decode" or not writes_cache
         if from_cache and ctx.kind == "prompt":
             cap = cache_view.group.ring_capacity

@@ -6,10 +6,10 @@ learns which model it belongs to.  Adding a part means registering a class under
 kind; the configuration then names that kind for the layers that use it.
 
     norm      Norm(spec, hidden_size, rt)        .forward(x_f32, out, ctx, rows_idx=None, rows=None)
-    position  PositionEncoding(spec, head_dim, rt)   .encode_and_store(qkv, ctx, kv, heads, writes_cache)
+    position  PositionEncoding(spec, head_dim, rt)   .encode(qkv, ctx, heads, kv_heads)   [.rotary_constants()]
     mixer     Mixer(spec, rt)                    .forward(xn, residual, ctx, cache_view, writes_cache)
     ffn       FeedForward(spec, rt)              .forward(xn, residual, ctx)
-    block     Block(layer_spec, norm1, mixer, norm2, ffn, rt)   .forward(x, ctx, cache_view, writes_cache)
+    block     Block(layer_spec, norm1, mixer, norm2, ffn, rt[, extra_norms={role: norm}])   .forward(x, ctx, cache_view, writes_cache)
 
 Optional, for one-token steps (see `NormRequest`, `LazyInput`): a norm may let the kernel that writes
 its input rows do its element-wise half and the projection that reads its output its row-wise half.
@@ -164,6 +164,12 @@ class StepContext:
         return max((p + q for p, q in zip(self.pos0, self.q_lens)), default=0)
 
 
+def first_norm_request_of(block, ctx) -> Optional["NormRequest"]:
+    """What `block` (any registered block class, or None) asks of whoever writes the rows it receives."""
+    ask = getattr(block, "first_norm_request", None)
+    return ask(ctx) if ask is not None else None
+
+
 class Part:
     """Common to all parts: which tensors it expects (local names) and how it takes them."""
 
@@ -186,16 +192,19 @@ class Norm(Part):
 
 
 class PositionEncoding(Part):
-    def encode_and_store(self, qkv, ctx: StepContext, kv, heads: int, writes_cache: bool) -> None:
+    """Gives queries and keys their positions.  It does not touch the cache: storing keys and
+    values is the mixer's business."""
+
+    def encode(self, qkv, ctx: StepContext, heads: int, kv_heads: int) -> None:
         """Give the step's queries and keys their positions, in place in `qkv`
-        ([tokens, (heads + 2 kv_heads) * head_dim], a token's absolute position being
-        ctx.batch.pos0[sequence] + its index in the sequence), then, if `writes_cache`, store
-        the keys and values in the cache `kv` (a csrc.bindings.KvView)."""
+        ([tokens, (heads + 2 kv_heads) * head_dim]: queries, keys, values; a token's absolute
+        position is ctx.batch.pos0[sequence] + its index in the sequence)."""
         raise NotImplementedError
 
     def rotary_constants(self):
         """(inv_freq fp32 device tensor, rotary_dim, pairing code) if the encoding is a plain
-        rotation that a mixer's kernel may apply itself, else None (the default)."""
+        rotation that a mixer's kernel may apply itself (fused with its cache write or with its
+        attention), else None (the default): the mixer then calls `encode`."""
         return None
 
 

@@ -1,9 +1,10 @@
-"""Arrangement of a layer's parts.  "prenorm": x += mixer(norm1(x)); x += ffn(norm2(x))
+"""Arrangement of a layer's parts.  "prenorm": x += mixer(norm1(x)); x += ffn(norm2(x)) (the second
+half left out for a layer without a feed-forward)
 (src/layers/block.rs:19-24,63-65; the residual uses the un-normed input,
 src/layers/attention.rs:757-759, src/layers/ffn.rs:113-116)."""
 from __future__ import annotations
 
-from .base import Block, Runtime, StepContext, register_part
+from .base import Block, Runtime, StepContext, first_norm_request_of, register_part
 
 
 class PreNormBlock(Block):
@@ -14,11 +15,17 @@ class PreNormBlock(Block):
 
     def forward(self, x, ctx: StepContext, cache_view, writes_cache: bool) -> None:
         xn = self._normed(self.norm1, x, ctx)
-        ctx.norm_ahead = self._request(self.norm2, self.ffn, ctx)     # of whoever adds the mixer's result into x
+        # what the next norm asks of whoever adds the mixer's result into x
+        if self.ffn is not None:
+            ctx.norm_ahead = self._request(self.norm2, self.ffn, ctx)
+        else:
+            ctx.norm_ahead = first_norm_request_of(ctx.next_block, ctx)
         self.mixer.forward(xn, x, ctx, cache_view, writes_cache)
+        if self.ffn is None:                     # a layer without a feed-forward
+            ctx.norm_ahead = None
+            return
         xn = self._normed(self.norm2, x, ctx)
-        nxt = ctx.next_block
-        ctx.norm_ahead = nxt.first_norm_request(ctx) if nxt is not None else None
+        ctx.norm_ahead = first_norm_request_of(ctx.next_block, ctx)
         self.ffn.forward(xn, x, ctx)
         ctx.norm_ahead = None
 

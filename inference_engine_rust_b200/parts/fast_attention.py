@@ -78,7 +78,7 @@ def decode_with_rotation(attn, qkv, out, ctx, cache_view, writes_cache: bool) ->
     """One-token step with the rotary encoding and the cache write inside the attention kernel.
     False (nothing launched) if the position encoding is no plain rotation or the kernel does
     not take this cache; the caller then encodes, stores and attends in separate kernels."""
-    rot = attn.position.rotary_constants()
+    rot = getattr(attn.position, "rotary_constants", lambda: None)()
     if rot is None or qkv.dtype != torch.bfloat16 or os.environ.get("IERT_FUSED_ROPE", "1") == "0":
         return False
     inv_freq, rotary_dim, pairing = rot

@@ -1,6 +1,6 @@
 """Rotary position encoding as a part: its constants (theta, how many dimensions rotate,
-which elements pair up) are parameters; the rotation itself runs inside the mixer's
-rope-and-store kernel.
+which elements pair up) are parameters; a mixer's kernel may apply the rotation itself
+(`rotary_constants`: fused with its cache write, or with its attention in one-token steps).
 
 angle(pos, k) = pos * theta^(-2k / rotary_dim), computed in fp32 on the device from a
 table of theta^(-2k / rotary_dim) made here in double precision.  (The reference reaches
@@ -22,6 +22,7 @@ PAIRINGS = {"half": B.PAIR_HALF, "interleaved": B.PAIR_INTERLEAVED}
 class RotaryEncoding(PositionEncoding):
     def __init__(self, spec, head_dim: int, rt: Runtime):
         self.theta = float(spec["theta"])
+        self.head_dim = head_dim
         self.rotary_dim = int(spec.get("rotary_dim", head_dim))
         pairing = spec.get("pairing", "half")
         if pairing not in PAIRINGS:
@@ -39,9 +40,9 @@ class RotaryEncoding(PositionEncoding):
     def rotary_constants(self):
         return self.inv_freq, self.rotary_dim, self.pairing
 
-    def encode_and_store(self, qkv, ctx, kv, heads: int, writes_cache: bool) -> None:
-        B.rope_kv_store(qkv, ctx.batch, kv, self.inv_freq, heads, self.rotary_dim, self.pairing,
-                        writes_cache, ctx.rt.err, ctx.stream)
+    def encode(self, qkv, ctx, heads: int, kv_heads: int) -> None:
+        B.rotate_qk(qkv, ctx.batch, self.inv_freq, heads, kv_heads, self.head_dim, self.rotary_dim, self.pairing,
+                    ctx.rt.err, ctx.stream)
 
 
 register_part("position", "rope", RotaryEncoding)

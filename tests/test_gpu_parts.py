@@ -409,15 +409,12 @@ class LearnedOffsets:
 
     def load(self, tensors):
         self.offsets = tensors["offsets"].float()
-        self.no_freq = torch.zeros(1, dtype=torch.float32, device=self.rt.device)
 
-    def encode_and_store(self, qkv, ctx, kv, heads, writes_cache):
-        from inference_engine_rust_b200.csrc import bindings as B
+    def encode(self, qkv, ctx, heads, kv_heads):
         pos = torch.cat([torch.arange(p0, p0 + q) for p0, q in zip(ctx.pos0, ctx.q_lens)]).to(qkv.device)
         rows = qkv[:ctx.n_tokens].view(ctx.n_tokens, -1, self.head_dim)
-        n = heads + kv.kv_heads                     # queries and keys; values stay as they are
+        n = heads + kv_heads                        # queries and keys; values stay as they are
         rows[:, :n] = (rows[:, :n].float() + self.offsets[pos % self.period][:, None, :]).to(qkv.dtype)
-        B.rope_kv_store(qkv, ctx.batch, kv, self.no_freq, heads, 0, B.PAIR_HALF, writes_cache, ctx.rt.err, ctx.stream)
 
 
 @dataclass(frozen=True)
@@ -557,3 +554,122 @@ def test_attention_asks_for_a_cut_by_length_when_it_pays():
     assert not FA.wants_length_cut([2047] * full, 8, 4, None, 64, 128)
     assert FA.wants_length_cut([2047] * (full + full // 3), 8, 4, None, 64, 128), "one and a third rounds"
     assert not FA.wants_length_cut([2047] * (2 * full - 2), 8, 4, None, 64, 128), "almost two full rounds"
+
+
+# ---- another block arrangement: norms after the parts too, and a layer without a feed-forward ----------
+
+
+class SandwichBlock:
+    """x += post_mixer(mixer(norm1(x))); x += post_ffn(ffn(norm2(x))): the two extra norms come by role
+    from `LayerSpec.extra_norms`.  The parts ADD into the tensor they are given, so each gets a zeroed
+    buffer, whose normed content is then added to x."""
+
+    def __init__(self, layer_spec, norm1, mixer, norm2, ffn, rt, extra_norms=None):
+        self.norm1, self.mixer, self.norm2, self.ffn, self.rt = norm1, mixer, norm2, ffn, rt
+        self.post = extra_norms or {}
+
+    def forward(self, x, ctx, cache_view, writes_cache):
+        ws, T = self.rt.workspace, ctx.n_tokens
+        for norm, post, run in ((self.norm1, "post_mixer", lambda xn, y: self.mixer.forward(xn, y, ctx, cache_view, writes_cache)),
+                                (self.norm2, "post_ffn", (lambda xn, y: self.ffn.forward(xn, y, ctx)) if self.ffn else None)):
+            if run is None:
+                continue
+            xn = ws.take("sandwich.normed", x.shape, self.rt.dtype)
+            norm.forward(x, xn, ctx, rows=T)
+            y = ws.take("sandwich.delta", x.shape, torch.float32)
+            y.zero_()
+            run(xn, y)
+            yn = ws.take("sandwich.delta_normed", x.shape, torch.float32)
+            self.post[post].forward(y, yn, ctx, rows=T)
+            x[:T] += yn[:T]
+
+
+@dataclass(frozen=True)
+class SandwichConfig:
+    hidden_size: int
+    vocab_size: int
+    architecture: str = "SandwichToyForCausalLM"
+
+    @classmethod
+    def from_dict(cls, raw):
+        return cls(raw["hidden_size"], raw["vocab_size"])
+
+
+def sandwich_spec(cfg: SandwichConfig):
+    from inference_engine_rust_b200.config.specs import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+    H = cfg.hidden_size
+    norm = PartSpec("rmsnorm", {"eps": 1e-5})
+    post = PartSpec("rmsnorm", {"eps": 1e-3})
+    attn = PartSpec("attention", {"hidden_size": H, "heads": 4, "kv_heads": 2, "head_dim": 16, "window": 24,
+                                  "scale": 0.25, "position": PartSpec("rope", {"theta": 1e4, "rotary_dim": 16, "pairing": "half"})})
+    ffn = PartSpec("swiglu", {"hidden_size": H, "intermediate_size": 72})
+    layers = []
+    for i, f in enumerate((ffn, None)):          # the second layer has no feed-forward
+        p = f"toy.{i}."
+        extra = {"post_mixer": (post, p + "post1.weight")}
+        if f is not None:
+            extra["post_ffn"] = (post, p + "post2.weight")
+        layers.append(LayerSpec(block=PartSpec("sandwich", {}), norm=norm, mixer=attn, ffn=f, mixer_prefix=p + "mix.",
+                                ffn_prefix=p + "ffn.", mixer_norm_name=p + "n1.weight", ffn_norm_name=p + "n2.weight",
+                                extra_norms=extra))
+    return ModelSpec(architecture=cfg.architecture, hidden_size=H, vocab_size=cfg.vocab_size, layers=tuple(layers),
+                     schedule=(ScheduleEntry(0), ScheduleEntry(1)), final_norm=norm, embedding_name="toy.embed.weight",
+                     final_norm_name="toy.norm.weight", lm_head_name=None, embedding_scale=1.0, max_position=256,
+                     bos_token_id=None, eos_token_id=None)
+
+
+def plain_sandwich(w, ids):
+    x = P.embed(w["toy.embed.weight"], ids, 1.0)
+    a = dict(heads=4, kv_heads=2, head_dim=16, rope_theta=1e4, window=24, scale=0.25)
+    for i in (0, 1):
+        p = f"toy.{i}."
+        y = P.attention_layer(P.rmsnorm(x, w[p + "n1.weight"], 1e-5), *(w[p + f"mix.{k}_proj.weight"] for k in "qkvo"), **a)
+        x = x + P.rmsnorm(y, w[p + "post1.weight"], 1e-3)
+        if i == 0:
+            y = P.ffn_layer(P.rmsnorm(x, w[p + "n2.weight"], 1e-5), w[p + "ffn.gate_proj.weight"],
+                            w[p + "ffn.up_proj.weight"], w[p + "ffn.down_proj.weight"])
+            x = x + P.rmsnorm(y, w[p + "post2.weight"], 1e-3)
+    return P.matmul(P.rmsnorm(x, w["toy.norm.weight"], 1e-5), w["toy.embed.weight"])
+
+
+def test_another_block_arrangement_with_more_norms_and_a_layer_without_feed_forward():
+    """A block class registered from here, norms after the mixer and the feed-forward named in the layer
+    specification, one layer that has no feed-forward: built, loaded by name and stepped (prompts,
+    then tokens one by one) without a change to the framework's files."""
+    from inference_engine_rust_b200 import LoadedModel, register_architecture
+    from inference_engine_rust_b200.config import registry
+    from inference_engine_rust_b200.parts import register_part, unregister_part
+    from inference_engine_rust_b200.weights import RandomSource
+    register_part("block", "sandwich", SandwichBlock)
+    register_architecture("SandwichToyForCausalLM", SandwichConfig, sandwich_spec)
+    try:
+        raw = {"architectures": ["SandwichToyForCausalLM"], "hidden_size": 64, "vocab_size": 101}
+        model = LoadedModel.random(raw, seed=8, dtype="float32", std=0.1)
+        names = model.model.expected_tensors()
+        assert "toy.0.post2.weight" in names and "toy.1.post1.weight" in names
+        assert "toy.1.post2.weight" not in names and "toy.1.n2.weight" not in names and "toy.1.ffn.down_proj.weight" not in names
+        src = RandomSource(names, 8, 0.1, dtype=torch.float32)
+        w = {n: src.get(n) for n in src.names()}
+        g = torch.Generator().manual_seed(1)
+        prompts = [torch.randint(0, 101, (n,), generator=g).tolist() for n in (40, 9)]
+        want = [plain_sandwich(w, p) for p in prompts]
+        eng = model.session(max_tokens=64 * 4, poison_cache=True).engine
+        assert not eng.use_graphs, "a block that does not declare graph_safe keeps graphs off"
+        slots = [eng.open_sequence() for _ in prompts]
+        tails = [6, 3]
+        out = eng.step([(s, p[:len(p) - t]) for s, p, t in zip(slots, prompts, tails)], want="all")
+        got, at = [[], []], 0
+        for i, (p, t) in enumerate(zip(prompts, tails)):
+            got[i].append(out[at:at + len(p) - t].clone())
+            at += len(p) - t
+        for k in range(max(tails)):
+            live = [i for i in range(2) if tails[i] > k]
+            out = eng.step([(slots[i], [prompts[i][len(prompts[i]) - tails[i] + k]]) for i in live], want="last")
+            for r, i in enumerate(live):
+                got[i].append(out[r:r + 1].clone())
+        eng.check_device()
+        for i in range(2):
+            compare(torch.cat(got[i]), want[i], "float32", f"sandwich toy, request {i}")
+    finally:
+        unregister_part("block", "sandwich")
+        registry._ARCHITECTURES.pop("SandwichToyForCausalLM", None)
