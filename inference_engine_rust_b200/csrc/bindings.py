@@ -115,6 +115,9 @@ def _declare(lib) -> None:
     lib.iert_gemm_rows.argtypes = [P, c_longlong, P, c_longlong, P, c_int, c_longlong, c_int, c_int, c_int, c_int,
                                    POINTER(RowScale), POINTER(NormAhead), c_int, P, S]
     lib.iert_gemm_rows.restype = c_int
+    lib.iert_gemm_tc_scaled.argtypes = [P, c_longlong, P, c_longlong, P, c_int, c_longlong, c_int, c_int, c_int, c_int,
+                                        P, c_longlong, P, c_int, POINTER(RowScale), POINTER(NormAhead), c_int, c_int, P, S]
+    lib.iert_gemm_tc_scaled.restype = c_int
     lib.iert_gemm_tc_gated_scaled.argtypes = [P, c_longlong, P, c_longlong, P, c_longlong, c_int, c_int, c_int,
                                               POINTER(RowScale), c_int, P, S]
     lib.iert_gemm_tc_gated_scaled.restype = c_int
@@ -326,6 +329,26 @@ def gemm_rows(x, w, out, M: int, mode: int, err, stream, scale: Optional[RowScal
     if status == 1:
         return False
     check(status, "gemm_rows")
+    return True
+
+
+def gemm_tc_scaled(x, w, out, M: int, mode: int, err, stream, scale: Optional[RowScale] = None,
+                   ahead: Optional[NormAhead] = None, force_bt: int = 0, force_splits: int = 0) -> bool:
+    """`gemm_tc` for one-token steps of 17 to 64 tokens with an RMSNorm split around the kernel: `scale`
+    (x is a norm's first half: outputs times the rows' 1 / rms) and / or `ahead` (a residual add that
+    also writes the next norm's first half; `ahead.parts` is set).  False, nothing launched, where
+    the launch would not go through the split-K reduction."""
+    N, K = w.shape
+    sc = GemmScratch.get(x.device)
+    status = core().iert_gemm_tc_scaled(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(),
+                                        dtype_code(out.dtype), out.stride(0), M, N, K, mode, sc.ws.data_ptr(),
+                                        sc.ws.numel(), sc.counters.data_ptr(), sc.counters.numel(),
+                                        byref(scale) if scale is not None else None,
+                                        byref(ahead) if ahead is not None else None, force_bt, force_splits,
+                                        err.data_ptr(), stream)
+    if status == 1:
+        return False
+    check(status, "gemm_tc_scaled")
     return True
 
 

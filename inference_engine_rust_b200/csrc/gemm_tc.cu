@@ -77,8 +77,11 @@ struct GemmParams {
   int tail_parts;     // > 1: the tiles from full_tiles on are cut into this many parts of k (see WorkIter)
   int full_tiles;
   int* err;
-  IertRowScale scale;   // weight-major gated tiles: scale.sumsq != null: x is the first half of an RMSNorm (see
-                        // common.cuh) and gate and up are multiplied by the rows' 1 / rms before the activation
+  IertRowScale scale;   // weight-major tiles of up to 64 tokens: scale.sumsq != null: x is the first half of an RMSNorm
+                        // (see common.cuh); the outputs (gated: gate and up, before the activation) are multiplied by
+                        // the rows' 1 / rms
+  IertNormAhead ahead;  // split-K residual add, tiles of 32 or 64 tokens: ahead.scaled_out != null: the reduction also
+                        // writes the next norm's first half
 };
 
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
@@ -137,9 +140,18 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
 // rows per split a row-at-a-time loop spent 30 us here.
 template <int BT>
 __device__ __forceinline__ void reduce_partial_rows(const GemmParams& p, const float* base, int t_first, int t_end,
-                                                    int t0, int n, int c4) {
+                                                    int t0, int n, int c4, int n_idx, const float* rstd) {
   const bool vec_res = p.mode == MODE_ADD_RESIDUAL && p.out_dtype == IERT_F32 && n + 4 <= p.N && (p.ldo & 3) == 0 &&
                        ((uintptr_t)p.out & 15) == 0;
+  const bool ahead = p.ahead.scaled_out != nullptr;      // (residual add into fp32: checked by the host)
+  float g[4] = {0.f, 0.f, 0.f, 0.f};                     // the next norm's scale for this thread's four columns
+  if (ahead) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      if (n + i < p.N)
+        g[i] = p.ahead.weight_dtype == IERT_F32 ? ((const float*)p.ahead.weight)[n + i]
+                                                : __bfloat162float(((const __nv_bfloat16*)p.ahead.weight)[n + i]);
+  }
   for (int t = t_first; t < t_end; t += 16) {
     float4 acc[4], res[4];
 #pragma unroll
@@ -167,12 +179,44 @@ __device__ __forceinline__ void reduce_partial_rows(const GemmParams& p, const f
     }
 #pragma unroll
     for (int h = 0; h < 4; ++h) {
-      if (t + 4 * h >= t_end) break;
-      if (vec_res)
-        *reinterpret_cast<float4*>((float*)p.out + (long long)(t0 + t + 4 * h) * p.ldo + n) =
+      if (t + 4 * h >= t_end) break;                     // the same for the 32 threads that share the row
+      const int row = t + 4 * h;
+      if (rstd) {                                        // the input rows' 1 / rms (see IertRowScale)
+        const float r = rstd[row];
+        acc[h].x *= r; acc[h].y *= r; acc[h].z *= r; acc[h].w *= r;
+      }
+      if (vec_res && !ahead) {
+        *reinterpret_cast<float4*>((float*)p.out + (long long)(t0 + row) * p.ldo + n) =
             make_float4(res[h].x + acc[h].x, res[h].y + acc[h].y, res[h].z + acc[h].z, res[h].w + acc[h].w);
-      else
-        write_out4(p, t0 + t + 4 * h, n, acc[h]);
+      } else if (ahead) {
+        // the new residual values, and beside them the next norm's first half (see IertNormAhead)
+        float* orow = (float*)p.out + (long long)(t0 + row) * p.ldo;
+        float nv[4] = {acc[h].x, acc[h].y, acc[h].z, acc[h].w};
+        if (vec_res) {
+          nv[0] += res[h].x; nv[1] += res[h].y; nv[2] += res[h].z; nv[3] += res[h].w;
+          *reinterpret_cast<float4*>(orow + n) = make_float4(nv[0], nv[1], nv[2], nv[3]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            if (n + i < p.N) { nv[i] += orow[n + i]; orow[n + i] = nv[i]; } else nv[i] = 0.f;
+          }
+        }
+        __nv_bfloat16* srow = (__nv_bfloat16*)p.ahead.scaled_out + (long long)(t0 + row) * p.ahead.ld;
+        if (n + 4 <= p.N && (p.ahead.ld & 3) == 0 && ((uintptr_t)p.ahead.scaled_out & 7) == 0) {
+          uint2 w2;
+          *reinterpret_cast<__nv_bfloat162*>(&w2.x) = __floats2bfloat162_rn(nv[0] * g[0], nv[1] * g[1]);
+          *reinterpret_cast<__nv_bfloat162*>(&w2.y) = __floats2bfloat162_rn(nv[2] * g[2], nv[3] * g[3]);
+          *reinterpret_cast<uint2*>(srow + n) = w2;
+        } else {
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            if (n + i < p.N) srow[n + i] = __float2bfloat16_rn(nv[i] * g[i]);
+        }
+        const float ss = warp_sum(nv[0] * nv[0] + nv[1] * nv[1] + nv[2] * nv[2] + nv[3] * nv[3]);
+        if (c4 == 0) p.ahead.sumsq_out[(size_t)(t0 + row) * p.ahead.parts + n_idx] = ss;
+      } else {
+        write_out4(p, t0 + row, n, acc[h]);
+      }
     }
   }
 }
@@ -369,8 +413,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   } else {
     // ---------------- epilogue: 4 warps, warp w reads TMEM lanes 32*(w%4).. ----------------
     pdl_wait();
-    float* rstd_s = reinterpret_cast<float*>(xch_s + 16 * 64 * 4);     // [64] (weight-major gated tiles only)
-    const bool scaled = !GATED && BT <= 64 && p.mode == MODE_GATED_SILU && p.scale.sumsq != nullptr;
+    // [64] row scales: behind the gated tile's exchange buffer, or in its place for a plain launch
+    float* rstd_s = reinterpret_cast<float*>(p.mode == MODE_GATED_SILU ? xch_s + 16 * 64 * 4 : xch_s);
+    const bool scaled = !GATED && BT <= 64 && p.scale.sumsq != nullptr;
     if (scaled) {                          // the rows' 1 / rms, while the weights stream
       row_scales_from_parts(p.scale, p.M < BT ? p.M : BT, rstd_s, (int)threadIdx.x - 64, 128);
       asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -626,7 +671,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             const int rows_per = (t_valid + p.splits - 1) / p.splits;
             const int r0 = split * rows_per, r1 = min(t_valid, r0 + rows_per);
             if constexpr (BT > 16) {
-              reduce_partial_rows<BT>(p, base, r0 + tr, r1, t0, n0 + c4 * 4, c4);
+              reduce_partial_rows<BT>(p, base, r0 + tr, r1, t0, n0 + c4 * 4, c4, n_idx, scaled ? rstd_s : nullptr);
             } else
             for (int t = r0 + tr; t < r1; t += 4) {        // a token row per 32 threads, 8 splits in flight
               float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -651,7 +696,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           asm volatile("bar.sync 1, 128;" ::: "memory");
           if (*ticket_s == p.splits - 1) {             // the last split of this tile: add in split order
             __threadfence();
-            reduce_partial_rows<BT>(p, base, tr, t_valid, t0, n0 + c4 * 4, c4);
+            reduce_partial_rows<BT>(p, base, tr, t_valid, t0, n0 + c4 * 4, c4, n_idx, scaled ? rstd_s : nullptr);
             if (threadIdx.x == 64) p.counters[tile] = 0;
           }
         }
@@ -809,15 +854,17 @@ int sm_count() {
 // Dynamic shared memory of a launch: ring, alignment slack, barriers; the weight-major gated tile
 // adds its exchange buffer, the residual add by TMA its two staging buffers.  The one formula for
 // the launch and for the estimate of how many CTAs an SM holds (ctas_per_sm_of).
-constexpr size_t dynamic_smem_bytes(int stages, int stage_bytes, bool gated_weight_major, bool tma_out) {
-  return (size_t)stages * stage_bytes + 1024 + 256 + (gated_weight_major ? XCH_BYTES : 0) + (tma_out ? 2 * OUT_STAGE_BYTES + 128 : 0);
+constexpr size_t dynamic_smem_bytes(int stages, int stage_bytes, bool gated_weight_major, bool tma_out, bool row_scales = false) {
+  return (size_t)stages * stage_bytes + 1024 + 256 + (gated_weight_major ? XCH_BYTES : row_scales ? 256 + 16 : 0) +
+         (tma_out ? 2 * OUT_STAGE_BYTES + 128 : 0);
 }
 
 template <int BT, bool GATED>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, GemmParams p, int grid, cudaStream_t stream,
            const CUtensorMap* mo = nullptr) {
   constexpr int STAGE_BYTES = (GATED ? 2 : 1) * W_STAGE_BYTES + BT * TILE_K * 2;
-  const size_t smem = dynamic_smem_bytes(p.stages, STAGE_BYTES, !GATED && p.mode == MODE_GATED_SILU, p.tma_out != 0);
+  const size_t smem = dynamic_smem_bytes(p.stages, STAGE_BYTES, !GATED && p.mode == MODE_GATED_SILU, p.tma_out != 0,
+                                         p.scale.sumsq != nullptr);
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(gemm_tc_kernel<BT, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess)
@@ -839,7 +886,7 @@ int ctas_per_sm_of(int stages) {
   if (stages < 0 || stages > 12) return 0;
   if (!cached[stages]) {
     // (a plain weight-major launch: no exchange buffer, no TMA-out staging; only such launches reduce cooperatively)
-    const size_t smem = dynamic_smem_bytes(stages, W_STAGE_BYTES + BT * TILE_K * 2, false, false);
+    const size_t smem = dynamic_smem_bytes(stages, W_STAGE_BYTES + BT * TILE_K * 2, false, false, true);   // (the larger of the two plain layouts)
     int n = 0, dev = 0, smem_sm = 0, regs_sm = 0;
     cudaFuncAttributes a;
     if (cudaGetDevice(&dev) == cudaSuccess && cudaFuncGetAttributes(&a, gemm_tc_kernel<BT, false>) == cudaSuccess &&
@@ -882,11 +929,16 @@ IERT_API int iert_gemm_tc_counter_count() { return 8192; }
 // and the pointers 16-byte aligned (TMA); otherwise IERT_BAD_ARGUMENT is returned and nothing
 // is launched.  ws / counters: scratch for split-K, shared by all launches on one stream;
 // counters must be zero before the first launch.  force_*: 0 = choose.
-IERT_API int iert_gemm_tc(const void* x, long long ldx, const void* w, long long ldw, void* out, int out_dtype,
-                          long long ldo, int M, int N, int K, int mode, float* ws, long long ws_bytes,
-                          int* counters, int n_counters, int force_bt, int force_splits, int force_stages,
-                          int* err, cudaStream_t stream) {
+namespace {
+int gemm_tc_impl(const void* x, long long ldx, const void* w, long long ldw, void* out, int out_dtype,
+                 long long ldo, int M, int N, int K, int mode, float* ws, long long ws_bytes,
+                 int* counters, int n_counters, int force_bt, int force_splits, int force_stages,
+                 const IertRowScale* scale, IertNormAhead* ahead, int* err, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return IERT_OK;
+  if (scale && (!scale->sumsq || scale->parts <= 0 || scale->hidden <= 0 || M > 64)) return IERT_BAD_ARGUMENT;
+  if (ahead && (mode != MODE_ADD_RESIDUAL || M > 64 || !ahead->weight || !ahead->scaled_out || !ahead->sumsq_out ||
+                (ahead->weight_dtype != IERT_F32 && ahead->weight_dtype != IERT_BF16)))
+    return IERT_BAD_ARGUMENT;
   if (K <= 0 || (K & 7) || (ldx & 7) || (ldw & 7) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15))
     return IERT_BAD_ARGUMENT;
   if (mode != MODE_STORE && mode != MODE_ADD_RESIDUAL) return IERT_BAD_ARGUMENT;
@@ -906,11 +958,13 @@ IERT_API int iert_gemm_tc(const void* x, long long ldx, const void* w, long long
 
   GemmParams p;
   p.scale = IertRowScale{nullptr, 0, 0, 0.f};
+  p.ahead = IertNormAhead{nullptr, 0, nullptr, 0, nullptr, 0};
+  if (scale) p.scale = *scale;
   p.tail_parts = 1; p.full_tiles = 0; p.tma_out = 0; p.t_group = 1 << 30;
   p.out = out; p.ldo = ldo; p.out_dtype = out_dtype; p.mode = mode;
   p.M = M; p.N = N; p.K = K;
   p.ws = ws; p.counters = counters; p.err = err;
-  if (!force_bt && !force_splits && ((M > 256 && mode == MODE_STORE) || (M >= 128 && force_stages == -1))) {
+  if (!scale && !ahead && !force_bt && !force_splits && ((M > 256 && mode == MODE_STORE) || (M >= 128 && force_stages == -1))) {
     // many tokens, plain store: 128 tokens on the MMA's M side, 256 weight rows on its N side
     // (whole tiles).  Measured on 2,048 tokens: better than weight rows on M for stores (vector
     // stores of a token's row), not for the residual add, which stays on the other kernel.
@@ -972,6 +1026,12 @@ IERT_API int iert_gemm_tc(const void* x, long long ldx, const void* w, long long
     }
   }
   p.splits = splits;
+  // row scales and the next norm's first half are the split-K reduction's work, on tiles of 32 or 64 tokens
+  if ((scale || ahead) && (splits < 2 || bt < 32 || bt > 64)) return IERT_BAD_ARGUMENT;
+  if (ahead) {
+    ahead->parts = (N + TILE_N - 1) / TILE_N;
+    p.ahead = *ahead;
+  }
   const int total_work = tiles * splits;
   if (!force_stages && ctas_per_sm == 2 && total_work <= sm_count()) {
     // every CTA has an SM to itself: let its ring use the whole shared memory
@@ -1026,6 +1086,30 @@ IERT_API int iert_gemm_tc(const void* x, long long ldx, const void* w, long long
     case 128: return launch<128, false>(mw, mx, p, grid, stream, p.tma_out ? &mo : nullptr);
     default: return launch<256, false>(mw, mx, p, grid, stream, p.tma_out ? &mo : nullptr);
   }
+}
+}  // namespace
+
+IERT_API int iert_gemm_tc(const void* x, long long ldx, const void* w, long long ldw, void* out, int out_dtype,
+                          long long ldo, int M, int N, int K, int mode, float* ws, long long ws_bytes,
+                          int* counters, int n_counters, int force_bt, int force_splits, int force_stages,
+                          int* err, cudaStream_t stream) {
+  return gemm_tc_impl(x, ldx, w, ldw, out, out_dtype, ldo, M, N, K, mode, ws, ws_bytes, counters, n_counters, force_bt,
+                      force_splits, force_stages, nullptr, nullptr, err, stream);
+}
+
+// The same for one-token steps of 17 to 64 tokens whose input or output takes part in an RMSNorm split around
+// the kernel boundary (see common.cuh):
+//   scale (optional)  x is a norm's first half: the outputs are multiplied by each row's 1 / rms;
+//   ahead (optional; mode 1)  the reduction also writes the next norm's first half; ahead->parts is set to
+//                     the number of partial sums per row (one per tile of 128 columns).
+// Both are the split-K reduction's work: IERT_BAD_ARGUMENT, nothing launched, where a launch would not split k
+// or its token tile is not 32 or 64.
+IERT_API int iert_gemm_tc_scaled(const void* x, long long ldx, const void* w, long long ldw, void* out, int out_dtype,
+                                 long long ldo, int M, int N, int K, int mode, float* ws, long long ws_bytes,
+                                 int* counters, int n_counters, const IertRowScale* scale, IertNormAhead* ahead,
+                                 int force_bt, int force_splits, int* err, cudaStream_t stream) {
+  return gemm_tc_impl(x, ldx, w, ldw, out, out_dtype, ldo, M, N, K, mode, ws, ws_bytes, counters, n_counters, force_bt,
+                      force_splits, 0, scale, ahead, err, stream);
 }
 
 // act[t, i] = silu(x[t] . w[i]) * (x[t] . w[inter + i]) for w = [gate; up] of 2 * inter rows,

@@ -30,6 +30,11 @@ def norm_ahead_enabled() -> bool:
     return os.environ.get("IERT_NORM_AHEAD", "1") != "0"
 
 
+# One-token steps of up to this many tokens may split a norm around a kernel boundary (the weight-major
+# tiles of the tcgen05 kernel end there).
+NORM_AHEAD_MAX_TOKENS = 64
+
+
 def apply(linear, x, out, n_rows: int, mode: int, stream: int, ctx=None) -> bool:
     """Run the tensor-core product if it takes these operands (bf16, K and row strides
     multiples of 8, 16-byte aligned); False means nothing was launched and the caller runs the
@@ -40,15 +45,22 @@ def apply(linear, x, out, n_rows: int, mode: int, stream: int, ctx=None) -> bool
         return False
     err = linear.rt.err
     scaled = x if isinstance(x, ScaledRows) else None
-    if n_rows <= ROWS_KERNEL_MAX_TOKENS and 2 * -(-linear.out_features // 128) <= 2 * B.sm_count():
+    request = ctx.norm_ahead if ctx is not None and mode == B.GEMM_ADD_RESIDUAL else None
+    thin = 2 * -(-linear.out_features // 128) <= 2 * B.sm_count()       # 128-row tiles alone would not fill the device
+    if n_rows <= NORM_AHEAD_MAX_TOKENS and thin and (scaled is not None or request is not None or n_rows <= ROWS_KERNEL_MAX_TOKENS):
         xt = scaled.scaled if scaled is not None else as_tensor(x, n_rows)
         if xt.dtype == torch.bfloat16:
-            request = ctx.norm_ahead if ctx is not None and mode == B.GEMM_ADD_RESIDUAL else None
             ahead = finish = None
             if request is not None:
-                ahead, finish = honour(request, out, ctx, "linear", -(-linear.out_features // 16))
-            if B.gemm_rows(xt, linear.weight, out, n_rows, mode, err, stream,
-                           scale=scaled.row_scale() if scaled is not None else None, ahead=ahead):
+                parts = -(-linear.out_features // (16 if n_rows <= ROWS_KERNEL_MAX_TOKENS else 128))
+                ahead, finish = honour(request, out, ctx, "linear", parts)
+            scale = scaled.row_scale() if scaled is not None else None
+            if n_rows <= ROWS_KERNEL_MAX_TOKENS:
+                done = B.gemm_rows(xt, linear.weight, out, n_rows, mode, err, stream, scale=scale, ahead=ahead)
+            else:
+                done = (scale is not None or ahead is not None) and \
+                    B.gemm_tc_scaled(xt, linear.weight, out, n_rows, mode, err, stream, scale=scale, ahead=ahead)
+            if done:
                 if finish is not None:
                     ctx.rows_ahead = finish()
                 return True

@@ -203,3 +203,67 @@ def test_gated_product_is_silu_gate_times_up(M, I, K):
         diff = (act.double() - ref).abs()
         bound = 1e-3 + (2.0 ** -8) * ref.abs() + 1e-3 * (gate.abs() + 1) * up.abs()
         assert torch.isfinite(act).all() and bool((diff <= bound).all()), f"{force}: max diff {diff.max().item():.4g}"
+
+
+# ---- one-token steps of 17 to 64 tokens: an RMSNorm split around the kernel boundary ---------------
+
+
+@pytest.mark.parametrize("M,N,K", [(17, 4096, 4096), (32, 4096, 14336), (64, 4096, 4096), (40, 520, 2048)])
+@pytest.mark.parametrize("wdt", [torch.bfloat16, torch.float32])
+def test_split_k_residual_add_writes_the_next_norms_first_half(M, N, K, wdt):
+    """Beside the new residual rows the split-K reduction writes bf16(row x scale vector) and one sum of
+    squares per row and tile of 128 columns; repeatable to the bit; refused where nothing is split."""
+    from inference_engine_rust_b200.csrc import bindings as B
+    g = torch.Generator(device=DEV).manual_seed(M + N + K)
+    x = torch.randn(M, K, device=DEV, generator=g).bfloat16()
+    w = (torch.randn(N, K, device=DEV, generator=g) * 0.5).bfloat16()
+    nw = (1.0 + 0.1 * torch.randn(N, device=DEV, generator=g)).to(wdt)
+    res0 = torch.randn(M, N, device=DEV, generator=g)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    tiles = -(-N // 128)
+    outs = []
+    for _ in range(2):
+        out = res0.clone()
+        scaled = torch.full((M, N), float("nan"), device=DEV, dtype=torch.bfloat16)
+        sumsq = torch.full((M, tiles), float("nan"), device=DEV)
+        ahead = B.norm_ahead(nw, scaled, sumsq)
+        assert B.gemm_tc_scaled(x, w, out, M, B.GEMM_ADD_RESIDUAL, err, B.stream_ptr(), ahead=ahead)
+        torch.cuda.synchronize()
+        assert err.item() == 0 and ahead.parts == tiles
+        ref = x.double() @ w.double().t() + res0.double()
+        assert bool(((out.double() - ref).abs() <= 2e-3 * (K ** 0.5) * 0.5).all())
+        assert torch.equal(scaled, (out * nw.float()).bfloat16())
+        pad = torch.zeros(M, tiles * 128, device=DEV, dtype=torch.float64)
+        pad[:, :N] = out.double()
+        assert torch.allclose(sumsq.double(), (pad.view(M, tiles, 128) ** 2).sum(-1), rtol=1e-5, atol=1e-6)
+        outs.append((out, scaled, sumsq))
+    assert all(torch.equal(a, b) for a, b in zip(*outs))
+    ahead = B.norm_ahead(nw, scaled, sumsq)
+    assert not B.gemm_tc_scaled(x, w, res0.clone(), M, B.GEMM_ADD_RESIDUAL, err, B.stream_ptr(), ahead=ahead, force_splits=1)
+
+
+@pytest.mark.parametrize("M,N,K,parts", [(17, 6144, 4096, 32), (64, 6144, 4096, 32), (33, 520, 2048, 1), (64, 4096, 4096, 7)])
+def test_split_k_store_applies_the_norms_second_half(M, N, K, parts):
+    from inference_engine_rust_b200.csrc import bindings as B
+    g = torch.Generator(device=DEV).manual_seed(M * 3 + N + K + parts)
+    rows = torch.randn(M, K, device=DEV, generator=g) * 3.0
+    nw = 1.0 + 0.1 * torch.randn(K, device=DEV, generator=g)
+    w = (torch.randn(N, K, device=DEV, generator=g) * 0.5).bfloat16()
+    eps = 1e-5
+    scaled = (rows * nw).bfloat16()
+    per = -(-K // parts)
+    pad = torch.zeros(M, per * parts, device=DEV, dtype=torch.float64)
+    pad[:, :K] = rows.double()
+    sumsq = (pad.view(M, parts, per) ** 2).sum(-1).float().contiguous()
+    rstd = 1.0 / torch.sqrt((rows.double() ** 2).mean(-1, keepdim=True) + eps)
+    ref = (scaled.double() * rstd) @ w.double().t()
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    scale = B.RowScale(sumsq=sumsq.data_ptr(), parts=parts, hidden=K, eps=eps)
+    for odt in (torch.bfloat16, torch.float32):
+        out = torch.full((M, N), float("nan"), device=DEV, dtype=odt)
+        assert B.gemm_tc_scaled(scaled, w, out, M, B.GEMM_STORE, err, B.stream_ptr(), scale=scale)
+        torch.cuda.synchronize()
+        assert err.item() == 0
+        bound = 2e-3 * (K ** 0.5) * 0.5 + 1e-5 * ref.abs() + (2.0 ** -8) * ref.abs() * (odt == torch.bfloat16)
+        diff = (out.double() - ref).abs()
+        assert torch.isfinite(out).all() and bool((diff <= bound).all()), f"{odt}: max diff {diff.max().item():.4g}"
