@@ -234,7 +234,29 @@ class Engine:
         """Run one step.  `entries` = [(slot, tokens)]; `want` = "last", "all", "none"/None, or
         for each sequence the places among its tokens whose logits are wanted.  Returns
         float32 [wanted, vocab] on the device, in the order of the entries and of `want`."""
-        return self._run(self.plan(entries, want), None)
+        plan = self._plan_one_token(entries, want)
+        return self._run(plan if plan is not None else self.plan(entries, want), None)
+
+    def _plan_one_token(self, entries, want: Want):
+        """`plan` for the step that is run thousands of times in a row: every sequence brings one token
+        and the logits of all (or none) are wanted.  The same checks, without the general
+        bookkeeping; None where the general plan has to decide (or to raise)."""
+        if not entries or not (want == "last" or want == "all" or want is None or want == "none"):
+            return None
+        held, lens, vocab, limit = self.cache.slots._held, self.cache.seq_lens, self.model.spec.vocab_size, self.cache.max_seq_len
+        slots, pos0, toks = [], [], []
+        for slot, t in entries:
+            if len(t) != 1 or slot not in held:
+                return None
+            tok, p = t[0], int(lens[slot])
+            if not 0 <= tok < vocab or p + 1 > limit:
+                return None
+            slots.append(int(slot)); pos0.append(p); toks.append(tok)
+        n = len(slots)
+        if len(set(slots)) != n:
+            return None
+        rows = list(range(n)) if want in ("last", "all") else []
+        return "decode", slots, [1] * n, pos0, toks, range(n + 1), rows
 
     def step_tokens_on_device(self, slots: Sequence[int], tokens: torch.Tensor,
                               rows: Optional[Sequence[int]] = None, want: Want = "last") -> Optional[torch.Tensor]:
@@ -248,7 +270,8 @@ class Engine:
         if (tokens.dim() != 1 or tokens.dtype != torch.int32 or tokens.device.type != self.rt.device.type
                 or len(rows) != n or any(not 0 <= r < tokens.shape[0] for r in rows)):
             raise StepError("device tokens must be int32 [rows] on the model's device, one row per sequence")
-        plan = self.plan([(s, (0,)) for s in slots], want)
+        entries = [(s, (0,)) for s in slots]
+        plan = self._plan_one_token(entries, want) or self.plan(entries, want)
         if plan[0] != "decode":
             raise StepError("tokens on the device can only continue running sequences by one token")
         return self._run(plan, (tokens, rows))
@@ -346,17 +369,10 @@ class Engine:
             g = self._graphs[(nb, unequal)] = _DecodeGraph(self, nb, unequal)
         o_cu, o_slot, o_pos, o_seq, o_tok, o_rows, total = self._layout(nb, nb, nb)
         host, turn = self._staging.next(total)
-        h = host.numpy()
-        h[o_cu:o_cu + nb + 1] = np.arange(nb + 1)
-        h[o_slot:o_slot + nb] = -1
-        h[o_slot:o_slot + n] = slots
-        h[o_pos:o_pos + nb] = 0
-        h[o_pos:o_pos + n] = pos0
-        h[o_seq:o_seq + nb] = -1
-        h[o_seq:o_seq + n] = np.arange(n)
-        h[o_tok:o_tok + nb] = 0
-        h[o_tok:o_tok + n] = tokens
-        h[o_rows:o_rows + nb] = np.arange(nb)
+        pad = nb - n
+        # cu_q | slot_ids | pos0 | tok_seq | tokens | logit_rows, padding sequences with slot and sequence -1
+        host.numpy()[:total] = (list(range(nb + 1)) + list(slots) + [-1] * pad + list(pos0) + [0] * pad
+                                + list(range(n)) + [-1] * pad + [int(t) for t in tokens] + [0] * pad + list(range(nb)))
         g.meta[:total].copy_(host[:total], non_blocking=True)
         self._staging.sent(turn)
         if device_tokens is not None:
