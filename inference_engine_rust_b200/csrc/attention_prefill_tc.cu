@@ -65,6 +65,30 @@ __device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, volatil
   }
   return false;
 }
+// Packed fp32 pairs (one instruction for two values) and the three-input maximum of sm_100.
+__device__ __forceinline__ uint64_t pack2(float a, float b) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& a, float& b) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -80,17 +104,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   uint8_t* q_s = smem;                                       // NSUB blocks of 128 rows
   uint8_t* k_s = q_s + NSUB * SUB_BYTES;                     // 2 stages x NSUB blocks of 64 rows
   uint8_t* v_s = k_s + 2 * NSUB * KV_SUB_BYTES;              // 2 stages x NSUB blocks of 64 rows
-  uint8_t* p_s = v_s + 2 * NSUB * KV_SUB_BYTES;              // one block: 128 rows x 64 keys
-  uint64_t* bars = (uint64_t*)(p_s + SUB_BYTES);
+  uint64_t* bars = (uint64_t*)(v_s + 2 * NSUB * KV_SUB_BYTES);
   uint64_t* q_full = bars;          // 1
   uint64_t* k_full = bars + 1;      // 2
   uint64_t* v_full = bars + 3;      // 2
   uint64_t* k_empty = bars + 5;     // 2: a key buffer is free once its score MMAs have finished
   uint64_t* v_empty = bars + 7;     // 2: a value buffer is free once its output MMAs have finished
-  uint64_t* s_full = bars + 9;      // 2
-  uint64_t* s_free = bars + 11;     // 2
-  uint64_t* p_ready = bars + 13;    // 1
-  uint64_t* pv_done = bars + 14;    // 1
+  uint64_t* s_full = bars + 9;      // 2: the scores of a tile are in their buffer
+  uint64_t* p_ready = bars + 11;    // 2: the probabilities of a tile are in their buffer (every softmax thread arrives)
+  uint64_t* pv_done = bars + 13;    // 2: the output MMAs of a tile have finished
   uint32_t* tmem_slot = (uint32_t*)(bars + 15);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
@@ -116,10 +138,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     mbar_init(q_full, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&k_full[i], 1); mbar_init(&v_full[i], 1); mbar_init(&k_empty[i], 1); mbar_init(&v_empty[i], 1);
-      mbar_init(&s_full[i], 1); mbar_init(&s_free[i], 128);
+      mbar_init(&s_full[i], 1); mbar_init(&p_ready[i], 128); mbar_init(&pv_done[i], 1);
     }
-    mbar_init(p_ready, 128);
-    mbar_init(pv_done, 1);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&map_q);
@@ -169,10 +189,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     if (lane == 0) {
       constexpr uint32_t IDESC_S = instr_desc_bf16(BM, BN);
       constexpr uint32_t IDESC_O = instr_desc_bf16_b_mn(BM, HD);
+      // The MMAs of this thread run in the order they are issued, so a score buffer needs no barrier of
+      // its own: the scores of tile it + 2 are issued after the output MMAs of tile it, which read the
+      // probabilities that the softmax wrote over the scores of tile it.
       auto scores = [&](int it) -> bool {                    // S[it & 1] = Q K_it^T
         const int st = it & 1;
         if (!wait_bar(&k_full[st], (it >> 1) & 1, abort_flag)) return false;
-        if (!wait_bar(&s_free[st], ((it >> 1) & 1) ^ 1, abort_flag)) return false;
         tc_fence_after();
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
@@ -186,21 +208,21 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       };
       if (!wait_bar(q_full, 0, abort_flag)) ok = false;
       if (ok) ok = scores(0);
+      if (ok && n_tiles > 1) ok = scores(1);
       for (int it = 0; ok && it < n_tiles; ++it) {
         const int st = it & 1;
-        if (it + 1 < n_tiles && !scores(it + 1)) { ok = false; break; }
-        if (!wait_bar(p_ready, it & 1, abort_flag)) { ok = false; break; }
+        if (!wait_bar(&p_ready[st], (it >> 1) & 1, abort_flag)) { ok = false; break; }
         if (!wait_bar(&v_full[st], (it >> 1) & 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll
-        for (int kk = 0; kk < BN / 16; ++kk) {               // 16 keys per instruction
-          const uint32_t pa = smem_addr(p_s) + kk * 32;
+        for (int kk = 0; kk < BN / 16; ++kk) {               // 16 keys per instruction: 8 columns of P
           const uint32_t vb = smem_addr(v_s + st * NSUB * KV_SUB_BYTES) + kk * 16 * 128;
-          umma_bf16(tmem_base + O_COL, smem_desc_k128(pa), smem_desc_mn128(vb, KV_SUB_BYTES), IDESC_O,
-                    (it > 0 || kk > 0) ? 1u : 0u);
+          umma_bf16_a_tmem(tmem_base + O_COL, tmem_base + st * BN + kk * 8, smem_desc_mn128(vb, KV_SUB_BYTES), IDESC_O,
+                           (it > 0 || kk > 0) ? 1u : 0u);
         }
-        umma_commit(pv_done);
+        umma_commit(&pv_done[st]);
         umma_commit(&v_empty[st]);
+        if (it + 2 < n_tiles && !scores(it + 2)) { ok = false; break; }
       }
     }
   } else {
@@ -222,34 +244,41 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
         for (int c = 0; c < BN; ++c) sc[c] = __uint_as_float(raw[c]);
       }
-      tc_fence_before();
-      mbar_arrive(&s_free[st]);
       // Scores stay raw; the scale (> 0) is folded into the exponent: p = 2^(s * scale - m).
       // A tile that every row sees entirely (the common case) takes the path without masks.
       const bool need_mask = (j0 + BN - 1 > i0) || (p.window > 0 && j0 < i0 + BM - 1 - (p.window - 1)) || (j0 + BN > len);
-      float mx = -INFINITY;
-      if (!need_mask) {
-#pragma unroll
-        for (int c = 0; c < BN; ++c) mx = fmaxf(mx, sc[c]);
-      } else {
+      if (need_mask) {
 #pragma unroll
         for (int c = 0; c < BN; ++c) {
           const int j = j0 + c;
           const bool vis = j <= i && j < len && (p.window <= 0 || j >= i - (p.window - 1));
           if (!vis) sc[c] = -INFINITY;
-          mx = fmaxf(mx, sc[c]);
         }
+      }
+      float mx;
+      {                                                      // four chains of three-input maxima
+        float m4[4];
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const float* s16 = sc + 16 * g;
+          float m = max3(s16[0], s16[1], s16[2]);
+#pragma unroll
+          for (int c = 3; c < 15; c += 2) m = max3(m, s16[c], s16[c + 1]);
+          m4[g] = fmaxf(m, s16[15]);
+        }
+        mx = fmaxf(max3(m4[0], m4[1], m4[2]), m4[3]);
       }
       mx *= p.scale_log2e;                                   // -inf stays -inf
       const bool grow = mx > m_used + 8.0f || (m_used == -INFINITY && mx != -INFINITY);
       const bool warp_grow = __any_sync(0xffffffffu, grow);
-      if (it > 0 && !wait_bar(pv_done, (it - 1) & 1, abort_flag)) { ok = false; break; }
       if (warp_grow) {
+        // the output so far refers to the old maximum: rescale it once the MMAs that add to it are done
+        if (it > 0 && !wait_bar(&pv_done[(it - 1) & 1], ((it - 1) >> 1) & 1, abort_flag)) { ok = false; break; }
         const float m_new = grow ? fmaxf(m_used, mx) : m_used;
         const float alpha = !grow ? 1.f : (m_used == -INFINITY ? 0.f : ex2(m_used - m_new));
         m_used = m_new;
         l *= alpha;
-        if (it > 0) {                                        // the output so far refers to the old maximum
+        if (it > 0) {
           tc_fence_after();
 #pragma unroll
           for (int c = 0; c < HD; c += 16) {
@@ -262,28 +291,33 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           tc_fence_before();
         }
       }
-      // P as bf16 into the swizzled tile: 16-byte chunk q of row r lives at chunk (q ^ (r & 7))
+      // P as bf16 over the first half of this tile's scores in tensor memory (each thread has read its whole
+      // row of scores before it writes): two keys per 32-bit column, the lower key in the lower half.
+      // Two scores per instruction (packed fp32 FMA and add).  A masked score is -inf and stays -inf through
+      // the FMA (the scale is positive, -m finite), and 2^-inf is 0: masked keys need no select here.
       const float neg_m = m_used == -INFINITY ? 0.f : -m_used;   // a row without a visible key: all p are 0
-      float l0 = 0.f, l1 = 0.f;
+      const uint64_t scale2 = pack2(p.scale_log2e, p.scale_log2e), neg_m2 = pack2(neg_m, neg_m);
+      uint64_t l2a = pack2(0.f, 0.f), l2b = l2a;
+      uint32_t pk[BN / 2];
 #pragma unroll
-      for (int q8 = 0; q8 < BN / 8; ++q8) {
-        uint4 pk;
-        __nv_bfloat162* pp = reinterpret_cast<__nv_bfloat162*>(&pk);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float a = sc[q8 * 8 + 2 * e], bb = sc[q8 * 8 + 2 * e + 1];
-          float pa = ex2(fmaf(a, p.scale_log2e, neg_m)), pb = ex2(fmaf(bb, p.scale_log2e, neg_m));
-          if (need_mask) { if (a == -INFINITY) pa = 0.f; if (bb == -INFINITY) pb = 0.f; }
-          l0 += pa; l1 += pb;
-          pp[e] = __floats2bfloat162_rn(pa, pb);
-        }
-        *reinterpret_cast<uint4*>(p_s + r * 128 + ((q8 ^ (r & 7)) << 4)) = pk;
+      for (int c = 0; c < BN / 2; ++c) {
+        float ea, eb;
+        unpack2(fma2(pack2(sc[2 * c], sc[2 * c + 1]), scale2, neg_m2), ea, eb);
+        const float pa = ex2(ea), pb = ex2(eb);
+        if (c & 1) l2b = add2(l2b, pack2(pa, pb)); else l2a = add2(l2a, pack2(pa, pb));
+        const __nv_bfloat162 two = __floats2bfloat162_rn(pa, pb);
+        pk[c] = *reinterpret_cast<const uint32_t*>(&two);
       }
+#pragma unroll
+      for (int c = 0; c < BN / 2; c += 16) tmem_st16_issue(tmem_base + lane_bits + st * BN + c, pk + c);
+      tmem_st_wait();
+      float l0, l1;
+      unpack2(add2(l2a, l2b), l0, l1);
       l += l0 + l1;
-      fence_proxy_async_smem();
-      mbar_arrive(p_ready);
+      tc_fence_before();
+      mbar_arrive(&p_ready[st]);
     }
-    if (ok && !wait_bar(pv_done, (n_tiles - 1) & 1, abort_flag)) ok = false;
+    if (ok && !wait_bar(&pv_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, abort_flag)) ok = false;
     if (ok) {
       tc_fence_after();
       const float inv = l > 0.f ? 1.0f / l : 0.f;
@@ -338,7 +372,7 @@ IERT_API int iert_attention_prefill_tc(const void* qkv, void* out, const IertBat
   p.heads = heads; p.kv_heads = kv_heads; p.window = window;
   p.scale_log2e = scale * 1.4426950408889634f;
   p.err = err;
-  const size_t smem = (size_t)NSUB * SUB_BYTES + 4 * (size_t)NSUB * KV_SUB_BYTES + SUB_BYTES + 128;
+  const size_t smem = (size_t)NSUB * SUB_BYTES + 4 * (size_t)NSUB * KV_SUB_BYTES + 256;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
