@@ -77,6 +77,7 @@ class ModelSpec:
     max_position: int
     bos_token_id: Optional[int]
     eos_token_id: Optional[int]
+    head: PartSpec = PartSpec("linear")   # what turns the final norm's rows into logits
 
     def validate(self) -> None:
         n = len(self.layers)

@@ -18,7 +18,7 @@ import torch
 
 from ..cache import PAGE_TOKENS, Cache, CacheError, CacheFull
 from ..csrc import bindings as B
-from ..parts.base import StepContext
+from ..parts.base import HostCopyUnavailable, StepContext
 from .model import Model
 
 
@@ -81,7 +81,9 @@ class _DecodeGraph:
         rt.workspace = self.ws
         try:
             def run():
-                ctx = engine._context("decode", self.meta, nb, nb, [1] * nb, [0] * nb, [-1] * nb)
+                # the launches are replayed for other sequences: their host lists must not be read
+                ctx = engine._context("decode", self.meta, nb, nb, [1] * nb, HostCopyUnavailable("pos0"),
+                                      HostCopyUnavailable("slots"))
                 ctx.unequal_lengths = unequal
                 model.forward(ctx, self.meta[o_tok:o_tok + nb], engine.cache,
                               self.meta[o_rows:o_rows + nb], nb, logits_out=self.logits)
@@ -117,7 +119,9 @@ class _PromptGraph:
         try:
             def run():
                 # launches are sized for the longest prompt the bucket can hold
-                ctx = engine._context("prompt", self.meta, nb, tb, [tb] + [0] * (nb - 1), [0] * nb, [-1] * nb)
+                # (prompts all start at position 0; which slots they are is not known here)
+                ctx = engine._context("prompt", self.meta, nb, tb, [tb] + [0] * (nb - 1), [0] * nb,
+                                      HostCopyUnavailable("slots"))
                 model.forward(ctx, self.meta[o_tok:o_tok + tb], engine.cache,
                               self.meta[o_rows:o_rows + nb], nb, logits_out=self.logits)
             run()                                      # eager once: lazy set-up happens outside the capture

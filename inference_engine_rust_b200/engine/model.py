@@ -15,7 +15,6 @@ from ..cache import CacheRequest
 from ..config.specs import ModelSpec
 from ..csrc import bindings as B
 from ..parts.base import Runtime, StepContext, first_norm_request_of, part_class
-from ..parts.linear import Linear
 from ..weights.loader import (RandomSource, TensorSpec, WeightError, check_source, fetch_many)
 
 
@@ -43,7 +42,7 @@ class Model:
             self.blocks.append(block)
         self.final_norm = part_class("norm", spec.final_norm.kind)(spec.final_norm, h, rt)
         self.embedding: Optional[torch.Tensor] = None
-        self.lm_head: Optional[Linear] = None
+        self.lm_head = part_class("head", spec.head.kind)(spec.head, h, spec.vocab_size, rt)
         self.loaded = False
         self.ignored_tensors: List[str] = []
         self.notes: List[str] = []       # what loading decided on its own (tied head, ignored tensors)
@@ -57,7 +56,7 @@ class Model:
             spec.final_norm_name: self.final_norm.tensor_specs()["weight"],
         }
         if spec.lm_head_name is not None:
-            out[spec.lm_head_name] = TensorSpec((spec.vocab_size, spec.hidden_size))
+            out[spec.lm_head_name] = self.lm_head.tensor_specs()["weight"]
         for ls, (norm1, mixer, norm2, ffn), extra in zip(spec.layers, self._layer_parts, self._extra_norms):
             out[ls.mixer_norm_name] = norm1.tensor_specs()["weight"]
             for local, ts in mixer.tensor_specs().items():
@@ -102,10 +101,11 @@ class Model:
 
         self.embedding = get(spec.embedding_name)
         self.final_norm.load({"weight": get(spec.final_norm_name)})
-        head = self.embedding if head_name is None else get(head_name)
-        self.lm_head = Linear(head, rt)
-        if head_name is None and self.lm_head.weight.dtype == self.embedding.dtype:
-            self.embedding = self.lm_head.weight          # tied: one copy
+        self.lm_head.load({"weight": self.embedding if head_name is None else get(head_name)})
+        tied = getattr(self.lm_head, "weight", None)
+        if head_name is None and tied is not None and tied.dtype == self.embedding.dtype \
+                and tied.shape == self.embedding.shape:
+            self.embedding = tied                          # tied: one copy
         for ls, (norm1, mixer, norm2, ffn), extra in zip(spec.layers, self._layer_parts, self._extra_norms):
             norm1.load({"weight": get(ls.mixer_norm_name)})
             mixer.load({local: get(ls.mixer_prefix + local) for local in mixer.tensor_specs()})
@@ -135,7 +135,7 @@ class Model:
     def graph_safe(self) -> bool:
         """True when every part declares `graph_safe`: its forward reads the step's sequences
         from device memory only, so a captured launch sequence stays right for later steps."""
-        parts = [self.final_norm]
+        parts = [self.final_norm, self.lm_head]
         for e in self.spec.schedule:
             parts.extend(p for p in self._layer_parts[e.layer] if p is not None)
             parts.extend(self._extra_norms[e.layer].values())
@@ -205,5 +205,5 @@ class Model:
         self.final_norm.forward(x, hn, ctx, rows_idx=logit_rows, rows=n_logit_rows)
         if logits_out is None:
             logits_out = torch.empty((n_logit_rows, spec.vocab_size), dtype=torch.float32, device=rt.device)
-        self.lm_head.apply(hn, logits_out, n_logit_rows, ctx.stream)
+        self.lm_head.forward(hn, logits_out, n_logit_rows, ctx)
         return logits_out

@@ -10,6 +10,7 @@ kind; the configuration then names that kind for the layers that use it.
     mixer     Mixer(spec, rt)                    .forward(xn, residual, ctx, cache_view, writes_cache)
     ffn       FeedForward(spec, rt)              .forward(xn, residual, ctx)
     block     Block(layer_spec, norm1, mixer, norm2, ffn, rt[, extra_norms={role: norm}])   .forward(x, ctx, cache_view, writes_cache)
+    head      Head(spec, hidden_size, vocab_size, rt)   .forward(hn, logits_f32, n_rows, ctx)
 
 Optional, for one-token steps (see `NormRequest`, `LazyInput`): a norm may let the kernel that writes
 its input rows do its element-wise half and the projection that reads its output its row-wise half.
@@ -29,7 +30,7 @@ from ..config.specs import LayerSpec, PartSpec
 from ..weights.loader import TensorSpec
 
 _REGISTRY: Dict[Tuple[str, str], type] = {}
-CATEGORIES = ("norm", "position", "mixer", "ffn", "block")
+CATEGORIES = ("norm", "position", "mixer", "ffn", "block", "head")
 
 
 def register_part(category: str, kind: str, cls: type, *, replace: bool = False) -> None:
@@ -133,7 +134,9 @@ class StepContext:
                   "decode": every sequence brings exactly one token
     batch         csrc.bindings.BatchView (device arrays cu_q, slot_ids, tok_seq, pos0)
     n_tokens      packed tokens, padding included;  n_seqs likewise
-    q_lens, pos0, slots   host copies (lists) for sizing launches and for host-side checks
+    q_lens, pos0, slots   host copies (lists) for sizing launches and for host-side checks; in a step that
+                  is being captured into a CUDA graph, `slots` (and, for one-token steps, `pos0`) are
+                  `HostCopyUnavailable`: reading them raises
     unequal_lengths       one-token steps: a mixer asked for its work to be cut by the sequences'
                           lengths rather than evenly (`Mixer.cut_by_length`)
     """
@@ -162,6 +165,28 @@ class StepContext:
     @property
     def max_kv_len(self) -> int:
         return max((p + q for p, q in zip(self.pos0, self.q_lens)), default=0)
+
+
+class HostCopyUnavailable:
+    """Stands in for `StepContext.slots` or `StepContext.pos0` while a step is being captured into a
+    CUDA graph.  The captured launches are replayed later for other sequences, so what a part reads
+    from the host lists at capture time would be frozen into them: any read raises instead.  A part
+    that declares `graph_safe` takes the sequences from device memory (`ctx.batch`,
+    `ctx.slot_ids_dev`, `ctx.pos0_dev`)."""
+
+    def __init__(self, what: str):
+        self.what = what
+
+    def _refuse(self, *args, **kwargs):
+        raise RuntimeError(
+            f"StepContext.{self.what} was read while the step was being captured into a CUDA graph; "
+            f"a part that declares graph_safe must read the step's sequences from device memory "
+            f"(ctx.batch, ctx.slot_ids_dev, ctx.pos0_dev), or declare graph_safe = False")
+
+    __getitem__ = __iter__ = __len__ = __bool__ = __contains__ = _refuse
+
+    def __repr__(self):
+        return f"<{self.what}: unavailable in a captured step>"
 
 
 def first_norm_request_of(block, ctx) -> Optional["NormRequest"]:
@@ -239,3 +264,17 @@ class Block(Part):
         """What this block's first norm asks of whoever writes the rows the block will receive (the
         block before it, or the embedding); None (the default): nothing."""
         return None
+
+
+class Head(Part):
+    """Logits from the rows that the final norm produced.  Its one tensor, "weight"
+    [vocab, hidden], is the output matrix; the model hands it the embedding table instead when the
+    output is tied.  `forward` writes float32 logits for `n_rows` rows."""
+
+    def forward(self, hn, logits, n_rows: int, ctx: StepContext) -> None:
+        raise NotImplementedError
+
+    def nbytes(self) -> int:
+        """Bytes of weights a step reads through this head."""
+        raise NotImplementedError
+

@@ -673,3 +673,120 @@ def test_another_block_arrangement_with_more_norms_and_a_layer_without_feed_forw
     finally:
         unregister_part("block", "sandwich")
         registry._ARCHITECTURES.pop("SandwichToyForCausalLM", None)
+
+
+# ---------------------------------------------------------------------------------------
+# another output head, defined here: logits with a soft cap
+
+
+def _expected_tensors(raw):
+    """Names and shapes of a configuration's tensors, from a model built on the device without weights."""
+    from inference_engine_rust_b200.config import config_from_dict, spec_of
+    from inference_engine_rust_b200.engine.model import Model
+    from inference_engine_rust_b200.parts import Runtime
+    return Model(spec_of(config_from_dict(raw)), Runtime(torch.float32, "cuda:0")).expected_tensors()
+
+
+def _soft_cap_head():
+    from inference_engine_rust_b200.parts.head import LinearHead
+
+    class SoftCapHead(LinearHead):
+        """logits = cap * tanh((hn . W^T) / cap): the linear head, then an element-wise cap (device ops of
+        fixed shape, so a captured step stays right)."""
+        graph_safe = True
+
+        def __init__(self, spec, hidden_size, vocab_size, rt):
+            super().__init__(spec, hidden_size, vocab_size, rt)
+            self.cap = float(spec["cap"])
+
+        def forward(self, hn, logits, n_rows, ctx):
+            super().forward(hn, logits, n_rows, ctx)
+            rows = logits[:n_rows]
+            rows.copy_(torch.tanh(rows / self.cap) * self.cap)
+
+    return SoftCapHead
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_another_output_head_is_registered_and_used(dtype):
+    """A head kind registered from here and named by the model specification: the engine's logits are the
+    plain implementation's with the cap applied, for prompts and for tokens one by one (through captured
+    graphs where the run uses them)."""
+    import dataclasses
+    from helpers import TINY_B
+    from inference_engine_rust_b200 import LoadedModel, register_architecture
+    from inference_engine_rust_b200.config import registry
+    from inference_engine_rust_b200.config.mistral import MistralConfig, build_spec
+    from inference_engine_rust_b200.config.specs import PartSpec
+    from inference_engine_rust_b200.parts import register_part, unregister_part
+    from inference_engine_rust_b200.weights import RandomSource
+    from helpers import WEIGHT_STD
+
+    @dataclass(frozen=True)
+    class CappedConfig(MistralConfig):                # the same keys; another name, so another specification
+        architecture: str = "CappedToyForCausalLM"
+
+    # the plain logits first (the tensor names and shapes are the configuration's own), so that the cap
+    # can be put where it binds for some logits and leaves the others nearly alone
+    base = dict(TINY_B, architectures=["MistralForCausalLM"])
+    src = RandomSource(_expected_tensors(base), 12, WEIGHT_STD, dtype=torch.float32)
+    w = {n: src.get(n) for n in src.names()}
+    if dtype == "bfloat16":
+        w = {n: t.to(torch.bfloat16).float() for n, t in w.items()}
+    g = torch.Generator().manual_seed(2)
+    ids = torch.randint(0, base["vocab_size"], (29,), generator=g).tolist()
+    plain = P.forward(base, w, ids, P.bf16_rounding if dtype == "bfloat16" else P.no_rounding)
+    cap = 0.6 * float(plain.abs().max())
+    want = torch.tanh(plain / cap) * cap
+    assert ((plain - want).abs() > 0.1 * cap).any(), "the cap never binds: the test would not see a head that ignores it"
+
+    register_part("head", "softcap", _soft_cap_head())
+    register_architecture("CappedToyForCausalLM", CappedConfig,
+                          lambda cfg: dataclasses.replace(build_spec(cfg), head=PartSpec("softcap", {"cap": cap})))
+    try:
+        raw = dict(TINY_B, architectures=["CappedToyForCausalLM"])
+        model = LoadedModel.random(raw, seed=12, dtype=dtype, std=WEIGHT_STD)
+        eng = model.session(max_tokens=64 * 2, poison_cache=True).engine
+        assert eng.use_graphs
+        s = eng.open_sequence()
+        got = [eng.step([(s, ids[:20])], want="all").clone()]
+        for t in ids[20:]:
+            got.append(eng.step([(s, [t])], want="last").clone())
+        eng.check_device()
+        compare(torch.cat(got), want, dtype, "capped head")
+    finally:
+        unregister_part("head", "softcap")
+        registry._ARCHITECTURES.pop("CappedToyForCausalLM", None)
+
+
+def test_a_part_that_reads_host_lists_in_a_captured_step_is_refused(toy_registered, monkeypatch):
+    """A mixer that declares graph_safe but takes the step's sequences from the host lists would have the
+    sequences of the capture frozen into its launches: the capture raises instead of going wrong later."""
+    from inference_engine_rust_b200 import LoadedModel
+    from inference_engine_rust_b200.parts import register_part
+
+    class Overconfident(RunningMeanMixer):
+        graph_safe = True
+
+    register_part("mixer", "running_mean", Overconfident, replace=True)
+    try:
+        raw = {"architectures": ["ToyForCausalLM"], "hidden_size": 64, "vocab_size": 97, "schedule": [[1, None]]}
+        model = LoadedModel.random(raw, seed=4, dtype="float32", std=0.1)
+        eng = model.session(max_tokens=64 * 2).engine
+        assert eng.use_graphs
+        from inference_engine_rust_b200.engine import engine as engine_module
+        prompt = [3, 5, 7, 11, 13, 17, 19, 23]
+        s = eng.open_sequence()
+        eng.step([(s, prompt)], want="last")           # a shape's first prompt is launched one by one
+        eng.close_sequence(s)
+        s = eng.open_sequence()
+        with pytest.raises(RuntimeError, match="graph_safe"):         # its second one is captured
+            eng.step([(s, prompt)], want="last")
+        eng.close_sequence(s)
+        monkeypatch.setattr(engine_module, "PROMPT_GRAPH_MAX_TOKENS", 4)
+        s = eng.open_sequence()
+        eng.step([(s, prompt)], want="last")           # too long for a captured prompt now: host lists are real
+        with pytest.raises(RuntimeError, match="graph_safe"):
+            eng.step([(s, [2])], want="last")
+    finally:
+        register_part("mixer", "running_mean", RunningMeanMixer, replace=True)
