@@ -78,6 +78,9 @@ class ModelSpec:
     bos_token_id: Optional[int]
     eos_token_id: Optional[int]
     head: PartSpec = PartSpec("linear")   # what turns the final norm's rows into logits
+    # Parts that run once per step, after the embedding and before the first block: (spec, tensor-name prefix).
+    # Each may change the embedded rows and publish tensors for the blocks (a per-layer input, say).
+    inputs: Sequence[Tuple[PartSpec, str]] = ()
 
     def validate(self) -> None:
         n = len(self.layers)

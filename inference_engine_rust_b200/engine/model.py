@@ -43,6 +43,7 @@ class Model:
         self.final_norm = part_class("norm", spec.final_norm.kind)(spec.final_norm, h, rt)
         self.embedding: Optional[torch.Tensor] = None
         self.lm_head = part_class("head", spec.head.kind)(spec.head, h, spec.vocab_size, rt)
+        self.inputs = [(part_class("input", ps.kind)(ps, h, spec.vocab_size, rt), prefix) for ps, prefix in spec.inputs]
         self.loaded = False
         self.ignored_tensors: List[str] = []
         self.notes: List[str] = []       # what loading decided on its own (tied head, ignored tensors)
@@ -57,6 +58,9 @@ class Model:
         }
         if spec.lm_head_name is not None:
             out[spec.lm_head_name] = self.lm_head.tensor_specs()["weight"]
+        for part, prefix in self.inputs:
+            for local, ts in part.tensor_specs().items():
+                out[prefix + local] = ts
         for ls, (norm1, mixer, norm2, ffn), extra in zip(spec.layers, self._layer_parts, self._extra_norms):
             out[ls.mixer_norm_name] = norm1.tensor_specs()["weight"]
             for local, ts in mixer.tensor_specs().items():
@@ -106,6 +110,8 @@ class Model:
         if head_name is None and tied is not None and tied.dtype == self.embedding.dtype \
                 and tied.shape == self.embedding.shape:
             self.embedding = tied                          # tied: one copy
+        for part, prefix in self.inputs:
+            part.load({local: get(prefix + local) for local in part.tensor_specs()})
         for ls, (norm1, mixer, norm2, ffn), extra in zip(spec.layers, self._layer_parts, self._extra_norms):
             norm1.load({"weight": get(ls.mixer_norm_name)})
             mixer.load({local: get(ls.mixer_prefix + local) for local in mixer.tensor_specs()})
@@ -135,7 +141,7 @@ class Model:
     def graph_safe(self) -> bool:
         """True when every part declares `graph_safe`: its forward reads the step's sequences
         from device memory only, so a captured launch sequence stays right for later steps."""
-        parts = [self.final_norm, self.lm_head]
+        parts = [self.final_norm, self.lm_head] + [part for part, _ in self.inputs]
         for e in self.spec.schedule:
             parts.extend(p for p in self._layer_parts[e.layer] if p is not None)
             parts.extend(self._extra_norms[e.layer].values())
@@ -145,7 +151,7 @@ class Model:
     def weight_bytes_per_step(self) -> int:
         """Bytes of weights a one-token step reads: every matrix each scheduled layer uses,
         the norm scales, the output head (the embedding rows it gathers are negligible)."""
-        total = self.lm_head.nbytes()
+        total = self.lm_head.nbytes() + sum(part.weight_bytes() for part, _ in self.inputs if hasattr(part, "weight_bytes"))
         for e in self.spec.schedule:
             norm1, mixer, norm2, ffn = self._layer_parts[e.layer]
             for part in (mixer, ffn):
@@ -187,13 +193,16 @@ class Model:
         x = ws.take("model.residual", (T, H), torch.float32)
         sched = spec.schedule
         # the first block's first norm may ask the embedding kernel for its element-wise half
-        request = first_norm_request_of(self.blocks[sched[0].layer], ctx) if sched else None
+        # (not when step inputs may still change the embedded rows)
+        request = first_norm_request_of(self.blocks[sched[0].layer], ctx) if sched and not self.inputs else None
         ahead = finish = None
         if request is not None:
             from ..parts.norm import honour
             ahead, finish = honour(request, x, ctx, "embed", 1)
         B.embed_gather(self.embedding, tokens, x, spec.embedding_scale, rt.err, ctx.stream, ahead=ahead)
         ctx.rows_ahead = finish() if finish is not None else None
+        for part, _ in self.inputs:
+            part.prepare(tokens, x, ctx)
         for pos, e in enumerate(sched):
             view = cache.layer_view(spec.cache_entry(pos))
             ctx.next_block = self.blocks[sched[pos + 1].layer] if pos + 1 < len(sched) else None

@@ -11,6 +11,7 @@ kind; the configuration then names that kind for the layers that use it.
     ffn       FeedForward(spec, rt)              .forward(xn, residual, ctx)
     block     Block(layer_spec, norm1, mixer, norm2, ffn, rt[, extra_norms={role: norm}])   .forward(x, ctx, cache_view, writes_cache)
     head      Head(spec, hidden_size, vocab_size, rt)   .forward(hn, logits_f32, n_rows, ctx)
+    input     StepInput(spec, hidden_size, vocab_size, rt)   .prepare(tokens, x_f32, ctx)
 
 Optional, for one-token steps (see `NormRequest`, `LazyInput`): a norm may let the kernel that writes
 its input rows do its element-wise half and the projection that reads its output its row-wise half.
@@ -30,7 +31,7 @@ from ..config.specs import LayerSpec, PartSpec
 from ..weights.loader import TensorSpec
 
 _REGISTRY: Dict[Tuple[str, str], type] = {}
-CATEGORIES = ("norm", "position", "mixer", "ffn", "block", "head")
+CATEGORIES = ("norm", "position", "mixer", "ffn", "block", "head", "input")
 
 
 def register_part(category: str, kind: str, cls: type, *, replace: bool = False) -> None:
@@ -154,6 +155,7 @@ class StepContext:
                                                    # applied next to the residual rows it writes
     rows_ahead: Optional[LazyInput] = None         # set by whoever honoured `norm_ahead`: that norm's lazy result
     next_block: object = None                      # the block that runs after the current one (None: the last)
+    shared: dict = field(default_factory=dict)     # what the model's step inputs published for the blocks, by name
     slot_ids_dev: Optional[torch.Tensor] = None   # int32 [n_seqs] view, for parts written in Python
     pos0_dev: Optional[torch.Tensor] = None
     cu_q_dev: Optional[torch.Tensor] = None
@@ -276,5 +278,16 @@ class Head(Part):
 
     def nbytes(self) -> int:
         """Bytes of weights a step reads through this head."""
+        raise NotImplementedError
+
+
+class StepInput(Part):
+    """Runs once per step, after the embedding and before the first block, on the step's token ids
+    (int32 on the device, padding included) and the embedded rows `x` (fp32 [tokens, hidden]).  It may
+    change `x` in place (a norm or a bias on the embedding) and may publish tensors for the blocks in
+    `ctx.shared[name]` (an input that every layer reads, computed from the ids once).  Its tensors are
+    found under the prefix that `ModelSpec.inputs` names beside its spec."""
+
+    def prepare(self, tokens, x, ctx: StepContext) -> None:
         raise NotImplementedError
 

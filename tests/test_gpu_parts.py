@@ -790,3 +790,150 @@ def test_a_part_that_reads_host_lists_in_a_captured_step_is_refused(toy_register
             eng.step([(s, [2])], want="last")
     finally:
         register_part("mixer", "running_mean", RunningMeanMixer, replace=True)
+
+
+# ---------------------------------------------------------------------------------------
+# step inputs, defined here: a bias on the embedded rows, and a per-layer input looked up from the
+# token ids once per step and read by a later layer's mixer
+
+
+class EmbedBias:
+    """x += bias: changes the embedded rows."""
+
+    def __init__(self, spec, hidden, vocab, rt):
+        self.hidden, self.bias = hidden, None
+
+    def tensor_specs(self):
+        from inference_engine_rust_b200.weights import TensorSpec
+        return {"bias": TensorSpec((self.hidden,))}
+
+    def load(self, tensors):
+        self.bias = tensors["bias"].float()
+
+    def prepare(self, tokens, x, ctx):
+        x[:ctx.n_tokens] += self.bias
+
+
+class PerLayerTable:
+    """Publishes table[token] ([tokens, width]) as ctx.shared["per_layer"]."""
+
+    def __init__(self, spec, hidden, vocab, rt):
+        self.vocab, self.width, self.table = vocab, int(spec["width"]), None
+
+    def tensor_specs(self):
+        from inference_engine_rust_b200.weights import TensorSpec
+        return {"table": TensorSpec((self.vocab, self.width))}
+
+    def load(self, tensors):
+        self.table = tensors["table"].float()
+
+    def prepare(self, tokens, x, ctx):
+        ctx.shared["per_layer"] = self.table[tokens[:ctx.n_tokens].long().clamp(min=0)]
+
+
+class PerLayerMixer:
+    """residual += W . (this layer's columns of the per-layer input); it ignores the normed rows."""
+
+    def __init__(self, part_spec, rt):
+        self.rt, self.hidden = rt, int(part_spec["hidden_size"])
+        self.lo, self.hi = part_spec["columns"]
+        self.w = None
+
+    def tensor_specs(self):
+        from inference_engine_rust_b200.weights import TensorSpec
+        return {"w": TensorSpec((self.hidden, self.hi - self.lo))}
+
+    def load(self, tensors):
+        self.w = tensors["w"].float()
+
+    def cache_request(self):
+        return None
+
+    def forward(self, xn, residual, ctx, cache_view, writes_cache):
+        residual[:ctx.n_tokens] += ctx.shared["per_layer"][:, self.lo:self.hi] @ self.w.t()
+
+
+@dataclass(frozen=True)
+class InputsToyConfig:
+    hidden_size: int
+    vocab_size: int
+    architecture: str = "InputsToyForCausalLM"
+
+    @classmethod
+    def from_dict(cls, raw):
+        return cls(raw["hidden_size"], raw["vocab_size"])
+
+
+def inputs_toy_spec(cfg):
+    from inference_engine_rust_b200.config.specs import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+    H = cfg.hidden_size
+    norm = PartSpec("rmsnorm", {"eps": 1e-5})
+    attn = PartSpec("attention", {"hidden_size": H, "heads": 4, "kv_heads": 4, "head_dim": 16, "window": None,
+                                  "scale": 0.25, "position": PartSpec("rope", {"theta": 1e4, "rotary_dim": 16, "pairing": "half"})})
+    ffn = PartSpec("swiglu", {"hidden_size": H, "intermediate_size": 80})
+    mixers = (attn, PartSpec("per_layer", {"hidden_size": H, "columns": (4, 12)}))
+    layers = tuple(LayerSpec(block=PartSpec("prenorm", {}), norm=norm, mixer=m, ffn=ffn, mixer_prefix=f"toy.{i}.mix.",
+                             ffn_prefix=f"toy.{i}.ffn.", mixer_norm_name=f"toy.{i}.n1.weight", ffn_norm_name=f"toy.{i}.n2.weight")
+                   for i, m in enumerate(mixers))
+    return ModelSpec(architecture=cfg.architecture, hidden_size=H, vocab_size=cfg.vocab_size, layers=layers,
+                     schedule=(ScheduleEntry(0), ScheduleEntry(1)), final_norm=norm, embedding_name="toy.embed.weight",
+                     final_norm_name="toy.norm.weight", lm_head_name=None, embedding_scale=1.0, max_position=256,
+                     bos_token_id=None, eos_token_id=None,
+                     inputs=((PartSpec("embed_bias", {}), "toy.in0."), (PartSpec("per_layer_table", {"width": 12}), "toy.in1.")))
+
+
+def plain_inputs_toy(w, ids):
+    x = P.embed(w["toy.embed.weight"], ids, 1.0) + w["toy.in0.bias"]
+    per_layer = w["toy.in1.table"][torch.tensor(ids)]
+    a = dict(heads=4, kv_heads=4, head_dim=16, rope_theta=1e4, window=None, scale=0.25)
+    x = x + P.attention_layer(P.rmsnorm(x, w["toy.0.n1.weight"], 1e-5), *(w[f"toy.0.mix.{k}_proj.weight"] for k in "qkvo"), **a)
+    x = x + P.ffn_layer(P.rmsnorm(x, w["toy.0.n2.weight"], 1e-5), *(w[f"toy.0.ffn.{k}_proj.weight"] for k in ("gate", "up", "down")))
+    x = x + per_layer[:, 4:12] @ w["toy.1.mix.w"].t()
+    x = x + P.ffn_layer(P.rmsnorm(x, w["toy.1.n2.weight"], 1e-5), *(w[f"toy.1.ffn.{k}_proj.weight"] for k in ("gate", "up", "down")))
+    return P.matmul(P.rmsnorm(x, w["toy.norm.weight"], 1e-5), w["toy.embed.weight"])
+
+
+def test_step_inputs_change_the_embedded_rows_and_feed_a_later_layer():
+    """Two step inputs registered from here and named by the model specification: one changes the embedded
+    rows, one publishes a per-layer input that the second layer's mixer (also defined here, without a
+    cache) reads.  Prompts in a batch, then tokens one by one, against the plain statement."""
+    from inference_engine_rust_b200 import LoadedModel, register_architecture
+    from inference_engine_rust_b200.config import registry
+    from inference_engine_rust_b200.parts import register_part, unregister_part
+    from inference_engine_rust_b200.weights import RandomSource
+    register_part("input", "embed_bias", EmbedBias)
+    register_part("input", "per_layer_table", PerLayerTable)
+    register_part("mixer", "per_layer", PerLayerMixer)
+    register_architecture("InputsToyForCausalLM", InputsToyConfig, inputs_toy_spec)
+    try:
+        raw = {"architectures": ["InputsToyForCausalLM"], "hidden_size": 64, "vocab_size": 89}
+        model = LoadedModel.random(raw, seed=21, dtype="float32", std=0.1)
+        names = model.model.expected_tensors()
+        assert {"toy.in0.bias", "toy.in1.table", "toy.1.mix.w"} <= set(names)
+        src = RandomSource(names, 21, 0.1, dtype=torch.float32)
+        w = {n: src.get(n) for n in src.names()}
+        g = torch.Generator().manual_seed(5)
+        prompts = [torch.randint(0, 89, (n,), generator=g).tolist() for n in (33, 12)]
+        want = [plain_inputs_toy(w, p) for p in prompts]
+        eng = model.session(max_tokens=64 * 2, poison_cache=True).engine
+        assert len(eng.cache.kv_groups) == 1 and sum(len(g.layers) for g in eng.cache.kv_groups) == 1
+        slots = [eng.open_sequence() for _ in prompts]
+        tails = [5, 2]
+        out = eng.step([(s, p[:len(p) - t]) for s, p, t in zip(slots, prompts, tails)], want="all")
+        got, at = [[], []], 0
+        for i, (p, t) in enumerate(zip(prompts, tails)):
+            got[i].append(out[at:at + len(p) - t].clone())
+            at += len(p) - t
+        for k in range(max(tails)):
+            live = [i for i in range(2) if tails[i] > k]
+            out = eng.step([(slots[i], [prompts[i][len(prompts[i]) - tails[i] + k]]) for i in live], want="last")
+            for r, i in enumerate(live):
+                got[i].append(out[r:r + 1].clone())
+        eng.check_device()
+        for i in range(2):
+            compare(torch.cat(got[i]), want[i], "float32", f"step inputs toy, request {i}")
+    finally:
+        unregister_part("input", "embed_bias")
+        unregister_part("input", "per_layer_table")
+        unregister_part("mixer", "per_layer")
+        registry._ARCHITECTURES.pop("InputsToyForCausalLM", None)
