@@ -41,6 +41,7 @@
 #include "sm100.cuh"
 
 #include <cstdlib>
+#include <cstring>
 #include <mutex>
 #include <unordered_map>
 
@@ -82,7 +83,25 @@ struct GemmParams {
                         // the rows' 1 / rms
   IertNormAhead ahead;  // split-K residual add, tiles of 32 or 64 tokens: ahead.scaled_out != null: the reduction also
                         // writes the next norm's first half
+  int trace_seq;        // >= 0: the launch's row in the trace (builds with IERT_GEMM_TRACE only)
 };
+
+// Built with -DIERT_GEMM_TRACE (IERT_EXTRA_DEFINES=IERT_GEMM_TRACE), the last 64 launches record when their
+// CTAs pass eight points, on the device-wide nanosecond timer; read with iert_gemm_tc_trace_read.  A measuring
+// aid: without the definition nothing of it is compiled.
+#ifdef IERT_GEMM_TRACE
+constexpr int TRACE_LAUNCHES = 64, TRACE_CTAS = 304, TRACE_EVENTS = 8;
+__device__ unsigned long long g_tc_trace[TRACE_LAUNCHES][TRACE_CTAS][TRACE_EVENTS];
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+#define IERT_TRACE(ev)                                                                                       \
+  do { if (p.trace_seq >= 0 && blockIdx.x < TRACE_CTAS) g_tc_trace[p.trace_seq][blockIdx.x][ev] = global_ns(); } while (0)
+#else
+#define IERT_TRACE(ev) do {} while (0)
+#endif
 
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
   for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
@@ -317,6 +336,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   if (threadIdx.x == 0) pdl_launch_dependents();
+  if (threadIdx.x == 0) IERT_TRACE(0);                       // start
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -337,6 +357,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!dep_ready && issued == stages) {
             pdl_wait();
+            IERT_TRACE(2);                                     // the kernel in front has finished
             for (int i = 0; i < issued; ++i)
               tma_load_2d(smem + (size_t)i * STAGE_BYTES + X_OFF, &map_x, &full[i], pend_kb[i] * TILE_K, pend_t0[i]);
             dep_ready = true;
@@ -351,12 +372,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             tma_load_2d(ws_ + W_STAGE_BYTES / 2, &map_w, &full[stage], kb * TILE_K, n0 + p.second_rows);
           if (dep_ready) tma_load_2d(ws_ + X_OFF, &map_x, &full[stage], kb * TILE_K, t0);
           else { pend_kb[issued] = kb; pend_t0[issued] = t0; }
+          if (issued == 0) IERT_TRACE(1);                    // first weights asked for
           ++issued;
           if (++stage == stages) { stage = 0; phase ^= 1; }
         }
       }
       if (!dep_ready) {
         pdl_wait();
+        IERT_TRACE(2);
         for (int i = 0; i < issued; ++i)
           tma_load_2d(smem + (size_t)i * STAGE_BYTES + X_OFF, &map_x, &full[i], pend_kb[i] * TILE_K, pend_t0[i]);
       }
@@ -387,6 +410,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * ACC_STRIDE);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!wait_or_abort(&full[stage], phase, abort_flag)) { ok = false; break; }
+          if (kb == kb0) IERT_TRACE(3);                        // first operands of the (last) work item have arrived
           tc_fence_after();
           const uint32_t w_addr = smem_addr(smem + (size_t)stage * STAGE_BYTES);
           const uint64_t da = smem_desc_k128(w_addr), db = smem_desc_k128(w_addr + X_OFF);
@@ -402,6 +426,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         }
         if (!ok) break;
         umma_commit(&acc_full[acc]);
+        IERT_TRACE(4);                                         // last MMA of the work item issued
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1;
       }
@@ -434,6 +459,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       const int n = n0 + n_local;
       const int t_valid = min(BT, p.M - t0);
       if (!wait_or_abort(&acc_full[acc], acc_phase, abort_flag)) { ok = false; break; }
+      if (threadIdx.x == 64) IERT_TRACE(5);                    // the accumulator is complete
       tc_fence_after();
       const bool chained = p.tail_parts > 1 && n_parts > 1;   // a part of a cut tile: adds in its turn
       if (chained && split > 0) {
@@ -651,6 +677,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       if (part) {
         __threadfence();
         asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (threadIdx.x == 64) IERT_TRACE(6);                  // the partial tile is in memory
         const int et = (int)threadIdx.x - 64, c4 = et & 31, tr = et >> 5;
         const float* base = p.ws + ((size_t)tile * p.splits * BT) * TILE_N;
         if (p.coop_reduce) {
@@ -708,6 +735,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     }
   }
 
+  if (threadIdx.x == 64) IERT_TRACE(7);                        // the epilogue warps are done
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -859,9 +887,20 @@ constexpr size_t dynamic_smem_bytes(int stages, int stage_bytes, bool gated_weig
          (tma_out ? 2 * OUT_STAGE_BYTES + 128 : 0);
 }
 
+#ifdef IERT_GEMM_TRACE
+int g_trace_meta[TRACE_LAUNCHES][8];
+int g_trace_next = 0;
+#endif
+
 template <int BT, bool GATED>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, GemmParams p, int grid, cudaStream_t stream,
            const CUtensorMap* mo = nullptr) {
+  p.trace_seq = -1;
+#ifdef IERT_GEMM_TRACE
+  p.trace_seq = g_trace_next % TRACE_LAUNCHES;
+  int* tm = g_trace_meta[p.trace_seq];
+  tm[0] = g_trace_next++; tm[1] = p.M; tm[2] = p.N; tm[3] = p.K; tm[4] = grid; tm[5] = BT; tm[6] = p.splits; tm[7] = p.mode;
+#endif
   constexpr int STAGE_BYTES = (GATED ? 2 : 1) * W_STAGE_BYTES + BT * TILE_K * 2;
   const size_t smem = dynamic_smem_bytes(p.stages, STAGE_BYTES, !GATED && p.mode == MODE_GATED_SILU, p.tma_out != 0,
                                          p.scale.sumsq != nullptr);
@@ -1088,6 +1127,16 @@ int gemm_tc_impl(const void* x, long long ldx, const void* w, long long ldw, voi
   }
 }
 }  // namespace
+
+#ifdef IERT_GEMM_TRACE
+// stamps: [64][304][8] unsigned 64-bit; meta: [64][8] int (sequence number, M, N, K, grid, token tile, splits, mode)
+IERT_API int iert_gemm_tc_trace_read(unsigned long long* stamps, int* meta) {
+  if (cudaMemcpyFromSymbol(stamps, g_tc_trace, sizeof(unsigned long long) * TRACE_LAUNCHES * TRACE_CTAS * TRACE_EVENTS) != cudaSuccess)
+    return IERT_CUDA_ERROR;
+  memcpy(meta, g_trace_meta, sizeof(g_trace_meta));
+  return IERT_OK;
+}
+#endif
 
 IERT_API int iert_gemm_tc(const void* x, long long ldx, const void* w, long long ldw, void* out, int out_dtype,
                           long long ldo, int M, int N, int K, int mode, float* ws, long long ws_bytes,
