@@ -211,11 +211,17 @@ class Rig:
         qd = cfg["num_attention_heads"] * cfg["head_dim"]
         return 2 * T * L * (H * qkv + qd * H + 3 * H * I) + 2 * H * V + L * 2 * T * T * qd
 
-    def prefill(self, runs=5, warm=3):
+    def prefill(self, runs=5, warm=3, idle_s=0.0):
+        """Device times of whole-prompt steps, one after another; with `idle_s` the device rests that long
+        before each timed step (a step that starts below the power cap, as a prompt between one-token
+        steps does, against steps back to back, which settle at the cap)."""
         torch, eng = self.torch, self.eng
         prompt = self.rng.integers(0, self.vocab, self.prefill_tokens).tolist()
         times = []
         for i in range(warm + runs):
+            if idle_s and i >= warm:
+                torch.cuda.synchronize()
+                time.sleep(idle_s)
             s = eng.open_sequence()
             start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             start.record()
@@ -406,6 +412,12 @@ def main() -> int:
                    "runs": len(times), "ms_min": round(min(times), 3), "ms_max": round(max(times), 3)}
         if "bf16_tflops_sustained" in pk:      # the step is tens of milliseconds of dense tensor work
             prefill["frac_of_sustained"] = round(flops / (pms * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12), 4)
+        # The steps above run back to back and settle at the power cap, as the sustained peak does.  The burst
+        # peak is a kernel that starts below the cap; its counterpart is a step after a second of rest.
+        rested = rig.prefill(runs=3, warm=0, idle_s=1.0)
+        rms = statistics.median(rested)
+        prefill["after_1s_idle"] = {"ms": round(rms, 3), "ms_min": round(min(rested), 3), "ms_max": round(max(rested), 3),
+                                    "frac": round(flops / (rms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4), "runs": len(rested)}
     kernels = rig.kernel_table(a.batch, pk) if a.kernels else None
     load_s, layers, full_layers, max_context = rig.load_s, rig.layers, rig.full_layers, rig.max_context
     rig.close()
