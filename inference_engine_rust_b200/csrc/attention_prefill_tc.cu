@@ -151,6 +151,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   bool ok = true;
+  pdl_launch_dependents();     // the next kernel may start its preamble now
+  pdl_wait();                  // everything below may depend on the kernel before (the set-up above overlapped it)
 
   if (warp == 4) {
     // ---------------- TMA producer ----------------
@@ -382,7 +384,7 @@ IERT_API int iert_attention_prefill_tc(const void* qkv, void* out, const IertBat
     configured = true;
   }
   dim3 grid(heads, (max_q_len + BM - 1) / BM, batch->n_seqs);
-  attention_prefill_tc_kernel<<<grid, THREADS, smem, stream>>>(map_q, map_kv, p, *batch);
+  launch_dep(attention_prefill_tc_kernel, grid, dim3(THREADS), smem, stream, map_q, map_kv, p, *batch);
   return cudaGetLastError() == cudaSuccess ? IERT_OK : IERT_CUDA_ERROR;
 }
 

@@ -33,10 +33,11 @@ class PreNormBlock(Block):
         return self._request(self.norm1, self.mixer, ctx)
 
     def _request(self, norm, part, ctx: StepContext):
-        """In one-token steps of up to 64 sequences a norm may ask whoever writes its input rows to do its
-        element-wise half (`NormRequest`), if the part behind it hands its input to a projection."""
+        """In steps of up to 64 tokens (one-token steps, short prompts) a norm may ask whoever writes its
+        input rows to do its element-wise half (`NormRequest`), if the part behind it hands its input to a
+        projection."""
         from . import fast_linear
-        if (self.rt.fast and ctx.kind == "decode" and ctx.n_tokens <= fast_linear.NORM_AHEAD_MAX_TOKENS
+        if (self.rt.fast and ctx.n_tokens <= fast_linear.NORM_AHEAD_MAX_TOKENS
                 and getattr(part, "takes_lazy_input", False) and fast_linear.norm_ahead_enabled()):
             return norm.request_ahead()
         return None
