@@ -11,6 +11,8 @@ raised here before anything is launched.
 """
 from __future__ import annotations
 
+import contextlib
+import gc
 from typing import List, Optional, Sequence, Tuple, Union
 
 import numpy as np
@@ -61,6 +63,22 @@ class _Staging:
         self.events[i] = ev
 
 
+@contextlib.contextmanager
+def _no_collection_while_capturing():
+    """Python's cyclic garbage collector may run at any allocation.  If it then destroys CUDA objects of an
+    engine that is no longer used (its graphs, its page-locked staging buffers) while this thread's stream
+    is capturing, the CUDA calls in their destructors fail and the process aborts.  Collect before the
+    capture and keep the collector off until it has ended."""
+    was_enabled = gc.isenabled()
+    gc.collect()
+    gc.disable()
+    try:
+        yield
+    finally:
+        if was_enabled:
+            gc.enable()
+
+
 class _DecodeGraph:
     """A captured one-token step for `nb` sequences: its own metadata buffer, workspace and
     logits buffer (a graph replays fixed addresses), and the graph."""
@@ -90,7 +108,7 @@ class _DecodeGraph:
             run()                                      # eager once: lazy set-up happens outside the capture
             torch.cuda.synchronize()
             before = B.launch_count
-            with torch.cuda.graph(self.graph):
+            with _no_collection_while_capturing(), torch.cuda.graph(self.graph):
                 run()
             self.launches = B.launch_count - before    # kernels one replay launches
         finally:
@@ -127,7 +145,7 @@ class _PromptGraph:
             run()                                      # eager once: lazy set-up happens outside the capture
             torch.cuda.synchronize()
             before = B.launch_count
-            with torch.cuda.graph(self.graph):
+            with _no_collection_while_capturing(), torch.cuda.graph(self.graph):
                 run()
             self.launches = B.launch_count - before
         finally:
