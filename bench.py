@@ -416,8 +416,10 @@ def main() -> int:
         # peak is a kernel that starts below the cap; its counterpart is a step after a second of rest.
         rested = rig.prefill(runs=3, warm=0, idle_s=1.0)
         rms = statistics.median(rested)
-        prefill["after_1s_idle"] = {"ms": round(rms, 3), "ms_min": round(min(rested), 3), "ms_max": round(max(rested), 3),
-                                    "frac": round(flops / (rms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4), "runs": len(rested)}
+        prefill.update({"ms_after_1s_idle": round(rms, 3), "ms_after_1s_idle_min": round(min(rested), 3),
+                        "ms_after_1s_idle_max": round(max(rested), 3),
+                        "frac_after_1s_idle": round(flops / (rms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+                        "runs_after_1s_idle": len(rested)})
     kernels = rig.kernel_table(a.batch, pk) if a.kernels else None
     load_s, layers, full_layers, max_context = rig.load_s, rig.layers, rig.full_layers, rig.max_context
     rig.close()
