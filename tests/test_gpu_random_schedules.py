@@ -112,3 +112,50 @@ def test_a_random_schedule_of_steps(name, seed, dtype):
     eng.cache.check()
     assert checked > 40
     compare(torch.cat(all_got), torch.cat(all_ref), dtype, f"{checked} logits gathered over the schedule")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_two_sessions_of_one_model_do_not_disturb_each_other(dtype):
+    """Two sessions of the same loaded model (shared weights, a cache and captured steps each), used in
+    turns, and a third one made and dropped in between: every logit as the plain implementation has it."""
+    import gc
+    from inference_engine_rust_b200 import LoadedModel
+    from inference_engine_rust_b200.weights import RandomSource
+    cfg = TINY["B"]
+    model = LoadedModel.random(cfg, seed=5, dtype=dtype, std=WEIGHT_STD)
+    src = RandomSource(model.model.expected_tensors(), 5, WEIGHT_STD, dtype=torch.float32)
+    w = {n: src.get(n) for n in src.names()}
+    if dtype == "bfloat16":
+        w = {n: t.to(torch.bfloat16).float() for n, t in w.items()}
+    rnd = P.bf16_rounding if dtype == "bfloat16" else P.no_rounding
+    rng = np.random.default_rng(9)
+    seqs = [rng.integers(0, cfg["vocab_size"], n).tolist() for n in (50, 71, 20, 66)]
+    refs = [P.forward(cfg, w, s, rnd) for s in seqs]
+    engines = [model.session(max_tokens=64 * 4, poison_cache=True).engine for _ in range(2)]
+    owner = [0, 1, 0, 1]                                   # which engine runs which sequence
+    slots, fed, got = [], [], [[] for _ in seqs]
+    for i, s in enumerate(seqs):
+        eng = engines[owner[i]]
+        slot = eng.open_sequence()
+        slots.append(slot)
+        got[i].append(eng.step([(slot, s[:10])], want="all").clone())
+        fed.append(10)
+    for round_ in range(10):
+        for e, eng in enumerate(engines):
+            mine = [i for i in range(len(seqs)) if owner[i] == e]
+            out = eng.step([(slots[i], [seqs[i][fed[i]]]) for i in mine], want="last")
+            for r, i in enumerate(mine):
+                got[i].append(out[r:r + 1].clone())
+                fed[i] += 1
+        if round_ == 3:                                    # a third session comes, steps (graphs and all) and goes
+            other = model.session(max_tokens=64 * 2).engine
+            s3 = other.open_sequence()
+            other.step([(s3, seqs[0][:5])], want="last")
+            for t in seqs[0][5:9]:
+                other.step([(s3, [t])], want="last")
+            del other
+            gc.collect()
+    for eng in engines:
+        eng.check_device()
+    for i in range(len(seqs)):
+        compare(torch.cat(got[i]), refs[i][:fed[i]], dtype, f"sequence {i} in session {owner[i]}")
