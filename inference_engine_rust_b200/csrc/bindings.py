@@ -123,6 +123,8 @@ def _declare(lib) -> None:
     lib.iert_gemm_tc_gated_scaled.restype = c_int
     lib.iert_gemm_tc_workspace_bytes.restype = c_longlong
     lib.iert_gemm_tc_counter_count.restype = c_int
+    lib.iert_gemm_tc_set_poll_limit.argtypes = [ctypes.c_uint]
+    lib.iert_gemm_tc_set_poll_limit.restype = None
     for name, args in sigs.items():
         fn = getattr(lib, name)
         fn.argtypes = args
@@ -295,6 +297,12 @@ class GemmScratch:
         if key not in cls._by_device:
             cls._by_device[key] = cls(device)
         return cls._by_device[key]
+
+
+def gemm_tc_set_poll_limit(polls: int) -> None:
+    """Polls of a tile's counter before a CTA of the split-K projection gives up waiting for the tile's other
+    CTAs (0: the default, about a second).  For tests of that bounded wait."""
+    core().iert_gemm_tc_set_poll_limit(int(polls))
 
 
 def gemm_tc(x, w, out, M: int, mode: int, err, stream, force_bt: int = 0, force_splits: int = 0,

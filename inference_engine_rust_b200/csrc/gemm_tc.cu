@@ -84,6 +84,7 @@ struct GemmParams {
   IertNormAhead ahead;  // split-K residual add, tiles of 32 or 64 tokens: ahead.scaled_out != null: the reduction also
                         // writes the next norm's first half
   int trace_seq;        // >= 0: the launch's row in the trace (builds with IERT_GEMM_TRACE only)
+  uint32_t poll_limit;  // polls of a tile's counter before a CTA gives up waiting for the other CTAs of its tile
 };
 
 // Built with -DIERT_GEMM_TRACE (IERT_EXTRA_DEFINES=IERT_GEMM_TRACE), the last 64 launches record when their
@@ -465,7 +466,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       if (chained && split > 0) {
         if (threadIdx.x == 64) {
           int seen = 0;
-          for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+          for (uint32_t i = 0; i < p.poll_limit; ++i) {
             asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(p.counters + tile) : "memory");
             if (seen >= split) break;
             __nanosleep(64);
@@ -685,7 +686,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           if (threadIdx.x == 64) {
             atomicAdd(&p.counters[tile], 1);
             int seen = 0;
-            for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+            for (uint32_t i = 0; i < p.poll_limit; ++i) {
               asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(p.counters + tile) : "memory");
               if (seen >= p.splits) break;
               __nanosleep(32);
@@ -892,10 +893,13 @@ int g_trace_meta[TRACE_LAUNCHES][8];
 int g_trace_next = 0;
 #endif
 
+uint32_t g_poll_limit = WAIT_LIMIT;
+
 template <int BT, bool GATED>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, GemmParams p, int grid, cudaStream_t stream,
            const CUtensorMap* mo = nullptr) {
   p.trace_seq = -1;
+  p.poll_limit = g_poll_limit;
 #ifdef IERT_GEMM_TRACE
   p.trace_seq = g_trace_next % TRACE_LAUNCHES;
   int* tm = g_trace_meta[p.trace_seq];
@@ -1139,6 +1143,11 @@ IERT_API int iert_gemm_tc_trace_read(unsigned long long* stamps, int* meta) {
   return IERT_OK;
 }
 #endif
+
+// How many times a CTA polls its tile's counter before it gives up waiting for the tile's other CTAs (default
+// 2^22, about a second; 0 restores the default).  For tests that let such a wait run out: the kernel then sets
+// IERT_ERR_WAIT_EXPIRED in the error word, skips the work that depended on the wait and ends like any other.
+IERT_API void iert_gemm_tc_set_poll_limit(unsigned int polls) { g_poll_limit = polls ? polls : WAIT_LIMIT; }
 
 IERT_API int iert_gemm_tc(const void* x, long long ldx, const void* w, long long ldw, void* out, int out_dtype,
                           long long ldo, int M, int N, int K, int mode, float* ws, long long ws_bytes,

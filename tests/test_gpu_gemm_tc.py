@@ -267,3 +267,40 @@ def test_split_k_store_applies_the_norms_second_half(M, N, K, parts):
         bound = 2e-3 * (K ** 0.5) * 0.5 + 1e-5 * ref.abs() + (2.0 ** -8) * ref.abs() * (odt == torch.bfloat16)
         diff = (out.double() - ref).abs()
         assert torch.isfinite(out).all() and bool((diff <= bound).all()), f"{odt}: max diff {diff.max().item():.4g}"
+
+
+def test_a_wait_between_ctas_that_runs_out_is_reported_and_harmless():
+    """The splits of a tile wait for one another on the tile's counter, with a limit.  Here the counter of
+    one tile is set so that its splits can never all be counted in (and the limit is shortened, so that the
+    test takes milliseconds): the kernel ends by itself, the device error word says that a wait expired, the
+    other tile's result is right, and after the counter is put back the next launch is right everywhere."""
+    from inference_engine_rust_b200.csrc import bindings as B
+    M, N, K, splits = 8, 256, 2048, 4                      # two tiles of 128 rows, four splits each: 8 CTAs
+    g = torch.Generator(device=DEV).manual_seed(3)
+    x = torch.randn(M, K, device=DEV, generator=g).bfloat16()
+    w = (torch.randn(N, K, device=DEV, generator=g) * 0.5).bfloat16()
+    ref = x.double() @ w.double().t()
+    bound = 2e-3 * (K ** 0.5) * 0.5
+    sc = B.GemmScratch.get(torch.device(DEV))
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    torch.cuda.synchronize()
+    assert int(sc.counters[:2].abs().sum()) == 0, "counters are zero between launches"
+    B.gemm_tc_set_poll_limit(1 << 12)
+    try:
+        sc.counters[0] = -1000                             # tile 0: never reaches 4
+        out = torch.full((M, N), float("nan"), device=DEV)
+        assert B.gemm_tc(x, w, out, M, B.GEMM_STORE, err, B.stream_ptr(), force_splits=splits)
+        torch.cuda.synchronize()
+        assert err.item() & B.ERR_WAIT_EXPIRED, "the expired wait was not reported"
+        assert torch.isnan(out[:, :128]).all(), "tile 0 must not have been written from partial sums"
+        assert bool(((out[:, 128:].double() - ref[:, 128:]).abs() <= bound).all()), "tile 1 is independent of tile 0"
+    finally:
+        B.gemm_tc_set_poll_limit(0)
+        sc.counters.zero_()
+        err.zero_()
+    out = torch.full((M, N), float("nan"), device=DEV)
+    assert B.gemm_tc(x, w, out, M, B.GEMM_STORE, err, B.stream_ptr(), force_splits=splits)
+    torch.cuda.synchronize()
+    assert err.item() == 0
+    assert bool(((out.double() - ref).abs() <= bound).all())
+    assert int(sc.counters[:2].abs().sum()) == 0
