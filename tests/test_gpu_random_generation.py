@@ -68,3 +68,21 @@ def test_random_workload_with_a_temperature(models, name, seed):
         runs.append(by_request)
     assert runs[0] == runs[1] == runs[2]
     assert len({tuple(t) for t in runs[0]}) > 1
+
+
+@pytest.mark.parametrize("run_ahead", [True, False])
+def test_the_context_limit_ends_a_request(models, run_ahead):
+    """A cache whose sequences hold at most L positions: a request ends with the token chosen from the last
+    position that fits ("context"), the others end by their own length; tokens equal the plain loop's."""
+    cfg, model, w = models["A"]
+    rng = np.random.default_rng(11)
+    prompts = [rng.integers(0, cfg["vocab_size"], n).tolist() for n in (60, 10, 63)]
+    limit, new = 66, 9
+    session = model.session(max_tokens=64 * 2 * 3, max_sequences=3, max_seq_len=limit, poison_cache=True)
+    res = session.generate(prompts, max_new_tokens=new, stop_ids=[], full=True, run_ahead=run_ahead)
+    for p, r in zip(prompts, res):
+        fits = min(new, limit - len(p) + 1)               # the token after the last position is still chosen
+        assert r.tokens == P.generate_greedy(cfg, w, p, fits)
+        assert r.finish_reason == ("length" if fits == new else "context")
+    session.engine.cache.check()
+    assert session.engine.cache.slots.free_count == session.engine.cache.n_slots
