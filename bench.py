@@ -233,6 +233,51 @@ class Rig:
                 times.append(start.elapsed_time(end))
         return times
 
+    # ---- where a layer's time goes inside the replayed graph --------------------------------------
+    def timeline(self, batch: int):
+        """Medians of the projection kernels' time stamps (device-wide timer) over the CTAs of each launch of
+        the last replayed one-token step.  Needs a build that records them: IERT_EXTRA_DEFINES=IERT_GEMM_TRACE."""
+        import ctypes
+        import numpy as np
+        from inference_engine_rust_b200.csrc import bindings as B
+        lib = B.core()
+        if not hasattr(lib, "iert_gemm_tc_trace_read"):
+            return None
+        slots = self.prefill_slots(batch)
+        self.decode_device(slots, 6, 3)
+        self.torch.cuda.synchronize()
+        launches = []
+        names = {"tc": ["start", "weights asked", "dependency", "operands", "last MMA", "accumulator", "partial out", "end"],
+                 "rows": ["start", "weights asked", "dependency", "last stage asked", "first stage full", "last stage full", "", "end"]}
+        for kind, fn, ctas in (("tc", "iert_gemm_tc_trace_read", 304), ("rows", "iert_gemm_rows_trace_read", 512)):
+            stamps = np.zeros((64, ctas, 8), dtype=np.uint64)
+            meta = np.zeros((64, 8), dtype=np.int32)
+            f = getattr(lib, fn)
+            f.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
+            if f(stamps.ctypes.data, meta.ctypes.data) != 0:
+                return None
+            for i in range(64):
+                if meta[i, 2] > 0:
+                    st = stamps[i, :min(int(meta[i, 4]), ctas)].astype(np.int64)
+                    if (st[:, 0] > 0).any():
+                        launches.append((kind, meta[i].tolist(), st))
+        launches.sort(key=lambda e: np.median(e[2][:, 0][e[2][:, 0] > 0]))
+        launches = launches[-(4 * self.layers + 1):]              # the last step's projections and its output head
+        t0 = min(int(e[2][e[2] > 0].min()) for e in launches)
+        out = []
+        for kind, meta, st in launches:
+            row = {"kernel": "gemm_tc" if kind == "tc" else "gemm_rows", "tokens": meta[1], "rows": meta[2], "k": meta[3],
+                   "ctas": meta[4], "us": {}}
+            for c, name in enumerate(names[kind]):
+                col = st[:, c]
+                col = col[col > 0]
+                if name and len(col):
+                    row["us"][name] = round((float(np.median(col)) - t0) / 1e3, 2)
+            row["us"]["last CTA's end"] = round((int(st.max()) - t0) / 1e3, 2)
+            out.append(row)
+        self.release(slots)
+        return out
+
     # ---- the dominant kernels one by one -----------------------------------------------------
     def kernel_table(self, batch: int, pk):
         """CUDA-event times of the projections (at `batch` tokens and at the prefill length) and of
@@ -360,6 +405,10 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=CONTEXT, help="tokens each sequence holds when decoding starts")
     ap.add_argument("--no-other-sizes", action="store_true",
                     help="skip the short measurements at Mistral 7B v0.3 and NeMo 12B sizes (points v03_*, nemo_*)")
+    ap.add_argument("--timeline", action="store_true",
+                    help="print, instead of the benchmark line, when the CTAs of each projection launch of a replayed "
+                         "one-token step passed their marked points (us, medians per launch); needs "
+                         "IERT_EXTRA_DEFINES=IERT_GEMM_TRACE in the environment, and --layers of 2 or 3")
     ap.add_argument("--kernels", action="store_true",
                     help="also time the dominant kernels one by one with CUDA events (projections and decode "
                          "attention at the decode batch, projections at the prefill length): key 'kernels'")
@@ -377,6 +426,16 @@ def main() -> int:
         a.warmup = 3
 
     pk = peaks()
+    if a.timeline:
+        rig = Rig(a.sizes, a.layers or 3, [a.batch], a.context, a.max_context, a.prefill_tokens, a.steps, a.warmup)
+        rows = rig.timeline(a.batch)
+        rig.close()
+        if rows is None:
+            print("bench.py --timeline: the kernels were built without IERT_EXTRA_DEFINES=IERT_GEMM_TRACE")
+            return 2
+        for r in rows:
+            print(json.dumps(r))
+        return 0
     batches = [a.batch] + [int(b) for b in a.points.split(",") if b.strip()]
     rig = Rig(a.sizes, a.layers, batches, a.context, a.max_context, a.prefill_tokens, a.steps, a.warmup)
     cfg, vocab = rig.cfg, rig.vocab
