@@ -355,6 +355,38 @@ class Rig:
                     "us": round(us, 2), "gb_s": round(kv_bytes / us / 1e3, 1), "frac": round(kv_bytes / us / 1e3 / pk["hbm_gbs"], 3)})
         eng.check_device()
         self.release(slots)
+        # prompt attention over one prompt of the prefill length (the kernel alone: queries, keys and values
+        # of one layer from a random projection, a fresh buffer per launch so that nothing waits in the L2)
+        import numpy as np
+        T, W = self.prefill_tokens, mix.q_dim + 2 * mix.kv_dim
+        if T >= 2:
+            reps = max(2, min(8, int(400e6 // (T * W * 2)) + 1))
+            bufs = [(torch.randn(T, W, device=rt.device) * 0.7).bfloat16() for _ in range(reps)]
+            p_out = torch.empty(T, mix.q_dim, device=rt.device, dtype=torch.bfloat16)
+            arrs = [torch.tensor(a, dtype=torch.int32, device=rt.device) for a in ([0, T], [0], np.zeros(T, dtype=np.int32), [0])]
+            view = B.BatchView(cu_q=arrs[0].data_ptr(), slot_ids=arrs[1].data_ptr(), tok_seq=arrs[2].data_ptr(),
+                               pos0=arrs[3].data_ptr(), n_seqs=1, n_tokens=T)
+            turn = [0]
+
+            def one():
+                turn[0] += 1
+                assert B.attention_prefill(bufs[turn[0] % reps], p_out, view, mix.heads, mix.kv_heads, mix.head_dim,
+                                           mix.window or 0, mix.scale, T, stream, err=rt.err)
+            for _ in range(3):
+                one()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            start.record()
+            for _ in range(2 * reps):
+                one()
+            end.record()
+            torch.cuda.synchronize()
+            us = start.elapsed_time(end) * 1e3 / (2 * reps)
+            window = mix.window or T
+            flops = 4.0 * mix.head_dim * mix.heads * sum(min(i + 1, window) for i in range(T))
+            out.append({"kernel": "prompt attention", "where": f"one prompt of {T} tokens", "us": round(us, 2),
+                        "tflops": round(flops / us / 1e6, 1), "frac": round(flops / us / 1e6 / pk["bf16_tflops"], 3)})
+            eng.check_device()
         return out
 
 
